@@ -1,0 +1,230 @@
+// Embedding gather, row gather, fused residual-add + RMSNorm, gated
+// activation, dtype casts.  Every kernel takes any row length; rows that can be
+// moved in 16-byte pieces are, others go element by element.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// row copies: out[r, :] = src[index[r], :]
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(const int* __restrict__ index, const T* __restrict__ src, T* __restrict__ out,
+                                   int rows, int cols, long long src_stride, long long out_stride, int src_rows,
+                                   int status_code, int* status) {
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const int s = index[r];
+  if (s < 0 || s >= src_rows) {
+    if (threadIdx.x == 0) ullm_report(status, status_code, r, s);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) out[(long long)r * out_stride + c] = from_f32<T>(0.f);
+    return;
+  }
+  const T* sp = src + (long long)s * src_stride;
+  T* op = out + (long long)r * out_stride;
+  if (rows_are_16B<T>(src, cols, src_stride) && rows_are_16B<T>(out, cols, out_stride)) {
+    const int n16 = (int)((cols * sizeof(T)) / 16);
+    const uint4* s4 = reinterpret_cast<const uint4*>(sp);
+    uint4* o4 = reinterpret_cast<uint4*>(op);
+    for (int c = threadIdx.x; c < n16; c += blockDim.x) o4[c] = s4[c];
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) op[c] = sp[c];
+  }
+}
+
+template <typename T>
+static int gather_rows_launch(const int* index, const void* src, void* out, int rows, int cols, long long src_stride,
+                              long long out_stride, int src_rows, int code, int* status, cudaStream_t st) {
+  if (rows == 0) return ULLM_OK;
+  int threads = 256;
+  if (cols * (int)sizeof(T) <= 16 * 64) threads = 64;
+  gather_rows_kernel<T><<<rows, threads, 0, st>>>(index, (const T*)src, (T*)out, rows, cols, src_stride, out_stride,
+                                                   src_rows, code, status);
+  return ullm_launch_status();
+}
+
+extern "C" int ullm_embedding(int dtype, const int* ids, const void* table, void* out, int tokens, int hidden,
+                              int vocab, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || hidden <= 0 || vocab <= 0) return ULLM_ERR_BAD_SIZE;
+  if (dtype == ULLM_DTYPE_F32)
+    return gather_rows_launch<float>(ids, table, out, tokens, hidden, hidden, hidden, vocab, ULLM_STATUS_TOKEN_ID,
+                                     status, st);
+  if (dtype == ULLM_DTYPE_BF16)
+    return gather_rows_launch<__nv_bfloat16>(ids, table, out, tokens, hidden, hidden, hidden, vocab,
+                                             ULLM_STATUS_TOKEN_ID, status, st);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_gather_rows(int dtype, const int* rows_index, const void* src, void* out, int rows, int cols,
+                                int src_rows, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows < 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
+  if (dtype == ULLM_DTYPE_F32)
+    return gather_rows_launch<float>(rows_index, src, out, rows, cols, cols, cols, src_rows, ULLM_STATUS_ROW, status,
+                                     st);
+  if (dtype == ULLM_DTYPE_BF16)
+    return gather_rows_launch<__nv_bfloat16>(rows_index, src, out, rows, cols, cols, cols, src_rows, ULLM_STATUS_ROW,
+                                             status, st);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// fused residual add + RMSNorm
+//   s = x (+ residual)          32-bit
+//   residual <- round(s)        (if residual given)
+//   out <- round(s * rsqrt(mean(s^2) + eps) * w)
+// One block per row; the unrounded sums wait in shared memory between the two
+// passes, so the norm sees the 32-bit sum while the stored residual is rounded.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* x, T* residual, const float* __restrict__ w, T* out, int cols,
+                                   float eps) {  // out may be x
+  extern __shared__ float row[];  // cols floats, then 33 for the reduction
+  float* scratch = row + cols;
+  const long long base = (long long)blockIdx.x * cols;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float s = to_f32(x[base + c]);
+    if (residual != nullptr) {
+      s += to_f32(residual[base + c]);
+      residual[base + c] = from_f32<T>(s);
+    }
+    row[c] = s;
+    acc += s * s;
+  }
+  const float total = block_sum(acc, scratch);
+  const float rstd = rsqrtf(total / (float)cols + eps);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) out[base + c] = from_f32<T>(row[c] * rstd * w[c]);
+}
+
+static int g_rmsnorm_smem_set[2] = {0, 0};
+
+template <typename T>
+static int add_rmsnorm_launch(int which, const void* x, void* residual, const float* w, void* out, int rows, int cols,
+                              float eps, cudaStream_t st) {
+  if (rows == 0) return ULLM_OK;
+  const size_t smem = (size_t)(cols + 33) * sizeof(float);
+  if (smem > 200 * 1024) return ULLM_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024 && !g_rmsnorm_smem_set[which]) {
+    if (cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess)
+      return ULLM_ERR_LAUNCH;
+    g_rmsnorm_smem_set[which] = 1;
+  }
+  int threads = 32;
+  while (threads < 1024 && threads * 4 < cols) threads <<= 1;
+  add_rmsnorm_kernel<T><<<rows, threads, smem, st>>>((const T*)x, (T*)residual, w, (T*)out, cols, eps);
+  return ullm_launch_status();
+}
+
+extern "C" int ullm_add_rmsnorm(int dtype, const void* x, void* residual, const float* weight, void* out, int rows,
+                                int cols, float eps, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows < 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
+  if (dtype == ULLM_DTYPE_F32) return add_rmsnorm_launch<float>(0, x, residual, weight, out, rows, cols, eps, st);
+  if (dtype == ULLM_DTYPE_BF16)
+    return add_rmsnorm_launch<__nv_bfloat16>(1, x, residual, weight, out, rows, cols, eps, st);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// gated activation: out[t, i] = act(gu[t, i]) * gu[t, I + i], in 32-bit
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
+__device__ __forceinline__ float act_gelu_tanh(float g) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * g * (1.f + tanhf(k * (g + 0.044715f * g * g * g)));
+}
+
+template <typename T, int ACT>
+__global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int inter) {
+  const long long n = rows * inter;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / inter;
+    const int c = (int)(i - t * inter);
+    const float g = to_f32(gu[t * 2 * inter + c]);
+    const float u = to_f32(gu[t * 2 * inter + inter + c]);
+    const float a = ACT == 0 ? act_silu(g) : act_gelu_tanh(g);
+    out[i] = from_f32<T>(a * u);
+  }
+}
+
+// bf16 rows whose halves start on 16-byte boundaries: 8 elements per thread.
+template <int ACT>
+__global__ void act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                      long long rows, int inter) {
+  const int per_row = inter / 8;
+  const long long n = rows * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + c);
+    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv);
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv);
+    uint4 ov;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gf = to_f32(g[k]);
+      const float a = ACT == 0 ? act_silu(gf) : act_gelu_tanh(gf);
+      o[k] = __float2bfloat16_rn(a * to_f32(u[k]));
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + c) = ov;
+  }
+}
+
+extern "C" int ullm_act_mul(int dtype, int act, const void* gate_up, void* out, int rows, int inter, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows < 0 || inter <= 0) return ULLM_ERR_BAD_SIZE;
+  if (act != 0 && act != 1) return ULLM_ERR_UNSUPPORTED;
+  if (rows == 0) return ULLM_OK;
+  const long long n = (long long)rows * inter;
+  const int threads = 256;
+  if (dtype == ULLM_DTYPE_BF16 && inter % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+    long long blocks = (n / 8 + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (act == 0)
+      act_mul_bf16x8_kernel<0><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+                                                               rows, inter);
+    else
+      act_mul_bf16x8_kernel<1><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+                                                               rows, inter);
+    return ullm_launch_status();
+  }
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == ULLM_DTYPE_F32) {
+    if (act == 0)
+      act_mul_kernel<float, 0><<<(int)blocks, threads, 0, st>>>((const float*)gate_up, (float*)out, rows, inter);
+    else
+      act_mul_kernel<float, 1><<<(int)blocks, threads, 0, st>>>((const float*)gate_up, (float*)out, rows, inter);
+  } else if (dtype == ULLM_DTYPE_BF16) {
+    if (act == 0)
+      act_mul_kernel<__nv_bfloat16, 0><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up,
+                                                                       (__nv_bfloat16*)out, rows, inter);
+    else
+      act_mul_kernel<__nv_bfloat16, 1><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up,
+                                                                       (__nv_bfloat16*)out, rows, inter);
+  } else {
+    return ULLM_ERR_BAD_DTYPE;
+  }
+  return ullm_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// bf16 -> f32 cast of a contiguous array (logits for the sampler and the host)
+// ---------------------------------------------------------------------------
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = __bfloat162float(in[i]);
+}
+
+extern "C" int ullm_cast_bf16_f32(const void* in, float* out, long long n, void* stream) {
+  if (n < 0) return ULLM_ERR_BAD_SIZE;
+  if (n == 0) return ULLM_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_bf16_f32_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)in, out, n);
+  return ullm_launch_status();
+}

@@ -1,0 +1,266 @@
+"""Python face of the compiled kernels: loads the shared library with ctypes
+and wraps each extern "C" launcher in a method that checks devices, dtypes,
+shapes and contiguity before passing raw pointers and the current CUDA stream.
+
+There is no CPU path here: a tensor that is not on a CUDA device is an error,
+and a missing or unbuildable library is an error at first use.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_ERRORS = {
+    1: "unsupported dtype",
+    2: "bad size argument",
+    3: "CUDA launch failed",
+    4: "size not supported by this kernel",
+}
+STATUS_MESSAGES = {
+    1: "token id out of range (row {index}: id {value})",
+    2: "position out of range of the position table (token {index}: position {value})",
+    3: "cache slot out of range (token {index}: slot {value})",
+    4: "row index out of range (row {index}: {value})",
+    5: "page id out of range in a block table (token {index}: page {value})",
+}
+
+MAX_HEAD_DIM = 512
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check_attention_sizes(num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int) -> None:
+    """Sizes the attention kernels take; anything else is refused here, at
+    construction, with the reason."""
+    if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
+        raise ValueError(f"num_heads={num_heads} must be a positive multiple of num_kv_heads={num_kv_heads}")
+    if head_dim <= 0 or head_dim > MAX_HEAD_DIM:
+        raise ValueError(f"head_dim={head_dim}: the attention kernels take 1..{MAX_HEAD_DIM}")
+    if rotary_dim < 0 or rotary_dim > head_dim or rotary_dim % 2:
+        raise ValueError(f"rotary_dim={rotary_dim} must be even and at most head_dim={head_dim}")
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}: the kernels run on CUDA tensors only (no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+class Kernels:
+    def __init__(self, lib_path: str | None = None):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine has no CPU path")
+        self.lib_path = lib_path or build()
+        self.lib = ctypes.CDLL(self.lib_path)
+        self._declare()
+        self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self._f32_out_mm = None
+
+    # -- ctypes signatures --------------------------------------------------
+    def _declare(self) -> None:
+        L = self.lib
+        P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+        sig = {
+            "ullm_embedding": [I, P, P, P, I, I, I, P, P],
+            "ullm_gather_rows": [I, P, P, P, I, I, I, P, P],
+            "ullm_add_rmsnorm": [I, P, P, P, P, I, I, F, P],
+            "ullm_act_mul": [I, I, P, P, I, I, P],
+            "ullm_cast_bf16_f32": [P, P, LL, P],
+            "ullm_qk_norm_rope_store": [I, P, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, LL, P, P],
+            "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_argmax": [P, LL, I, I, P, P],
+            "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P],
+        }
+        for name, args in sig.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = c_int
+
+    @staticmethod
+    def _check(code: int, what: str) -> None:
+        if code != 0:
+            raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+
+    # -- status word ----------------------------------------------------------
+    def raise_on_status(self) -> None:
+        """Reads the device status word (synchronizes) and raises if a kernel
+        refused an out-of-range index since the last call."""
+        s = self.status.tolist()
+        if s[0] != 0:
+            self.status.zero_()
+            msg = STATUS_MESSAGES.get(s[0], "status {code}").format(index=s[1], value=s[2], code=s[0])
+            raise KernelError(f"a kernel refused an index: {msg}")
+
+    # -- library matrix products ---------------------------------------------
+    def linear(self, x, weight, out, bias=None):
+        """out = x @ weight.T (+ bias).  The vendor library's matrix product,
+        float32 without any reduced-precision mode."""
+        _need(x, "x")
+        _need(out, "out")
+        if bias is not None:
+            torch.addmm(bias, x, weight.t(), out=out)
+        else:
+            torch.mm(x, weight.t(), out=out)
+        return out
+
+    def linear_f32_out(self, x, weight, out):
+        """out (float32) = x @ weight.T for x/weight in float32 or bfloat16."""
+        _need(out, "out", torch.float32)
+        if x.dtype == torch.float32:
+            torch.mm(x, weight.t(), out=out)
+            return out
+        if self._f32_out_mm is None:
+            try:
+                torch.mm(x[:1], weight[:8].t(), out_dtype=torch.float32)
+                self._f32_out_mm = True
+            except (TypeError, RuntimeError):
+                self._f32_out_mm = False
+        if self._f32_out_mm:
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        else:
+            tmp = torch.mm(x, weight.t())
+            self._check(self.lib.ullm_cast_bf16_f32(_ptr(tmp), _ptr(out), tmp.numel(), _stream()), "cast")
+        return out
+
+    # -- hand-written kernels ----------------------------------------------------
+    def embedding(self, ids, table, out):
+        _need(ids, "ids", torch.int32)
+        _need(table, "table")
+        _need(out, "out", table.dtype)
+        T, H = out.shape
+        if ids.numel() < T or table.shape[1] != H:
+            raise KernelError(f"embedding: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_embedding(_DT[table.dtype], _ptr(ids), _ptr(table), _ptr(out), T, H,
+                                            table.shape[0], _ptr(self.status), _stream()), "embedding")
+
+    def gather_rows(self, src, rows, out):
+        _need(src, "src")
+        _need(rows, "rows", torch.int32)
+        _need(out, "out", src.dtype)
+        R, C = out.shape
+        if src.shape[1] != C or rows.numel() < R:
+            raise KernelError(f"gather_rows: src {tuple(src.shape)}, rows {tuple(rows.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_gather_rows(_DT[src.dtype], _ptr(rows), _ptr(src), _ptr(out), R, C, src.shape[0],
+                                              _ptr(self.status), _stream()), "gather_rows")
+
+    def add_rmsnorm(self, x, residual, weight, eps, out):
+        _need(x, "x")
+        _need(weight, "weight", torch.float32)
+        _need(out, "out", x.dtype)
+        if residual is not None:
+            _need(residual, "residual", x.dtype)
+            if residual.shape != x.shape:
+                raise KernelError("add_rmsnorm: residual shape differs from x")
+        rows, cols = x.shape
+        if weight.numel() != cols or out.shape != x.shape:
+            raise KernelError(f"add_rmsnorm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_add_rmsnorm(_DT[x.dtype], _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), rows,
+                                              cols, float(eps), _stream()), f"add_rmsnorm (row length {cols})")
+
+    def act_mul(self, gate_up, out, act: int = 0):
+        _need(gate_up, "gate_up")
+        _need(out, "out", gate_up.dtype)
+        rows, inter = out.shape
+        if gate_up.shape != (rows, 2 * inter):
+            raise KernelError(f"act_mul: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_act_mul(_DT[gate_up.dtype], act, _ptr(gate_up), _ptr(out), rows, inter, _stream()),
+                    "act_mul")
+
+    def check_attention_sizes(self, *a):
+        check_attention_sizes(*a)
+
+    def qk_norm_rope_store(self, qkv, num_q, num_kv, head_dim, q_w, k_w, eps, cos, sin, rotary_dim, positions,
+                           slot_mapping, k_pages, v_pages):
+        _need(qkv, "qkv")
+        T, W = qkv.shape
+        if W != (num_q + 2 * num_kv) * head_dim:
+            raise KernelError(f"qk_norm_rope_store: qkv row length {W} != (Hq + 2 Hkv) * D")
+        for t, n in ((q_w, "q_norm weight"), (k_w, "k_norm weight"), (cos, "cos table"), (sin, "sin table")):
+            if t is not None:
+                _need(t, n, torch.float32)
+        max_pos = 0
+        if rotary_dim > 0:
+            if cos is None or sin is None or cos.shape != sin.shape or cos.shape[1] != rotary_dim // 2:
+                raise KernelError("qk_norm_rope_store: cos/sin tables must be [positions, rotary_dim / 2]")
+            max_pos = cos.shape[0]
+            _need(positions, "positions", torch.int32)
+        num_slots = 0
+        if slot_mapping is not None:
+            _need(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages, "k_pages", qkv.dtype)
+            _need(v_pages, "v_pages", qkv.dtype)
+            if k_pages.shape[-2:] != (num_kv, head_dim) or v_pages.shape != k_pages.shape:
+                raise KernelError(f"qk_norm_rope_store: pages {tuple(k_pages.shape)} do not end in (Hkv, D)")
+            num_slots = k_pages.numel() // (num_kv * head_dim)
+        self._check(self.lib.ullm_qk_norm_rope_store(
+            _DT[qkv.dtype], _ptr(qkv), T, num_q, num_kv, head_dim, _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos),
+            _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
+            num_slots, _ptr(self.status), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
+
+    def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
+                        head_dim, page_size, window, scale, ctx=None):
+        """Attention of every row of the flat batch over its request's pages.
+        `qkv` holds q in its first num_q * head_dim columns."""
+        _need(qkv, "qkv")
+        _need(out, "out", qkv.dtype)
+        _need(k_pages, "k_pages", qkv.dtype)
+        _need(v_pages, "v_pages", qkv.dtype)
+        for t, n in ((block_table, "block_table"), (req_slots, "req_slots"), (cu_q, "cu_q"), (kv_len, "kv_len"), (token_req, "token_req")):
+            _need(t, n, torch.int32)
+        T = out.shape[0]
+        if out.shape[1] != num_q * head_dim or qkv.shape[0] < T:
+            raise KernelError(f"paged_attention: out {tuple(out.shape)}, qkv {tuple(qkv.shape)}")
+        if k_pages.shape[-3:] != (page_size, num_kv, head_dim):
+            raise KernelError(f"paged_attention: pages {tuple(k_pages.shape)} != [*, {page_size}, {num_kv}, {head_dim}]")
+        num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
+        self._check(self.lib.ullm_paged_attention_generic(
+            _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+            block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), _ptr(token_req), T, num_q, num_kv, head_dim, page_size,
+            int(window), float(scale), num_pages, _ptr(self.status), _stream()),
+            f"paged_attention (head_dim {head_dim})")
+
+    def argmax(self, logits, out):
+        _need(logits, "logits", torch.float32, contiguous=False)
+        _need(out, "out", torch.int32)
+        R, V = logits.shape
+        if logits.stride(1) != 1 or out.numel() < R:
+            raise KernelError("argmax: logits rows must be contiguous and out must hold one id per row")
+        self._check(self.lib.ullm_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+
+    def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None):
+        _need(logits, "logits", torch.float32, contiguous=False)
+        R, V = logits.shape
+        if logits.stride(1) != 1:
+            raise KernelError("sample: logits rows must be contiguous")
+        for t, n, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                         (top_p, "top_p", torch.float32), (min_p, "min_p", torch.float32),
+                         (uniform, "uniform", torch.float32), (out, "out", torch.int32)):
+            _need(t, n, dt)
+            if t.numel() < R:
+                raise KernelError(f"sample: {n} holds {t.numel()} values for {R} rows")
+        if probs_out is not None:
+            _need(probs_out, "probs_out", torch.float32)
+            if probs_out.shape != (R, V):
+                raise KernelError("sample: probs_out must be [rows, vocab]")
+        self._check(self.lib.ullm_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k),
+                                         _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out), _ptr(probs_out),
+                                         _stream()), "sample")

@@ -1,0 +1,116 @@
+// Per-head q/k RMSNorm, position rotation, and the write of this step's keys
+// and values into the cache pages, fused: one warp per (token, head).
+//
+//   q head: x <- rope(norm(x))   written back in place (the attention kernel
+//                                reads q from the projection buffer)
+//   k head: cache[slot] <- rope(norm(x))
+//   v head: cache[slot] <- x
+//
+// Norm, rotation angles (cos/sin read from 32-bit tables) and the rotation
+// itself are computed in 32-bit; one rounding at the store.  Rotary layout:
+// the first rotary_dim elements of a head are two halves (x1 | x2); o1 = x1 cos
+// - x2 sin and o2 = x2 cos + x1 sin stay in place as (o1 | o2).
+#include "common.cuh"
+
+#define QK_MAX_HEAD_DIM 512
+#define QK_WARPS 4
+
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num_kv, int head_dim,
+                                          const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                          int rotary_dim, int max_positions, const int* __restrict__ positions,
+                                          const int* __restrict__ slot_mapping, T* k_cache, T* v_cache,
+                                          long long num_slots, int* status) {
+  __shared__ float sh[QK_WARPS][QK_MAX_HEAD_DIM];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = num_q + 2 * num_kv;
+  const long long unit = (long long)blockIdx.x * QK_WARPS + warp;
+  if (unit >= (long long)tokens * heads) return;
+  const int t = (int)(unit / heads);
+  const int h = (int)(unit - (long long)t * heads);
+  const bool is_q = h < num_q;
+  const bool is_k = !is_q && h < num_q + num_kv;
+  long long slot = -1;
+  if (!is_q) {
+    if (slot_mapping == nullptr) return;  // this execution reads another one's cache
+    slot = slot_mapping[t];
+    if (slot < 0) return;  // padding row
+    if (slot >= num_slots) {
+      if (lane == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
+      return;
+    }
+  }
+  T* src = qkv + (long long)t * heads * head_dim + (long long)h * head_dim;
+  float* y = sh[warp];
+  if (!is_q && !is_k) {  // value head: plain copy
+    const int kvh = h - num_q - num_kv;
+    T* dst = v_cache + (slot * num_kv + kvh) * head_dim;
+    for (int e = lane; e < head_dim; e += 32) dst[e] = src[e];
+    return;
+  }
+  const float* w = is_q ? q_w : k_w;
+  float ss = 0.f;
+  for (int e = lane; e < head_dim; e += 32) {
+    const float v = to_f32(src[e]);
+    y[e] = v;
+    ss += v * v;
+  }
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)head_dim + eps);
+    for (int e = lane; e < head_dim; e += 32) y[e] = y[e] * rstd * w[e];
+  }
+  __syncwarp();
+  T* dst = is_q ? src : k_cache + (slot * num_kv + (h - num_q)) * head_dim;
+  const int half = rotary_dim / 2;
+  int pos = 0;
+  if (rotary_dim > 0) {
+    pos = positions[t];
+    if (pos < 0 || pos >= max_positions) {
+      if (lane == 0) ullm_report(status, ULLM_STATUS_POSITION, t, pos);
+      pos = 0;
+    }
+  }
+  const float* cr = cos_t + (long long)pos * half;
+  const float* sr = sin_t + (long long)pos * half;
+  for (int e = lane; e < head_dim; e += 32) {
+    float o;
+    if (e < half) {
+      o = y[e] * cr[e] - y[e + half] * sr[e];
+    } else if (e < rotary_dim) {
+      const int j = e - half;
+      o = y[e] * cr[j] + y[j] * sr[j];
+    } else {
+      o = y[e];
+    }
+    dst[e] = from_f32<T>(o);
+  }
+}
+
+extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
+                                       const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                       const float* sin_t, int rotary_dim, int max_positions, const int* positions,
+                                       const int* slot_mapping, void* k_cache, void* v_cache, long long num_slots,
+                                       int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0) return ULLM_ERR_BAD_SIZE;
+  if (head_dim > QK_MAX_HEAD_DIM || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+    return ULLM_ERR_UNSUPPORTED;
+  if (rotary_dim > 0 && (cos_t == nullptr || sin_t == nullptr || positions == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const long long units = (long long)tokens * (num_q + 2 * num_kv);
+  const long long blocks = (units + QK_WARPS - 1) / QK_WARPS;
+  if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
+  if (dtype == ULLM_DTYPE_F32)
+    qk_norm_rope_store_kernel<float><<<(int)blocks, QK_WARPS * 32, 0, st>>>(
+        (float*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
+        positions, slot_mapping, (float*)k_cache, (float*)v_cache, num_slots, status);
+  else if (dtype == ULLM_DTYPE_BF16)
+    qk_norm_rope_store_kernel<__nv_bfloat16><<<(int)blocks, QK_WARPS * 32, 0, st>>>(
+        (__nv_bfloat16*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
+        positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status);
+  else
+    return ULLM_ERR_BAD_DTYPE;
+  return ullm_launch_status();
+}

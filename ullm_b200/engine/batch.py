@@ -1,0 +1,138 @@
+"""The flat batch of one step and the buffers it lives in.
+
+The reference rebuilds flat arrays per step in `InputBatch.update_batch`
+(ullm/core/input_batch.py:80-220): ids, positions, the slots new keys go to,
+cumulative lengths, the rows whose logits are wanted.  Here a step's integer
+inputs are packed into ONE pinned host buffer and reach the device in one
+copy; the block tables are already there (the cache manager keeps them).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens (a prompt portion, or one
+    decoded token) and the places among them whose logits are wanted."""
+
+    request_id: str
+    tokens: list[int]
+    want: list[int] = field(default_factory=list)
+
+
+@dataclass
+class GroupStep:
+    """A cache group's metadata for this step (device tensors)."""
+
+    block_table: torch.Tensor  # [slots, pages per request] int32, indexed by request slot
+    kv_len: torch.Tensor  # [B] int32: tokens each request holds after this step
+    slot_mapping: torch.Tensor  # [T] int32: flat slot of each new token (-1: none)
+    req_slots: torch.Tensor  # [B] int32: request slot of each batch row
+    page_size: int
+    window: int | None
+
+
+class Workspace:
+    """Named activation buffers that persist across steps (so a captured CUDA
+    graph finds them at the same address).  `get` returns the first `rows` rows;
+    a buffer grows when more rows are asked for than it has, which bumps
+    `generation` (anything that recorded addresses must be re-recorded)."""
+
+    def __init__(self, device, min_rows: int = 0):
+        self.device = device
+        self.min_rows = min_rows
+        self.buffers: dict[str, torch.Tensor] = {}
+        self.generation = 0
+
+    def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        buf = self.buffers.get(name)
+        if buf is None or buf.shape[0] < rows or buf.shape[1] != cols or buf.dtype != dtype:
+            cap = max(rows, self.min_rows if buf is None else buf.shape[0], 1)
+            buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            self.buffers[name] = buf
+            self.generation += 1
+        return buf[:rows]
+
+
+@dataclass
+class StepContext:
+    """Everything a part may read about the step.  Device tensors are views of
+    the staging buffer; the host lists mirror them for parts that loop on the
+    host (a test's toy mixer does)."""
+
+    num_tokens: int
+    num_requests: int
+    num_logits_rows: int
+    token_ids: torch.Tensor  # [T] int32
+    positions: torch.Tensor  # [T] int32
+    token_req: torch.Tensor  # [T] int32: batch row of each token
+    cu_q: torch.Tensor  # [B+1] int32
+    logits_rows: torch.Tensor  # [R] int32: flat token rows whose logits are wanted
+    req_slots: torch.Tensor  # [B] int32
+    groups: list[GroupStep]
+    workspace: Workspace
+    # host mirrors
+    cu_q_host: list[int]
+    req_slots_host: list[int]
+    start_positions_host: list[int]  # tokens each request held before this step
+    max_q_len: int = 1
+    max_kv_len: int = 1
+    decode_only: bool = False
+
+
+class StepStaging:
+    """Pinned host buffer + device buffer for a step's integers."""
+
+    def __init__(self, device, max_tokens: int, max_requests: int, num_groups: int):
+        self.device = torch.device(device)
+        self.max_tokens = max_tokens
+        self.max_requests = max_requests
+        self.num_groups = num_groups
+        n = self.size_for(max_tokens, max_requests)
+        pin = self.device.type == "cuda"
+        self.host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
+        self.dev = torch.zeros(n, dtype=torch.int32, device=self.device)
+
+    def size_for(self, T: int, B: int) -> int:
+        # ids, positions, token_req, logits_rows, slot_mapping per group: T each;
+        # cu_q: B+1; kv_len, req_slots: B each.  Segments start on 4-int boundaries.
+        def up(x):
+            return (x + 3) // 4 * 4
+
+        return up(T) * (4 + self.num_groups) + up(B + 1) + 2 * up(B)
+
+    def ensure(self, T: int, B: int) -> None:
+        if T > self.max_tokens or B > self.max_requests:
+            self.max_tokens = max(T, self.max_tokens)
+            self.max_requests = max(B, self.max_requests)
+            n = self.size_for(self.max_tokens, self.max_requests)
+            pin = self.device.type == "cuda"
+            self.host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
+            self.dev = torch.zeros(n, dtype=torch.int32, device=self.device)
+
+    def layout(self, T: int, B: int) -> dict[str, tuple[int, int]]:
+        """Offsets for capacities (T, B): segments are laid out for the CAPACITY
+        so that a fixed capacity gives fixed addresses."""
+
+        def up(x):
+            return (x + 3) // 4 * 4
+
+        off, out = 0, {}
+        for name in ("token_ids", "positions", "token_req", "logits_rows"):
+            out[name] = (off, T)
+            off += up(T)
+        for g in range(self.num_groups):
+            out[f"slot_mapping{g}"] = (off, T)
+            off += up(T)
+        out["cu_q"] = (off, B + 1)
+        off += up(B + 1)
+        out["kv_len"] = (off, B)
+        off += up(B)
+        out["req_slots"] = (off, B)
+        off += up(B)
+        out["_end"] = (off, 0)
+        return out

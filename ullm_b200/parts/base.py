@@ -1,0 +1,127 @@
+"""What every part is: an object built from sizes and constants alone, that
+declares its parameters by name, receives tensors for them, and runs on a flat
+batch of tokens.  No part knows which model it is in.
+
+Interfaces (what a new part must have):
+
+* every part: `param_decls() -> {name: ParamDecl}` and
+  `materialize(make) -> None`, where `make(name, decl)` returns the tensor for a
+  declared parameter; the part keeps what it needs and lists the tensors under
+  their checkpoint names in `self.tensors`.
+* Norm: `forward(x, residual=None, out=None) -> out`; with a residual the sum
+  x + residual is formed in 32-bit, written back to `residual`, and normed.
+* PositionEncoding: `tables() -> dict of device tensors` handed to the mixer's
+  kernel, plus `rotary_dim`.
+* Mixer: `cache_need() -> CacheNeed | None`, `state_need() -> StateNeed | None`,
+  `forward(x[T, hidden], ctx, cache) -> [T, hidden]`; `cache` is the
+  LayerCache of this execution (pages of its group + the group's step
+  metadata, and its state rows if it asked for any).
+* FeedForward: `forward(x[T, hidden], ctx) -> [T, hidden]`.
+* Block: `forward(x, residual, ctx, cache) -> (x, residual)`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamDecl:
+    """A parameter as the checkpoint stores it.  `role` decides precision and
+    random init: "matrix" (embedding and linear weights: engine dtype, N(0,
+    std)), "bias" (engine dtype, N(0, std)), "norm" (always held in 32-bit,
+    1 + N(0, norm_std))."""
+
+    shape: tuple[int, ...]
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """Keys and values this mixer keeps per token: `num_kv_heads` x `head_dim`
+    for K and for V.  `window`: None keeps every token, w keeps the last w."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-request state of fixed size: one row of `shape` per live request."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+Maker = Callable[[str, ParamDecl], torch.Tensor]
+
+
+class Part:
+    def __init__(self) -> None:
+        self.tensors: dict[str, torch.Tensor] = {}
+
+    def param_decls(self) -> dict[str, ParamDecl]:
+        return {}
+
+    def materialize(self, make: Maker) -> None:
+        for name, decl in self.param_decls().items():
+            self.tensors[name] = make(name, decl)
+
+    def subparts(self) -> dict[str, "Part"]:
+        """Nested parts by tensor-name prefix."""
+        return {}
+
+    # -- walking a tree of parts ------------------------------------------
+    def all_decls(self, prefix: str = "") -> dict[str, ParamDecl]:
+        out = {prefix + n: d for n, d in self.param_decls().items()}
+        for sub_prefix, sub in self.subparts().items():
+            out.update(sub.all_decls(prefix + sub_prefix))
+        return out
+
+    def materialize_all(self, make: Maker, prefix: str = "") -> None:
+        self.materialize(lambda n, d: make(prefix + n, d))
+        for sub_prefix, sub in self.subparts().items():
+            sub.materialize_all(make, prefix + sub_prefix)
+
+    def all_tensors(self, prefix: str = "") -> dict[str, torch.Tensor]:
+        out = {prefix + n: t for n, t in self.tensors.items()}
+        for sub_prefix, sub in self.subparts().items():
+            out.update(sub.all_tensors(prefix + sub_prefix))
+        return out
+
+
+class Norm(Part):
+    def forward(self, x, residual=None, out=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    rotary_dim: int = 0
+
+    def tables(self) -> dict[str, torch.Tensor]:
+        return {}
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, x, ctx, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, x, residual, ctx, cache):
+        raise NotImplementedError
