@@ -1,0 +1,290 @@
+"""Each CUDA kernel alone against a plain float32 torch reference of the same
+operation, at sizes other than the engine's tiny models: row lengths and
+vocabularies that are no power of two, head sizes in steps of 16, odd head
+counts and groups, windows, ragged batches."""
+
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = [pytest.mark.gpu, pytest.mark.needs_cuda]
+
+DTYPES = [torch.float32, torch.bfloat16]
+ATOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+def K():
+    from ullm_b200.csrc import kernels
+
+    return kernels()
+
+
+def close(got, ref, dtype, scale=None):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    s = scale if scale is not None else max(ref.abs().max().item(), 1e-6)
+    err = (got - ref).abs().max().item() / s
+    assert err <= ATOL[dtype], f"max err {err:.3e} of scale (limit {ATOL[dtype]})"
+
+
+def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [24, 100, 1000, 4096])
+def test_embedding_and_gather(dtype, H):
+    V, T = 777, 53
+    table = rnd(V, H, seed=1, dtype=dtype)
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2)).int().cuda()
+    out = torch.empty(T, H, dtype=dtype, device="cuda")
+    K().embedding(ids, table, out)
+    assert torch.equal(out, table[ids.long()])
+    rows = torch.tensor([5, 0, 52, 7], dtype=torch.int32, device="cuda")
+    g = torch.empty(4, H, dtype=dtype, device="cuda")
+    K().gather_rows(out, rows, g)
+    assert torch.equal(g, out[rows.long()])
+
+
+def test_embedding_refuses_bad_id():
+    from ullm_b200.csrc.ops import KernelError
+
+    table = rnd(10, 16)
+    ids = torch.tensor([1, 10], dtype=torch.int32, device="cuda")
+    out = torch.empty(2, 16, device="cuda")
+    K().embedding(ids, table, out)
+    with pytest.raises(KernelError, match="token id"):
+        K().raise_on_status()
+    K().raise_on_status()  # cleared
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [16, 100, 1000, 4096, 13000])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_add_rmsnorm(dtype, H, with_res):
+    T, eps = 37, 3e-6
+    x = rnd(T, H, seed=3, dtype=dtype)
+    res = rnd(T, H, seed=4, dtype=dtype) if with_res else None
+    w = (1 + 0.3 * torch.randn(H, generator=torch.Generator().manual_seed(5))).cuda()
+    s = x.float() + (res.float() if with_res else 0)
+    ref = pm.rms_norm(s, w, eps)
+    res_in = res.clone() if with_res else None
+    out = torch.empty_like(x)
+    K().add_rmsnorm(x, res_in, w, eps, out)
+    close(out, ref, dtype)
+    if with_res:
+        assert torch.equal(res_in, s.to(dtype)), "the stored residual is the rounded 32-bit sum"
+    # in place
+    x2 = x.clone()
+    K().add_rmsnorm(x2, res.clone() if with_res else None, w, eps, x2)
+    assert torch.equal(x2, out)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("I", [8, 100, 176, 3072])
+def test_act_mul(dtype, I):
+    T = 29
+    gu = rnd(T, 2 * I, seed=6, dtype=dtype, scale=2.0)
+    out = torch.empty(T, I, dtype=dtype, device="cuda")
+    K().act_mul(gu, out, 0)
+    close(out, pm.silu_mul(gu[:, :I].float(), gu[:, I:].float()), dtype)
+    K().act_mul(gu, out, 1)
+    g = gu[:, :I].float()
+    close(out, torch.nn.functional.gelu(g, approximate="tanh") * gu[:, I:].float(), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,rot", [(4, 2, 16, 16), (6, 1, 48, 48), (5, 5, 80, 40), (8, 2, 128, 128), (3, 1, 256, 256), (2, 2, 96, 0)])
+def test_qk_norm_rope_store(dtype, Hq, Hkv, D, rot):
+    T, max_pos, page, pages, eps = 23, 300, 8, 7, 1e-5
+    W = (Hq + 2 * Hkv) * D
+    qkv = rnd(T, W, seed=7, dtype=dtype)
+    qw = (1 + 0.2 * torch.randn(D, generator=torch.Generator().manual_seed(8))).cuda()
+    kw = (1 + 0.2 * torch.randn(D, generator=torch.Generator().manual_seed(9))).cuda()
+    pos = torch.randint(0, max_pos, (T,), generator=torch.Generator().manual_seed(10)).int().cuda()
+    slots = torch.randperm(page * pages, generator=torch.Generator().manual_seed(11))[:T].int()
+    slots[3] = -1
+    slots = slots.cuda()
+    cos = sin = None
+    if rot:
+        c, s = pm.rope_table(rot, 50000.0, max_pos)
+        cos, sin = c.cuda(), s.cuda()
+    kp = torch.full((pages, page, Hkv, D), 7.0, dtype=dtype, device="cuda")
+    vp = torch.full((pages, page, Hkv, D), 7.0, dtype=dtype, device="cuda")
+    x = qkv.float().view(T, Hq + 2 * Hkv, D)
+    q = pm.rms_norm(x[:, :Hq], qw, eps)
+    k = pm.rms_norm(x[:, Hq:Hq + Hkv], kw, eps)
+    v = x[:, Hq + Hkv:]
+    if rot:
+        def rope(t):
+            r = pm.apply_rope(t[..., :rot], cos[pos.long()], sin[pos.long()])
+            return torch.cat((r, t[..., rot:]), -1)
+        q, k = rope(q), rope(k)
+    work = qkv.clone()
+    K().qk_norm_rope_store(work, Hq, Hkv, D, qw, kw, eps, cos, sin, rot, pos, slots, kp, vp)
+    close(work[:, : Hq * D].view(T, Hq, D), q, dtype)
+    assert torch.equal(work[:, Hq * D:], qkv[:, Hq * D:]), "k and v columns of the projection stay as they were"
+    kf, vf = kp.view(-1, Hkv, D), vp.view(-1, Hkv, D)
+    keep = slots >= 0
+    close(kf[slots[keep].long()], k[keep], dtype)
+    assert torch.equal(vf[slots[keep].long()], v[keep].to(dtype))
+    untouched = torch.ones(page * pages, dtype=torch.bool)
+    untouched[slots[keep].long().cpu()] = False
+    assert (kf[untouched.cuda()] == 7.0).all() and (vf[untouched.cuda()] == 7.0).all()
+
+
+def attention_reference(q, kf, vf, block_table, req_slots, q_lens, kv_lens, Hq, Hkv, D, page, window, scale):
+    T = q.shape[0]
+    out = torch.zeros(T, Hq, D)
+    t = 0
+    for r, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        for j in range(ql):
+            pos = kl - ql + j
+            lo = max(0, pos - window + 1) if window else 0
+            keys = torch.arange(lo, pos + 1)
+            slots = block_table[req_slots[r]][keys // page] * page + keys % page
+            for h in range(Hq):
+                kh = h // (Hq // Hkv)
+                s = (kf[slots, kh] @ q[t, h]) * scale
+                out[t, h] = torch.softmax(s, 0) @ vf[slots, kh]
+            t += 1
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [
+    (4, 2, 16, 4, 0), (9, 3, 32, 16, 0), (6, 1, 48, 16, 24), (5, 5, 80, 8, 0), (8, 2, 128, 16, 0),
+    (8, 2, 128, 16, 33), (2, 1, 256, 32, 0), (3, 3, 64, 16, 7),
+])
+def test_paged_attention_ragged_batch(dtype, Hq, Hkv, D, page, window):
+    q_lens = [1, 37, 1, 2, 64]
+    kv_lens = [150, 37, 1, 100, 130]
+    B, T = len(q_lens), sum(q_lens)
+    max_pages = 16 if page >= 16 else 64
+    pages = sum(-(-k // page) for k in kv_lens) + 3
+    g = torch.Generator().manual_seed(12)
+    perm = torch.randperm(pages, generator=g)
+    slots_of_req = [4, 0, 6, 2, 1]
+    bt = torch.full((8, max_pages), -1, dtype=torch.int32)
+    used = 0
+    for r, kl in enumerate(kv_lens):
+        n = -(-kl // page)
+        bt[slots_of_req[r], :n] = perm[used:used + n].int()
+        used += n
+    kp = rnd(pages, page, Hkv, D, seed=13, dtype=dtype)
+    vp = rnd(pages, page, Hkv, D, seed=14, dtype=dtype)
+    W = (Hq + 2 * Hkv) * D
+    qkv = rnd(T, W, seed=15, dtype=dtype)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32).cuda()
+    token_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)]).cuda()
+    out = torch.empty(T, Hq * D, dtype=dtype, device="cuda")
+    scale = D ** -0.5
+    K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
+                        torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale)
+    K().raise_on_status()
+    ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(T, Hq, D), kp.float().cpu().view(-1, Hkv, D),
+                              vp.float().cpu().view(-1, Hkv, D), bt.long(), slots_of_req, q_lens, kv_lens, Hq, Hkv, D,
+                              page, window, scale)
+    close(out.view(T, Hq, D), ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_one_far_key(dtype):
+    """One key among 700 matches the query (score far above the rest): the
+    output must be that key's value, wherever it lies: first position, a
+    page's last slot, a page's first slot, the newest position."""
+    Hq, Hkv, D, page = 4, 2, 64, 16
+    n = 700
+    pages = -(-n // page)
+    for hot in (0, 15, 16, 351, 687, 699):
+        k = torch.randn(n, Hkv, D, generator=torch.Generator().manual_seed(16)) * 0.1
+        v = torch.randn(n, Hkv, D, generator=torch.Generator().manual_seed(17))
+        qv = torch.randn(Hq, D, generator=torch.Generator().manual_seed(18))
+        qv = qv / qv.norm(dim=-1, keepdim=True) * 12.0
+        for h in range(Hq):
+            k[hot, h // 2] = 0
+        k[hot, 0] = (qv[0] + qv[1]) / 2
+        k[hot, 1] = (qv[2] + qv[3]) / 2
+        perm = torch.randperm(pages, generator=torch.Generator().manual_seed(19))
+        kp = torch.zeros(pages, page, Hkv, D)
+        vp = torch.zeros(pages, page, Hkv, D)
+        for p in range(n):
+            kp[perm[p // page], p % page] = k[p]
+            vp[perm[p // page], p % page] = v[p]
+        qkv = torch.zeros(1, (Hq + 2 * Hkv) * D)
+        qkv[0, : Hq * D] = qv.reshape(-1)
+        out = torch.empty(1, Hq * D, dtype=dtype, device="cuda")
+        bt = perm.int()[None].cuda()
+        z = torch.zeros(1, dtype=torch.int32, device="cuda")
+        K().paged_attention(qkv.to(dtype).cuda(), out, kp.to(dtype).cuda(), vp.to(dtype).cuda(), bt, z,
+                            torch.tensor([0, 1], dtype=torch.int32).cuda(), torch.tensor([n], dtype=torch.int32).cuda(),
+                            z, Hq, Hkv, D, page, 0, 1.0)
+        ref = attention_reference(qkv[:, : Hq * D].to(dtype).float().view(1, Hq, D), kp.to(dtype).float().view(-1, Hkv, D),
+                                  vp.to(dtype).float().view(-1, Hkv, D), perm[None], [0], [1], [n], Hq, Hkv, D, page, 0, 1.0)
+        close(out.view(1, Hq, D), ref, dtype)
+        got = out.float().cpu().view(Hq, D)
+        for h in range(Hq):
+            assert (got[h] - v[hot, h // 2]).abs().max() < 0.15, f"hot key at {hot} not found by head {h}"
+
+
+@pytest.mark.parametrize("V", [17, 331, 1000, 151936])
+def test_argmax_lowest_index_on_ties(V):
+    R = 5
+    lg = rnd(R, V, seed=20)
+    lg[1, 3] = lg[1, V - 1] = 50.0
+    lg[2, :] = 0.0
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    K().argmax(lg, out)
+    ref = [int(torch.argmax(r)) for r in lg.cpu()]
+    ref[1], ref[2] = 3, 0
+    assert out.tolist() == ref
+
+
+@pytest.mark.parametrize("V", [331, 5000, 151936])
+def test_sampling_filters_and_draws(V):
+    cases = [(0.7, 20, 0.95, 0.0), (1.0, -1, 0.5, 0.0), (1.3, 5, 1.0, 0.1), (0.5, -1, 1.0, 0.3), (1.0, -1, 1.0, 0.0),
+             (0.0, -1, 1.0, 0.0), (2.0, 1, 1.0, 0.0), (0.9, 50, 0.3, 0.05)]
+    R = len(cases)
+    lg = rnd(R, V, seed=21, scale=2.5)
+    us = [0.0, 0.13, 0.5, 0.77, 0.999999, 0.3, 0.6, 0.42]
+    dev = lambda xs, dt: torch.tensor(xs, dtype=dt, device="cuda")
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    probs = torch.empty(R, V, device="cuda")
+    K().sample(lg, dev([c[0] for c in cases], torch.float32), dev([c[1] for c in cases], torch.int32),
+               dev([c[2] for c in cases], torch.float32), dev([c[3] for c in cases], torch.float32),
+               dev(us, torch.float32), out, probs)
+    for r, (t, k, p, mp) in enumerate(cases):
+        row = lg[r].cpu()
+        if t <= 0:
+            assert int(out[r]) == pm.greedy(row)
+            continue
+        ref = pm.filtered_distribution(row, t, k, p, mp)
+        got = probs[r].cpu()
+        # the kept sets agree except for entries within rounding of a threshold
+        differ = (got > 0) != (ref > 0)
+        assert differ.sum().item() <= 2, f"case {r}: kept sets differ in {differ.sum().item()} entries"
+        if differ.sum().item() == 0:
+            assert (got - ref).abs().max().item() < 1e-5
+        ref_draw = pm.inverse_cdf_draw(got, us[r])
+        assert got[int(out[r])] > 0, "a filtered-out token was drawn"
+        c = torch.cumsum(got.double(), 0)
+        i = int(out[r])
+        lo = float(c[i - 1]) if i > 0 else 0.0
+        assert lo - 1e-5 <= us[r] * float(c[-1]) <= float(c[i]) + 1e-5, f"case {r}: drew {i}, inverse CDF gives {ref_draw}"
+
+
+def test_sampling_is_independent_of_batch():
+    V = 4099
+    lg = rnd(6, V, seed=22, scale=2.0)
+    f = lambda xs: torch.tensor(xs, dtype=torch.float32, device="cuda")
+    t, p, mp, u = f([0.8] * 6), f([0.9] * 6), f([0.02] * 6), f([0.1, 0.3, 0.5, 0.7, 0.9, 0.2])
+    k = torch.tensor([40] * 6, dtype=torch.int32, device="cuda")
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    K().sample(lg, t, k, p, mp, u, out)
+    one = torch.empty(1, dtype=torch.int32, device="cuda")
+    for r in range(6):
+        K().sample(lg[r:r + 1], t[r:r + 1], k[r:r + 1], p[r:r + 1], mp[r:r + 1], u[r:r + 1], one)
+        assert int(one) == int(out[r])

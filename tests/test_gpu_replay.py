@@ -1,0 +1,217 @@
+"""The engine against the plain implementation under every way of cutting the
+work: whole, last 32 tokens one by one, portions of changing size, mixed
+batches with so few pages that they are used again.  float32 and bfloat16."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import SHARPEN, assert_close, first_bad_row, plain_logits, random_ids, weights_for, write_model_dir
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CASES = [("A", "float32"), ("B", "float32"), ("C", "float32"), ("A", "bfloat16"), ("B", "bfloat16"), ("C", "bfloat16")]
+LENGTHS = {"A": 100, "B": 200, "C": 180}
+
+
+def make_runner(tmp_path, tag, dtype, num_pages, sharpen=1.0, max_requests=4, **kw):
+    from ullm_b200.engine import ModelRunner
+
+    cfg, w, page = weights_for(tag, dtype, sharpen)
+    d = write_model_dir(str(tmp_path / f"model_{tag}_{dtype}"), cfg, w)
+    from conftest import device
+
+    r = ModelRunner(d, dtype=dtype, device=device(), page_size=page, num_pages=num_pages, max_requests=max_requests,
+                    max_context=cfg["max_position_embeddings"], max_step_tokens=64, poison_cache=True, **kw)
+    return r, cfg, w, page
+
+
+def run_cut(runner, rid, ids, cuts, want_all=True):
+    """Feeds ids in portions of the given sizes; returns logits at every position."""
+    from ullm_b200.engine import StepEntry
+
+    runner.add_request(rid)
+    outs, i = [], 0
+    for n in cuts:
+        lg = runner.step([StepEntry(rid, ids[i:i + n], list(range(n)))])
+        outs.append(lg.float().cpu().clone())
+        i += n
+    runner.check_device_status()
+    runner.end_request(rid)
+    assert i == len(ids)
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("tag,dtype", CASES)
+def test_whole_prompt(tmp_path, tag, dtype):
+    n = LENGTHS[tag]
+    runner, cfg, w, page = make_runner(tmp_path, tag, dtype, num_pages=-(-n // ALL_PAGE(tag)) + 1)
+    ids = random_ids(cfg["vocab_size"], n, 11)
+    ref = plain_logits(ids, w, cfg)
+    got = run_cut(runner, "a", ids, [n])
+    assert_close(got, ref, dtype, f"{tag} whole")
+    runner.cache.check_invariants()
+
+
+def ALL_PAGE(tag):
+    from tiny_configs import ALL
+
+    return ALL[tag][2]
+
+
+@pytest.mark.parametrize("tag,dtype", CASES)
+def test_last_32_one_by_one(tmp_path, tag, dtype):
+    n = LENGTHS[tag]
+    runner, cfg, w, page = make_runner(tmp_path, tag, dtype, num_pages=-(-n // ALL_PAGE(tag)) + 1)
+    ids = random_ids(cfg["vocab_size"], n, 12)
+    ref = plain_logits(ids, w, cfg)
+    got = run_cut(runner, "a", ids, [n - 32] + [1] * 32)
+    bad = first_bad_row(got, ref, dtype)
+    assert bad is None, f"first wrong position {bad} (page size {page}, prefill {n - 32})"
+    assert_close(got, ref, dtype, f"{tag} decode")
+
+
+@pytest.mark.parametrize("tag,dtype", CASES)
+def test_portions_of_changing_size(tmp_path, tag, dtype):
+    n = LENGTHS[tag]
+    runner, cfg, w, page = make_runner(tmp_path, tag, dtype, num_pages=-(-n // ALL_PAGE(tag)) + 1)
+    ids = random_ids(cfg["vocab_size"], n, 13)
+    ref = plain_logits(ids, w, cfg)
+    pattern = [7, 2, 5, 3, 16, 2, 1, 9, 4, 17, 2, 33]
+    cuts, left, i = [], n, 0
+    while left > 0:
+        c = min(pattern[i % len(pattern)], left)
+        cuts.append(c)
+        left -= c
+        i += 1
+    got = run_cut(runner, "a", ids, cuts)
+    bad = first_bad_row(got, ref, dtype)
+    assert bad is None, f"first wrong position {bad}; cuts {cuts}"
+    assert_close(got, ref, dtype, f"{tag} portions")
+
+
+@pytest.mark.parametrize("tag,dtype", CASES)
+def test_mixed_batches_with_page_reuse(tmp_path, tag, dtype):
+    """Eight requests, at most four live, portions of some beside decoded tokens
+    of others; the pool is so small that finished requests' pages are used again."""
+    from ullm_b200.engine import StepEntry
+
+    page = ALL_PAGE(tag)
+    lens = [37, 64, 21, 50, 33, 48, 10, 59]
+    # room for the four longest requests at once, no more
+    num_pages = sum(-(-L // page) for L in sorted(lens)[-4:])
+    runner, cfg, w, page = make_runner(tmp_path, tag, dtype, num_pages=num_pages)
+    prompts = [random_ids(cfg["vocab_size"], L, 20 + i) for i, L in enumerate(lens)]
+    refs = [plain_logits(p, w, cfg) for p in prompts]
+    # every request: a prefill in portions, then its last 8 tokens one by one
+    plans = []
+    for i, L in enumerate(lens):
+        portions, left = [], L - 8
+        sizes = [5 + 3 * i, 2, 11, 7, 30]
+        k = 0
+        while left > 0:
+            c = min(sizes[k % len(sizes)], left)
+            portions.append(c)
+            left -= c
+            k += 1
+        plans.append(portions + [1] * 8)
+    got = [[] for _ in lens]
+    done_at = [0] * len(lens)
+    waiting = list(range(len(lens)))
+    live: list[int] = []
+    used_pages = set()
+    steps = 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            i = waiting.pop(0)
+            runner.add_request(f"r{i}")
+            live.append(i)
+        entries = []
+        for i in live:
+            n = plans[i].pop(0)
+            entries.append(StepEntry(f"r{i}", prompts[i][done_at[i]:done_at[i] + n], list(range(n))))
+        lg = runner.step(entries).float().cpu()
+        row = 0
+        for e, i in zip(entries, list(live)):
+            n = len(e.tokens)
+            got[i].append(lg[row:row + n].clone())
+            row += n
+            done_at[i] += n
+            for g in range(len(runner.cache.groups)):
+                used_pages.update((g, p) for p in runner.cache.requests[f"r{i}"].pages[g] if p >= 0)
+        for i in list(live):
+            if not plans[i]:
+                runner.end_request(f"r{i}")
+                live.remove(i)
+        runner.cache.check_invariants()
+        steps += 1
+    runner.check_device_status()
+    assert sum(lens) > num_pages * page, "the pool must be too small to hold everything at once"
+    for i in range(len(lens)):
+        g = torch.cat(got[i])
+        bad = first_bad_row(g, refs[i], dtype)
+        assert bad is None, f"request {i}: first wrong position {bad}"
+        assert_close(g, refs[i], dtype, f"{tag} mixed r{i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_key_and_window_edge_with_sharp_attention(tmp_path, dtype):
+    """q_norm weights scaled up make the softmax peaky, so that a single wrong
+    or missing key (a far one, one at the window's edge, one on a page edge)
+    moves the logits far beyond the tolerance."""
+    for tag, n in (("B", 250), ("C", 300)):
+        runner, cfg, w, page = make_runner(tmp_path, tag, dtype, num_pages=-(-n // ALL_PAGE(tag)) + 1, sharpen=SHARPEN[dtype])
+        ids = random_ids(cfg["vocab_size"], n, 31)
+        ref = plain_logits(ids, w, cfg)
+        got = run_cut(runner, "a", ids, [n - 40, 3, 5] + [1] * 32)
+        bad = first_bad_row(got, ref, dtype)
+        assert bad is None, f"{tag}: first wrong position {bad}"
+        assert_close(got, ref, dtype, f"{tag} sharp")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tmp_path, dtype):
+    runner, cfg, w, page = make_runner(tmp_path, "B", dtype, num_pages=4)
+    for n in (1, 2, 3):
+        ids = random_ids(cfg["vocab_size"], n, 40 + n)
+        ref = plain_logits(ids, w, cfg)
+        got = run_cut(runner, f"s{n}", ids, [1] * n)
+        assert_close(got, ref, dtype, f"first {n}")
+
+
+@pytest.mark.needs_cuda
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """bin/trace_run as a user runs it: steps on stdin, <step>.f32 files out."""
+    cfg, w, page = weights_for("B", dtype)
+    d = write_model_dir(str(tmp_path / "m"), cfg, w)
+    out = tmp_path / "out"
+    a = random_ids(cfg["vocab_size"], 70, 51)
+    b = random_ids(cfg["vocab_size"], 40, 52)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[30:32], "want": []}, {"id": "b", "tokens": b[:40], "want": [39]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[32:69], "want": [36]}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[69:70], "want": [0]}], "end": ["a"]},
+    ]
+    p = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out),
+         "--max-tokens", "192"],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    ra, rb = plain_logits(a, w, cfg), plain_logits(b, w, cfg)
+    V = cfg["vocab_size"]
+
+    def read(i):
+        return torch.frombuffer(bytearray((out / f"{i}.f32").read_bytes()), dtype=torch.float32).view(-1, V)
+
+    assert_close(read(0), ra[[0, 29]], dtype, "step 0")
+    assert_close(read(1), rb[[39]], dtype, "step 1")
+    assert_close(read(2), ra[[68]], dtype, "step 2")
+    assert_close(read(3), ra[[69]], dtype, "step 3")
