@@ -1,0 +1,169 @@
+"""Generation through the Python entry point: greedy tokens against the plain
+implementation, chunked prompts under a token budget, prefix sharing, CUDA-graph
+decode against eager decode, preemption under a tiny pool, sampling that does
+not depend on the batch."""
+
+import asyncio
+
+import pytest
+import torch
+
+import plain_model as pm
+from conftest import device
+from helpers import random_ids, weights_for, write_model_dir
+
+pytestmark = pytest.mark.gpu
+
+
+def make_llm(tmp_path, tag, dtype="float32", **kw):
+    from ullm_b200 import LLM, EngineConfig
+
+    cfg, w, page = weights_for(tag, dtype)
+    d = write_model_dir(str(tmp_path / f"m{tag}{dtype}{len(kw)}"), cfg, w)
+    args = dict(model=d, max_bs=4, context_len=cfg["max_position_embeddings"], page_size=page, num_pages=64,
+                max_num_batched_tokens=64, dtype=dtype)
+    args.update(kw)
+    ec = EngineConfig(**args)
+    if device() == "cpu":
+        type(ec).device = property(lambda self: "cpu")
+    return LLM(ec), cfg, {k: v.float() for k, v in w.items()}
+
+
+def test_tiny_a_workload_greedy(tmp_path):
+    """3 requests, prompts of 5, 11 and 17 ids, 8 greedy tokens each."""
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "A")
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (5, 11, 17)]
+    outs = llm.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == pm.greedy_generate(p, w, cfg, 8)
+        assert o.finish_reason.name == "LENGTH" and o.num_prompt_tokens == len(p)
+    llm.engine.runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_tiny_b_workload_chunked_with_shared_prefix(tmp_path, eager):
+    """5 requests (prompts 1, 7, 16, 33, 64), 12 new tokens, token budget 8,
+    plus two requests that share a 32-token prefix."""
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "B", max_num_batched_tokens=8, max_bs=3, enforce_eager=eager)
+    prompts = [random_ids(331, n, 70 + n) for n in (1, 7, 16, 33, 64)]
+    shared = random_ids(331, 32, 99)
+    prompts += [shared + [5, 6, 7]]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True)
+    outs = llm.generate_batch(prompts, sp)
+    prompts += [shared + [9]]
+    outs += llm.generate_batch(prompts[-1:], sp)
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == pm.greedy_generate(p, w, cfg, 12), f"prompt of {len(p)}"
+    st = llm.engine.stats()
+    assert st["prefix_hit_tokens"] >= 32, "the second request with the shared prefix reuses its pages"
+    if not eager and device() != "cpu":
+        assert llm.engine.decode_graphs.replays > 0
+    llm.engine.runner.cache.check_invariants()
+
+
+def test_preemption_under_a_tiny_pool_keeps_the_tokens(tmp_path):
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "B", num_pages=7, max_bs=3, max_num_batched_tokens=32)
+    prompts = [random_ids(331, n, 80 + n) for n in (30, 20, 25)]
+    outs = llm.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=30, ignore_eos=True))
+    assert llm.engine.stats()["preemptions"] >= 1, "7 pages of 16 cannot hold three requests of ~55 tokens"
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == pm.greedy_generate(p, w, cfg, 30)
+    llm.engine.runner.cache.check_invariants()
+
+
+def test_finish_rules(tmp_path):
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "A", context_len=40)
+    p = random_ids(256, 10, 5)
+    ref = pm.greedy_generate(p, w, cfg, 30)
+    # eos stops (and is emitted), unless ignored
+    o = llm.generate_batch([p], SamplingParams(temperature=0.0, max_new_tokens=30, eos_token_id=ref[3]))[0]
+    stop_at = ref.index(ref[3]) + 1
+    assert o.token_ids == ref[:stop_at] and o.finish_reason.name == "STOP"
+    # max_tokens bounds prompt + generated
+    o = llm.generate_batch([p], SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True))[0]
+    assert len(o.token_ids) == 4 and o.finish_reason.name == "LENGTH"
+    # the context length bounds everything; a longer prompt keeps its last ids
+    o = llm.generate_batch([p], SamplingParams(temperature=0.0, ignore_eos=True))[0]
+    assert len(o.token_ids) == 30
+    long = random_ids(256, 55, 6)
+    o = llm.generate_batch([long], SamplingParams(temperature=0.0, max_new_tokens=2, ignore_eos=True))[0]
+    assert o.prompt_token_ids == long[-40:] and len(o.token_ids) == 1
+
+
+def test_async_generate_streams_tokens(tmp_path):
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "A")
+    p1, p2 = random_ids(256, 9, 1), random_ids(256, 4, 2)
+
+    async def consume(p):
+        toks = []
+        async for out in llm.generate(p, SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)):
+            toks.append(out.token_id)
+            last = out
+        assert last.is_finished and last.num_generated_tokens == 6 and last.num_prompt_tokens == len(p)
+        return toks
+
+    async def main():
+        r = await asyncio.gather(consume(p1), consume(p2))
+        await llm.shutdown()
+        return r
+
+    t1, t2 = asyncio.run(main())
+    assert t1 == pm.greedy_generate(p1, w, cfg, 6) and t2 == pm.greedy_generate(p2, w, cfg, 6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sampled_tokens_do_not_depend_on_the_batch(tmp_path, dtype):
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "B", dtype=dtype)
+    prompts = [random_ids(331, n, 90 + n) for n in (7, 16, 33)]
+    sp = [SamplingParams(temperature=0.7, top_k=20, top_p=0.95, max_new_tokens=12, ignore_eos=True, seed=4 + i)
+          for i in range(3)]
+    together = llm.generate_batch(prompts, sp)
+    for p, s, o in zip(prompts, sp, together):
+        alone = llm.generate_batch([p], s)[0]
+        if dtype == "float32":
+            assert alone.token_ids == o.token_ids
+        assert len(o.token_ids) == 12
+    # temperature sampling follows the filtered distribution of the plain implementation
+    if dtype == "float32":
+        p = prompts[1]
+        o = together[1]
+        ids = list(p)
+        from ullm_b200.sampling import uniform_for
+
+        for step, tok in enumerate(o.token_ids):
+            lg = pm.forward_logits(ids, w, cfg)[-1]
+            probs = pm.filtered_distribution(lg, 0.7, 20, 0.95, 0.0)
+            assert probs[tok] > 0, f"step {step}: token {tok} is outside the top-k/top-p set"
+            assert tok == pm.inverse_cdf_draw(probs, uniform_for(5, step))
+            ids.append(tok)
+
+
+def test_long_decoding_bf16_tracks_the_plain_logits(tmp_path):
+    """120 greedy tokens in bfloat16; every chosen token's plain logit is within
+    the bfloat16 tolerance of the plain maximum (teacher-forced on the engine's
+    own tokens, so one near-tie cannot derail the comparison)."""
+    from helpers import TOL
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "C", dtype="bfloat16")
+    p = random_ids(509, 20, 7)
+    o = llm.generate_batch([p], SamplingParams(temperature=0.0, max_new_tokens=120, ignore_eos=True))[0]
+    assert len(o.token_ids) == 120
+    lg = pm.forward_logits(p + o.token_ids, w, cfg)
+    scale = lg.abs().max().item()
+    for i, tok in enumerate(o.token_ids):
+        row = lg[len(p) - 1 + i]
+        assert row.max().item() - row[tok].item() <= 2 * TOL["bfloat16"] * scale, f"token {i}"

@@ -245,6 +245,23 @@ class CacheManager:
                 self._mark(g, rc.slot, lo, first_needed, rc.pages[g])
                 rc.first_live_page[g] = first_needed
 
+    def publish(self, rc: RequestCache, tokens) -> None:
+        """Makes the request's completed full pages findable by other requests
+        while it is still running (`tokens`: the ids whose keys/values are
+        written).  The request keeps holding them.  The reference publishes only
+        at finish (ullm/core/kv_cache.py:358-398)."""
+        if self.tree is None:
+            return
+        ps = self.page_size
+        full = min(rc.num_tokens, len(tokens)) // ps
+        while len(rc.prefix_nodes) < full:
+            i = len(rc.prefix_nodes)
+            parent = rc.prefix_nodes[-1] if rc.prefix_nodes else None
+            node = self.tree.adopt(parent, tuple(tokens[i * ps:(i + 1) * ps]), rc.pages[0][i])
+            if node is None:
+                break  # someone else published this content first; ours stays private until release
+            rc.prefix_nodes.append(node)
+
     def release(self, rc: RequestCache, tokens=None) -> None:
         """The request ends (finished, aborted or preempted): its slot and pages
         are given back.  With `tokens` (the ids whose keys/values are written)

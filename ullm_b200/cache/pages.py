@@ -160,6 +160,20 @@ class PrefixTree:
             node = child
         return dup
 
+    def adopt(self, parent: "_Node | None", key: tuple, page: int) -> "_Node | None":
+        """Adds one page below `parent` (None: the root) on behalf of a live
+        request, which holds it from the start (ref 1).  Returns None when that
+        content is already in the tree (the caller keeps its page private)."""
+        node = parent if parent is not None else self.root
+        if key in node.children:
+            return None
+        child = _Node(key, page, node, next(self._uid))
+        child.ref = 1
+        child.stamp = next(self._clock)
+        node.children[key] = child
+        self.num_pages += 1
+        return child
+
     def evict(self, n: int) -> list[int]:
         """Removes up to n unreferenced leaves, least recently used first, and
         returns their pages."""

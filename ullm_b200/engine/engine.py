@@ -1,0 +1,166 @@
+"""Engine: scheduler + step function + sampler, one `step()` at a time
+(ullm/core/engine.py:24-200 is the reference's; its executor, worker processes
+and batch queue collapse into direct calls here)."""
+
+from __future__ import annotations
+
+import logging
+import time
+
+import torch
+
+from ..config.engine_config import EngineConfig
+from ..sampling.params import EngineStepResult, FinishReason, SamplingParams
+from ..sampling.sampler import Sampler
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Scheduler, Sequence, SequenceStatus
+
+logger = logging.getLogger("ullm_b200")
+
+
+class Engine:
+    def __init__(self, config: EngineConfig, runner: ModelRunner | None = None):
+        self.config = config
+        logging.basicConfig(level=getattr(logging, config.log_level.upper(), logging.INFO),
+                            format="%(levelname)s %(asctime)s %(name)s: %(message)s")
+        t0 = time.time()
+        self.runner = runner or ModelRunner(
+            config.model,
+            dtype=config.dtype,
+            device=config.device,
+            page_size=config.page_size,
+            num_pages=config.num_pages,
+            gpu_memory_utilization=config.gpu_memory_utilization,
+            max_requests=config.max_bs,
+            max_context=config.context_len,
+            max_step_tokens=config.max_num_batched_tokens,
+            load_format=config.load_format,
+            seed=config.seed,
+            random_std=config.random_init_std,
+            random_norm_std=config.random_init_norm_std,
+            enable_prefix_cache=config.enable_prefix_caching,
+        )
+        cache = self.runner.cache
+        logger.info("model ready in %.1f s; KV cache: %d pages of %d tokens (%d tokens)", time.time() - t0,
+                    cache.num_pages, cache.page_size, cache.num_pages * cache.page_size)
+        self.context_len = min(config.context_len, self.runner.max_context)
+        self.scheduler = Scheduler(cache, config.max_bs, config.max_num_batched_tokens, self.context_len)
+        self.sampler = Sampler(self.runner.device, max(config.max_bs, 1), self.runner.spec.vocab_size)
+        self.decode_graphs = None
+        if not config.enforce_eager and self.runner.device.type == "cuda":
+            from .graph import DecodeGraphs
+
+            self.decode_graphs = DecodeGraphs(self.runner, self.sampler, config.max_bs)
+        self._seed_counter = 0
+        self.profile_steps = config.profile
+        self.step_times: list[tuple[int, int, float]] = []
+
+    # -- requests -------------------------------------------------------------------
+    def add_sequence(self, sequence_id: str, prompt_token_ids: list[int], sampling_params: SamplingParams) -> None:
+        """ullm/core/engine.py:72-90: a prompt longer than the context keeps its
+        last `context_len` ids."""
+        ids = [int(t) for t in prompt_token_ids]
+        if not ids:
+            raise ValueError("empty prompt")
+        V = self.runner.spec.vocab_size
+        bad = [t for t in ids if not 0 <= t < V]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside the vocabulary of {V}")
+        if len(ids) > self.context_len:
+            ids = ids[-self.context_len:]
+        seed = sampling_params.seed
+        if seed is None:
+            seed = (self.config.seed * 1000003 + self._seed_counter) & 0x7FFFFFFF
+            self._seed_counter += 1
+        seq = Sequence(sequence_id, ids, len(ids), sampling_params, seed=seed)
+        self.scheduler.add_sequence(seq)
+        logger.debug("Added sequence %s.", sequence_id)
+
+    def abort_sequence(self, sequence_id: str) -> None:
+        seq = self.scheduler.get_sequence(sequence_id)
+        if seq:
+            self.scheduler.finish_sequence(seq, FinishReason.ABORT)
+        logger.debug("Aborted sequence %s.", sequence_id)
+
+    def has_unfinished_sequences(self) -> bool:
+        return self.scheduler.has_unfinished_sequences()
+
+    # -- one step ---------------------------------------------------------------------
+    def step(self) -> list[EngineStepResult]:
+        """Schedules a batch, runs it, samples, updates the sequences
+        (ullm/core/engine.py:101-119)."""
+        sched = self.scheduler.schedule()
+        results = [
+            EngineStepResult(seq.seq_id, -1, True, reason, seq.num_prompt_tokens, seq.num_generated_tokens)
+            for seq, reason in sched.finished
+        ]
+        if not sched.scheduled:
+            return results
+        t0 = time.perf_counter() if self.profile_steps else 0.0
+        sampling = [s for s in sched.scheduled if s.samples]
+        params = [s.seq.sampling_params for s in sampling]
+        seeds = [s.seq.seed for s in sampling]
+        counters = [s.seq.num_generated_tokens for s in sampling]
+        decode_only = all(s.num_tokens == 1 and s.samples for s in sched.scheduled)
+        if decode_only and self.decode_graphs is not None and self.decode_graphs.takes(len(sched.scheduled)):
+            entries = [StepEntry(s.seq.seq_id, [s.seq.token_ids[s.start]], [0]) for s in sched.scheduled]
+            token_ids = self.decode_graphs.run(entries, params, seeds, counters)
+        else:
+            entries = [
+                StepEntry(s.seq.seq_id, s.seq.token_ids[s.start:s.start + s.num_tokens],
+                          [s.num_tokens - 1] if s.samples else [])
+                for s in sched.scheduled
+            ]
+            logits = self.runner.step(entries)
+            token_ids = []
+            if sampling:
+                self.sampler.stage(params, seeds, counters)
+                self.sampler.run(logits, len(sampling))
+                token_ids = self.sampler.fetch(len(sampling))
+            else:
+                torch.cuda.synchronize() if self.runner.device.type == "cuda" else None
+        self.runner.check_device_status()
+        it = iter(token_ids)
+        for s in sched.scheduled:
+            self.scheduler.on_step_done(s)
+            if not s.samples:
+                continue
+            tok = next(it)
+            seq = s.seq
+            if seq.status != SequenceStatus.RUNNING:
+                continue
+            self.scheduler.append_token(seq, tok)
+            finished, reason = self._is_sequence_finished(seq)
+            if finished:
+                self.scheduler.finish_sequence(seq, reason)
+            results.append(EngineStepResult(seq.seq_id, tok, finished, reason, seq.num_prompt_tokens,
+                                            seq.num_generated_tokens))
+        if self.profile_steps:
+            self.step_times.append((len(sched.scheduled), sched.num_tokens, time.perf_counter() - t0))
+        return results
+
+    def _is_sequence_finished(self, seq: Sequence) -> tuple[bool, FinishReason | None]:
+        """ullm/core/engine.py:175-200, same order: eos, max_tokens (total
+        length), max_new_tokens, context length."""
+        p = seq.sampling_params
+        if seq.token_ids[-1] == p.eos_token_id and not p.ignore_eos:
+            return True, FinishReason.STOP
+        if p.max_tokens and seq.num_tokens >= p.max_tokens:
+            return True, FinishReason.LENGTH
+        if p.max_new_tokens and seq.num_generated_tokens >= p.max_new_tokens:
+            return True, FinishReason.LENGTH
+        if seq.num_tokens >= self.context_len:
+            return True, FinishReason.LENGTH
+        return False, None
+
+    def stats(self) -> dict:
+        c = self.runner.cache
+        d = dict(self.scheduler.stats)
+        d.update(pages_total=c.num_pages, pages_free=c.num_free_pages(0),
+                 pages_in_prefix_tree=c.tree.num_pages if c.tree is not None else 0,
+                 steps_run=self.runner.steps_run)
+        return d
+
+    def shutdown(self) -> None:
+        self.decode_graphs = None

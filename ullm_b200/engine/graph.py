@@ -1,0 +1,72 @@
+"""CUDA-graph replay of decode steps.
+
+ullm/core/cuda_graph.py:9-97 and ullm/core/model_runner.py:428-500 capture the
+model forward for batch sizes [1, 2, 4, 8, 16, 32, ...] and replay the smallest
+one that fits, padding the batch.  Here the captured work is the whole device
+side of a decode step: embedding to logits AND the sampling kernel.  The step's
+integers and the sampling parameters live in fixed device buffers that are
+refreshed by two small copies before each replay; block tables are on the
+device already.  Graphs are captured on first use of a batch size, from the
+live batch itself (a decode step is idempotent: it writes the same keys and
+values and the same token again).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .batch import StepEntry
+
+
+def graph_batch_sizes(max_bs: int) -> list[int]:
+    sizes = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
+    if max_bs not in sizes:
+        sizes.append(max_bs)
+    return sorted(set(sizes))
+
+
+class DecodeGraphs:
+    def __init__(self, runner, sampler, max_bs: int):
+        self.runner = runner
+        self.sampler = sampler
+        self.sizes = graph_batch_sizes(max_bs)
+        self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, tuple]] = {}
+        self.pool = None
+        self.replays = 0
+
+    def takes(self, batch: int) -> bool:
+        return batch <= self.sizes[-1]
+
+    def padded(self, batch: int) -> int:
+        return next(s for s in self.sizes if s >= batch)
+
+    def _signature(self) -> tuple:
+        r = self.runner
+        return (r.workspace.generation, r.staging.dev.data_ptr(), self.sampler.dev.data_ptr())
+
+    def run(self, entries: list[StepEntry], params, seeds, counters) -> list[int]:
+        """One decode step for `entries` (one token each); returns their sampled ids."""
+        r = self.runner
+        B = len(entries)
+        Bp = self.padded(B)
+        ctx = r.prepare(entries, pad_to=Bp)
+        self.sampler.stage(params, seeds, counters)
+        held = self.graphs.get(Bp)
+        if held is None or held[1] != self._signature():
+            # warm up eagerly (sizes every workspace buffer), then record
+            logits = r.run_model(ctx)
+            self.sampler.run(logits, Bp)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self.pool):
+                logits = r.run_model(ctx)
+                self.sampler.run(logits, Bp)
+            if self.pool is None:
+                self.pool = g.pool()
+            self.graphs[Bp] = (g, self._signature())
+            held = self.graphs[Bp]
+        held[0].replay()
+        self.replays += 1
+        ids = self.sampler.fetch(B)
+        r.commit(entries)
+        return ids

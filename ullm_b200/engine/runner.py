@@ -144,10 +144,15 @@ class ModelRunner:
         return request_id in self.cache.requests
 
     # -- the step -------------------------------------------------------------------
-    def prepare(self, entries: list[StepEntry]) -> StepContext:
+    def prepare(self, entries: list[StepEntry], pad_to: int | None = None) -> StepContext:
         """Reserves pages for the step's tokens and stages its integers on the
         device.  Raises OutOfPages (nothing of the step has run then; pages
-        reserved for earlier entries stay with their requests)."""
+        reserved for earlier entries stay with their requests).
+
+        `pad_to` (decode steps replayed from a CUDA graph): the batch is filled
+        up to that many one-token rows that belong to no request: token 0,
+        batch row -1 (attention writes zeros), slot -1 (nothing is stored); their
+        logits rows are computed and ignored."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         cache = self.cache
@@ -217,6 +222,21 @@ class ModelRunner:
             cu.append(t)
             max_q = max(max_q, n)
             max_kv = max(max_kv, start + n)
+        if pad_to is not None and pad_to > B:
+            if T != B:
+                raise ValueError("only one-token steps can be padded")
+            extra = pad_to - B
+            h[o_ids + t:o_ids + t + extra] = 0
+            h[o_pos + t:o_pos + t + extra] = 0
+            h[o_req + t:o_req + t + extra] = -1
+            for g in range(len(cache.groups)):
+                o_sm = seg(f"slot_mapping{g}")
+                h[o_sm + t:o_sm + t + extra] = -1
+            h[o_rows + r:o_rows + r + extra] = range(t, t + extra)
+            h[o_kv + B:o_kv + pad_to] = 0
+            h[o_rs + B:o_rs + pad_to] = 0
+            cu.extend(range(t + 1, t + extra + 1))
+            T = R = B = pad_to
         h[o_cu:o_cu + B + 1] = cu
         cache.flush_block_tables()
         end = lay["_end"][0]
@@ -237,7 +257,8 @@ class ModelRunner:
             token_ids=d[o_ids:o_ids + T], positions=d[o_pos:o_pos + T], token_req=d[o_req:o_req + T],
             cu_q=d[o_cu:o_cu + B + 1], logits_rows=d[o_rows:o_rows + R], req_slots=req_slots,
             groups=groups, workspace=self.workspace,
-            cu_q_host=cu, req_slots_host=[rc.slot for rc in rcs], start_positions_host=starts,
+            cu_q_host=cu, req_slots_host=[rc.slot for rc in rcs] + [0] * (B - len(rcs)),
+            start_positions_host=starts + [0] * (B - len(rcs)),
             max_q_len=max_q, max_kv_len=max_kv, decode_only=(max_q == 1),
         )
 
@@ -247,12 +268,17 @@ class ModelRunner:
         `want` lists (a view of a buffer that the next step overwrites), or None
         when nothing is wanted."""
         ctx = self.prepare(entries)
-        caches = self.cache.layer_caches(ctx.groups)
-        logits = self.model.forward(ctx, caches)
+        logits = self.run_model(ctx)
+        self.commit(entries)
+        return logits
+
+    def run_model(self, ctx: StepContext) -> torch.Tensor | None:
+        return self.model.forward(ctx, self.cache.layer_caches(ctx.groups))
+
+    def commit(self, entries: list[StepEntry]) -> None:
         for e in entries:
             self.cache.commit(self.cache.requests[e.request_id], len(e.tokens))
         self.steps_run += 1
-        return logits
 
     def check_device_status(self) -> None:
         if self.device.type == "cuda":

@@ -1,0 +1,67 @@
+"""Chooses the next token of each row of a batch of logits.
+
+ullm/layers/sampler.py:20-56 is the reference: float32 logits / temperature,
+top-k, top-p, min-p, softmax, one multinomial draw from torch's global
+generator.  Here the filters and the draw are one CUDA kernel per row
+(csrc/sampling.cu), greedy rows take its argmax branch, and the uniform number
+of a row comes from a counter-based generator keyed by the request's seed and
+its step count, so a request's tokens do not depend on its batch neighbours.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..csrc import kernels
+from .params import SamplingParams
+
+_MASK64 = (1 << 64) - 1
+
+
+def uniform_for(seed: int, step: int) -> float:
+    """A number in [0, 1) from (seed, step): splitmix64 of a mixed key."""
+    z = (seed * 0x9E3779B97F4A7C15 + (step + 1) * 0xBF58476D1CE4E5B9) & _MASK64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK64
+    z ^= z >> 31
+    return (z >> 40) / float(1 << 24)
+
+
+class Sampler:
+    def __init__(self, device, max_rows: int, vocab_size: int):
+        self.device = torch.device(device)
+        self.max_rows = max_rows
+        self.vocab_size = vocab_size
+        pin = self.device.type == "cuda"
+        # one pinned block: temperature, top_p, min_p, uniform (float32) then top_k (int32 bits)
+        self.host = torch.zeros(5, max_rows, dtype=torch.float32, pin_memory=pin)
+        self.dev = torch.zeros(5, max_rows, dtype=torch.float32, device=self.device)
+        self.out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+
+    def stage(self, params: list[SamplingParams], seeds: list[int], steps: list[int]) -> None:
+        """Writes the rows' parameters into the pinned block and copies it."""
+        R = len(params)
+        if R > self.max_rows:
+            raise ValueError(f"{R} rows to sample, room for {self.max_rows}")
+        h = self.host.numpy()
+        hk = self.host[4].view(torch.int32).numpy()
+        V = self.vocab_size
+        for r, (p, seed, step) in enumerate(zip(params, seeds, steps)):
+            h[0, r] = p.temperature if p.temperature > 0 else 0.0
+            h[1, r] = p.top_p
+            h[2, r] = p.min_p
+            h[3, r] = uniform_for(seed, step)
+            hk[r] = V if p.top_k <= 0 else min(p.top_k, V)  # ullm/core/input_batch.py:163-171
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def run(self, logits: torch.Tensor, rows: int) -> torch.Tensor:
+        """Samples rows 0..rows-1 of `logits` with the staged parameters; the
+        ids stay on the device (int32 [rows])."""
+        d = self.dev
+        kernels().sample(logits[:rows], d[0], d[4].view(torch.int32), d[1], d[2], d[3], self.out)
+        return self.out[:rows]
+
+    def fetch(self, rows: int) -> list[int]:
+        self.out_host[:rows].copy_(self.out[:rows], non_blocking=False)
+        return self.out_host[:rows].tolist()
