@@ -1,0 +1,292 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second (batch 8 by
+default, also batch 1 and 64), prefill tokens per second at 2,048 tokens, and
+the fraction of the roofline each reaches.  Qwen3-8B layer sizes, random
+bfloat16 weights, synthetic token ids.
+
+    python bench.py --gpus 1 --steps K --warmup W
+
+prints ONE JSON line.  `value` times K decode steps with CUDA events around the
+engine's own decode path (staging copy, graph replay, token read-back); `e2e`
+times the same K steps through the public entry point (`Engine.step` under
+`LLM`), host token ids in and out.  For more than one GPU it says so and
+exits 2: this engine runs on one GPU.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen3-8B layer sizes
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "num_hidden_layers": 36,
+    "hidden_size": 4096,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "intermediate_size": 12288,
+    "vocab_size": 151936,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "attention_bias": False,
+    "tie_word_embeddings": False,
+    "use_sliding_window": False,
+    "max_position_embeddings": 40960,
+    "torch_dtype": "bfloat16",
+}
+CONTEXT_LEN = 4096
+START_CONTEXT = 2048
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int = 0):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.device_index = device_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def model_numbers(cfg: dict, layers: int) -> dict:
+    H, Hq, Hkv, D, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                           cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+    per_layer = (Hq + 2 * Hkv) * D * H + H * Hq * D + 2 * I * H + H * I
+    return {
+        "layer_weight_elems": per_layer,
+        "head_elems": V * H,
+        "kv_bytes_per_token": layers * 2 * Hkv * D * 2,
+        "weight_bytes_decode": (layers * per_layer + V * H) * 2,  # every matrix once; embedding rows are negligible
+    }
+
+
+def decode_bytes(nums: dict, batch: int, mean_ctx: float, hidden: int) -> float:
+    return nums["weight_bytes_decode"] + batch * mean_ctx * nums["kv_bytes_per_token"] + batch * hidden * 2
+
+
+def prefill_flops(cfg: dict, layers: int, T: int) -> float:
+    n = model_numbers(cfg, layers)
+    gemm = 2.0 * T * layers * n["layer_weight_elems"] + 2.0 * n["head_elems"]  # logits for the last token only
+    attn = layers * 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * (T * (T + 1) / 2)
+    return gemm + attn
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from ullm_b200.config import EngineConfig
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine.llm import LLM
+    from ullm_b200.sampling import SamplingParams
+
+    cfg = dict(QWEN3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    K, W = args.steps, args.warmup
+    max_bs = 64
+    tmp = tempfile.mkdtemp(prefix="ullm_b200_bench_")
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    tokens_per_req = START_CONTEXT + 2 * (K + W) + 64
+    num_pages = max_bs * (-(-tokens_per_req // PAGE_SIZE)) + 64
+    ec = EngineConfig(
+        model=tmp, max_bs=max_bs, context_len=CONTEXT_LEN, page_size=PAGE_SIZE, num_pages=num_pages,
+        max_num_batched_tokens=4096, dtype="bfloat16", load_format="random", seed=0, enable_prefix_caching=False,
+        log_level="warning",
+    )
+    llm = LLM(ec)
+    eng = llm.engine
+    runner = eng.runner
+    kern = kernels()
+    g = torch.Generator().manual_seed(1)
+
+    def prompt(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+
+    sp = SamplingParams(temperature=0.0, ignore_eos=True, max_new_tokens=10**9)
+
+    def start_batch(B, tag):
+        ids = [f"{tag}{i}" for i in range(B)]
+        for sid in ids:
+            eng.add_sequence(sid, prompt(START_CONTEXT), sp)
+        while any(s.num_pending > 1 or s.status.name == "WAITING" for s in
+                  [eng.scheduler.get_sequence(i) for i in ids]):
+            eng.step()
+        return ids
+
+    def stop_batch(ids):
+        for sid in ids:
+            eng.abort_sequence(sid)
+
+    def time_decode(B, tag, steps, warmup):
+        """Device-timed decode through Engine.step: (ms per step, wall seconds per step, launches per step)."""
+        ids = start_batch(B, tag)
+        for _ in range(warmup):
+            eng.step()
+        torch.cuda.synchronize()
+        l0 = kern.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        ms = e0.elapsed_time(e1) / steps
+        launches = (kern.launches - l0) / steps
+        ctx = START_CONTEXT + warmup + steps / 2.0
+        stop_batch(ids)
+        return ms, wall / steps, launches, ctx
+
+    # ---- prefill of 2,048 tokens ---------------------------------------------------
+    pre_ms = []
+    for i in range(max(3, min(W, 5)) + 5):
+        sid = f"p{i}"
+        eng.add_sequence(sid, prompt(PREFILL_TOKENS), SamplingParams(temperature=0.0, ignore_eos=True, max_new_tokens=1))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+    pre = statistics.median(pre_ms[3:])
+    pflops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / (pre / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre, 3),
+               "frac": round(pflops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode ----------------------------------------------------------------------
+    B = args.batch
+    with ClockSampler() as clk:
+        ms, wall, launches, ctx = time_decode(B, "d", K, W)
+    clocks = clk.summary()
+    value = B / (ms / 1e3)
+    e2e_value = B / wall
+    dbytes = decode_bytes(nums, B, ctx, cfg["hidden_size"])
+    achieved = dbytes / (ms / 1e3) / 1e9
+    points = {}
+    for pb in (1, 64):
+        pms, _pw, _pl, _pc = time_decode(pb, f"b{pb}_", max(8, K // 2), max(3, W))
+        points[f"decode_b{pb}"] = round(pb / (pms / 1e3), 1)
+    h2d = runner.staging.layout(runner.staging.max_tokens, runner.staging.max_requests)["_end"][0] * 4 \
+        + eng.sampler.host.numel() * 4
+    out = {
+        "metric": "decode tok/s at batch 8, Qwen3-8B shape (also batch 1/64 and 2048-token prefill)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "config": {
+            "model": "Qwen3-8B shape", "global_batch": B, "seq_len": CONTEXT_LEN, "parallelism": "single-gpu",
+            "layers": layers, "layers_of_config": full_layers, "hidden_size": cfg["hidden_size"],
+            "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"],
+            "vocab_size": cfg["vocab_size"], "start_context": START_CONTEXT, "page_size": PAGE_SIZE,
+            "kv_dtype": "bf16", "l2": "inputs>L2 (each step streams all weights)", "peaks": pk["source"],
+            "cuda_graph": not ec.enforce_eager,
+        },
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(B * 4)},
+        "gpu_launches": int(round(launches * K)),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    return out
+
+
+def run_reference(args) -> dict:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "ullm")):
+        return {"impl": "reference", "unavailable": "izmttk/ullm is not installed under baseline/_ref (offline install failed or was not done)"}
+    return {"impl": "reference", "unavailable":
+            "izmttk/ullm needs a tokenizer and FlashInfer JIT downloads for its engine; neither is available offline"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
+    out = run_ours(args)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

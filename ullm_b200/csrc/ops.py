@@ -74,6 +74,7 @@ class Kernels:
         self._declare()
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._f32_out_mm = None
+        self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
     # -- ctypes signatures --------------------------------------------------
     def _declare(self) -> None:
@@ -95,8 +96,8 @@ class Kernels:
             fn.argtypes = args
             fn.restype = c_int
 
-    @staticmethod
-    def _check(code: int, what: str) -> None:
+    def _check(self, code: int, what: str) -> None:
+        self.launches += 1
         if code != 0:
             raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
 

@@ -30,7 +30,7 @@ class DecodeGraphs:
         self.runner = runner
         self.sampler = sampler
         self.sizes = graph_batch_sizes(max_bs)
-        self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, tuple]] = {}
+        self.graphs: dict[int, tuple] = {}  # size -> (graph, signature, kernels recorded)
         self.pool = None
         self.replays = 0
 
@@ -58,15 +58,23 @@ class DecodeGraphs:
             self.sampler.run(logits, Bp)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            from ..csrc import kernels
+
+            before = kernels().launches
             with torch.cuda.graph(g, pool=self.pool):
                 logits = r.run_model(ctx)
                 self.sampler.run(logits, Bp)
+            captured = kernels().launches - before
+            kernels().launches = before  # recording launched nothing
             if self.pool is None:
                 self.pool = g.pool()
-            self.graphs[Bp] = (g, self._signature())
+            self.graphs[Bp] = (g, self._signature(), captured)
             held = self.graphs[Bp]
         held[0].replay()
         self.replays += 1
+        from ..csrc import kernels as _k
+
+        _k().launches += held[2]
         ids = self.sampler.fetch(B)
         r.commit(entries)
         return ids
