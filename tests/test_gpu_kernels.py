@@ -288,3 +288,130 @@ def test_sampling_is_independent_of_batch():
     for r in range(6):
         K().sample(lg[r:r + 1], t[r:r + 1], k[r:r + 1], p[r:r + 1], mp[r:r + 1], u[r:r + 1], one)
         assert int(one) == int(out[r])
+
+
+class _DecodeCtx:
+    """What the attention dispatcher reads of a step's context."""
+
+    def __init__(self, batch):
+        from ullm_b200.engine.batch import Workspace
+
+        self.decode_only = True
+        self.num_requests = batch
+        self.workspace = Workspace(torch.device("cuda"))
+        self.max_q_len = 1
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [
+    (32, 8, 128, 16, 0), (8, 8, 128, 16, 0), (16, 1, 64, 16, 0), (12, 3, 64, 8, 0), (6, 2, 128, 32, 0),
+    (32, 8, 128, 16, 100), (4, 2, 64, 4, 37), (9, 3, 128, 1, 0),
+])
+@pytest.mark.parametrize("batch", [1, 3, 40])
+def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch):
+    """The split tensor-core decode kernel against the plain reference: contexts
+    of 1 token, around page and tile edges, and long ones; padding rows (length
+    0) give zeros."""
+    dtype = torch.bfloat16
+    lens = [1, 15, 16, 17, 63, 64, 65, 300, 1000, 2049, 0, 33, 129, 511, 77, 5]
+    kv_lens = [lens[(i * 7 + batch) % len(lens)] for i in range(batch)]
+    if batch == 1:
+        kv_lens = [2049]
+    max_pages = -(-max(kv_lens + [1]) // page) + 1
+    pages = sum(-(-k // page) for k in kv_lens) + 2
+    g = torch.Generator().manual_seed(30 + batch)
+    perm = torch.randperm(pages, generator=g)
+    slots_of_req = torch.randperm(batch + 3, generator=g)[:batch].tolist()
+    bt = torch.full((batch + 3, max_pages), -1, dtype=torch.int32)
+    used = 0
+    for r, kl in enumerate(kv_lens):
+        n = -(-kl // page)
+        bt[slots_of_req[r], :n] = perm[used:used + n].int()
+        used += n
+    kp = rnd(pages, page, Hkv, D, seed=31, dtype=dtype)
+    vp = rnd(pages, page, Hkv, D, seed=32, dtype=dtype)
+    # slots never written hold NaN: the kernel must not read them
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    for r, kl in enumerate(kv_lens):
+        for p in range(kl):
+            written[int(bt[slots_of_req[r], p // page]) * page + p % page] = True
+    kp.view(-1, Hkv, D)[~written.cuda()] = float("nan")
+    vp.view(-1, Hkv, D)[~written.cuda()] = float("nan")
+    W = (Hq + 2 * Hkv) * D
+    qkv = rnd(batch, W, seed=33, dtype=dtype)
+    cu = torch.arange(batch + 1, dtype=torch.int32).cuda()
+    token_req = torch.arange(batch, dtype=torch.int32).cuda()
+    out = torch.full((batch, Hq * D), 9.0, dtype=dtype, device="cuda")
+    scale = D ** -0.5
+    ctx = _DecodeCtx(batch)
+    before = K().launches
+    K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
+                        torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale, ctx)
+    K().raise_on_status()
+    assert "attn.decode_scratch" in ctx.workspace.buffers, "the decode kernel was not chosen"
+    live = [r for r, kl in enumerate(kv_lens) if kl > 0]
+    ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(batch, Hq, D)[live],
+                              torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),
+                              torch.nan_to_num(vp.float().cpu()).view(-1, Hkv, D), bt.long(),
+                              [slots_of_req[r] for r in live], [1] * len(live), [kv_lens[r] for r in live], Hq, Hkv, D,
+                              page, window, scale)
+    got = out.view(batch, Hq, D).float().cpu()
+    assert torch.isfinite(got).all()
+    close(got[live], ref, dtype)
+    for r, kl in enumerate(kv_lens):
+        if kl == 0:
+            assert (got[r] == 0).all()
+
+
+class _MixedCtx(_DecodeCtx):
+    def __init__(self, batch):
+        super().__init__(batch)
+        self.decode_only = False
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [
+    (32, 8, 128, 16, 0), (8, 8, 128, 16, 0), (16, 1, 64, 16, 0), (9, 3, 64, 8, 0), (6, 2, 128, 32, 0),
+    (8, 2, 128, 16, 100), (4, 2, 64, 4, 37), (12, 4, 128, 1, 0), (5, 1, 64, 16, 0),
+])
+def test_prefill_attention_bf16_mixed_batch(Hq, Hkv, D, page, window):
+    """The tensor-core kernel for batches with prompt portions: whole prompts,
+    portions that continue a long context, two-token portions, single decoded
+    tokens, lengths around tile edges (64 keys, 128 rows / group tokens)."""
+    dtype = torch.bfloat16
+    q_lens = [1, 37, 1, 2, 64, 129, 300, 31, 200]
+    kv_lens = [150, 37, 1, 100, 130, 129, 700, 95, 200]
+    B, T = len(q_lens), sum(q_lens)
+    max_pages = -(-max(kv_lens) // page) + 1
+    pages = sum(-(-k // page) for k in kv_lens) + 3
+    g = torch.Generator().manual_seed(40)
+    perm = torch.randperm(pages, generator=g)
+    slots_of_req = torch.randperm(B + 2, generator=g)[:B].tolist()
+    bt = torch.full((B + 2, max_pages), -1, dtype=torch.int32)
+    used = 0
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    for r, kl in enumerate(kv_lens):
+        n = -(-kl // page)
+        bt[slots_of_req[r], :n] = perm[used:used + n].int()
+        for p in range(kl):
+            written[int(perm[used + p // page]) * page + p % page] = True
+        used += n
+    kp = rnd(pages, page, Hkv, D, seed=41, dtype=dtype)
+    vp = rnd(pages, page, Hkv, D, seed=42, dtype=dtype)
+    kp.view(-1, Hkv, D)[~written.cuda()] = float("nan")
+    vp.view(-1, Hkv, D)[~written.cuda()] = float("nan")
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, seed=43, dtype=dtype)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32).cuda()
+    token_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)]).cuda()
+    out = torch.full((T, Hq * D), 9.0, dtype=dtype, device="cuda")
+    scale = D ** -0.5
+    K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
+                        torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale,
+                        _MixedCtx(B))
+    K().raise_on_status()
+    assert K().attention_path == "prefill"
+    ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(T, Hq, D),
+                              torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),
+                              torch.nan_to_num(vp.float().cpu()).view(-1, Hkv, D), bt.long(), slots_of_req, q_lens,
+                              kv_lens, Hq, Hkv, D, page, window, scale)
+    got = out.view(T, Hq, D).float().cpu()
+    assert torch.isfinite(got).all()
+    close(got, ref, dtype)

@@ -1,0 +1,354 @@
+// Paged decode attention for bfloat16: one query token per request, keys and
+// values streamed once from the pages.  Split over the key range (grid.x) and,
+// inside a block, over its four warps; every warp runs an online softmax over
+// its own keys with tensor-core products (mma.sync m16n8k16, fp32 accumulate):
+//
+//   rows of the 16-row tile = the query heads that share one kv head (<= 16)
+//   S[16 x 16 keys]  = Q[16 x D] K^T          (scores, fp32)
+//   O[16 x D]       += P[16 x 16 keys] V      (P rounded to bf16, O fp32)
+//
+// K and V rows (one head of one token: D bf16) are gathered page by page with
+// cp.async into a three-stage ring per warp (chunks of 16 bytes, XOR-swizzled by
+// row so that ldmatrix reads are conflict-free).  Rows past the end of the range
+// are zero-filled, never read.  The warps' partial (max, sum, O) are merged in
+// shared memory; with more than one split the block writes its partial to the
+// scratch arrays and a second kernel merges the splits.  Softmax and all
+// accumulation are 32-bit; exp is ex2 on log2(e)-scaled scores.
+//
+// The grid depends on the batch size and the split count only, never on the
+// lengths, so a captured launch stays valid as the requests grow.
+#include "common.cuh"
+
+#define DEC_WARPS 4
+#define DEC_TILE 16   // keys per warp iteration
+#define DEC_STAGES 3
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool pred) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
+                                                  const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// shared memory of one block: per warp a ring of K and V tiles; afterwards reused for the merge
+template <int D>
+struct DecodeSmem {
+  static constexpr int ROW_BYTES = D * 2;
+  static constexpr int TILE_BYTES = DEC_TILE * ROW_BYTES;
+  static constexpr int WARP_BYTES = DEC_STAGES * 2 * TILE_BYTES;
+  static constexpr int RING_BYTES = DEC_WARPS * WARP_BYTES;
+  static constexpr int MERGE_BYTES = DEC_WARPS * 16 * (D + 2) * 4;
+  static constexpr int BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
+};
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
+                        const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                        const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_slots,
+                        const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int num_q, int num_kv, int page_size, int window,
+                        float scale_log2, long long num_pages, int* status) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
+  constexpr int KSTEPS = D / 16;       // k-steps of the score product
+  constexpr int NT_O = D / 8;          // n-tiles of the output
+  using S = DecodeSmem<D>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
+  const int group = num_q / num_kv;
+  const int kvl = kv_len[b];
+  const int pos = kvl - 1;
+  const int lo = (window > 0 && pos >= 0) ? max(0, pos - window + 1) : 0;
+  const int n_keys = pos >= 0 ? pos - lo + 1 : 0;
+  // this block's keys, then this warp's keys (both in whole tiles, except the last)
+  int per_split = (n_keys + num_splits - 1) / num_splits;
+  per_split = (per_split + DEC_TILE * DEC_WARPS - 1) / (DEC_TILE * DEC_WARPS) * (DEC_TILE * DEC_WARPS);
+  const int s_begin = min(n_keys, split * per_split), s_end = min(n_keys, s_begin + per_split);
+  const int per_warp = per_split / DEC_WARPS;
+  const int w_begin = lo + min(s_end, s_begin + warp * per_warp), w_end = lo + min(s_end, s_begin + (warp + 1) * per_warp);
+  const int tiles = (w_end - w_begin + DEC_TILE - 1) / DEC_TILE;
+  const int* bt = block_table + (long long)req_slots[b] * max_pages;
+  const long long kv_row = (long long)num_kv * D;
+
+  // ---- Q fragments (A operand), rows >= group are zero -------------------------------
+  unsigned qa[KSTEPS][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+    const __nv_bfloat16* q0 = q + (long long)b * q_row_stride + (long long)(kh * group + r0) * D;
+    const __nv_bfloat16* q1 = q + (long long)b * q_row_stride + (long long)(kh * group + r1) * D;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      qa[kk][0] = r0 < group ? *reinterpret_cast<const unsigned*>(q0 + kk * 16 + c) : 0u;
+      qa[kk][1] = r1 < group ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + c) : 0u;
+      qa[kk][2] = r0 < group ? *reinterpret_cast<const unsigned*>(q0 + kk * 16 + 8 + c) : 0u;
+      qa[kk][3] = r1 < group ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + 8 + c) : 0u;
+    }
+  }
+
+  unsigned char* ring = smem + warp * S::WARP_BYTES;
+  auto issue = [&](int tile) {
+    unsigned char* kbuf = ring + (tile % DEC_STAGES) * 2 * S::TILE_BYTES;
+    unsigned char* vbuf = kbuf + S::TILE_BYTES;
+    const int base = w_begin + tile * DEC_TILE;
+    // lanes 0..15 look up the slot of row `lane`
+    long long my_slot = -1;
+    if (lane < DEC_TILE) {
+      const int key = base + lane;
+      if (key < w_end) {
+        const int page = bt[key / page_size];
+        if (page < 0 || page >= num_pages) ullm_report(status, ULLM_STATUS_PAGE, b, page);
+        else my_slot = (long long)page * page_size + key % page_size;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < DEC_TILE * CHUNKS / 32; ++i) {
+      const int c = i * 32 + lane;
+      const int row = c / CHUNKS, ch = c % CHUNKS;
+      const long long slot = __shfl_sync(0xffffffffu, my_slot, row);
+      const bool ok = slot >= 0;
+      const long long off = ok ? (slot * kv_row + (long long)kh * D + ch * 8) : 0;
+      const int sw = row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16);
+      cp_async_16(kbuf + sw, k_cache + off, ok);
+      cp_async_16(vbuf + sw, v_cache + off, ok);
+    }
+  };
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT_O][4];
+#pragma unroll
+  for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < tiles) issue(s);
+    cp_async_commit();
+  }
+  for (int it = 0; it < tiles; ++it) {
+    if (it + DEC_STAGES - 1 < tiles) issue(it + DEC_STAGES - 1);
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
+    __syncwarp();
+    const unsigned char* kbuf = ring + (it % DEC_STAGES) * 2 * S::TILE_BYTES;
+    const unsigned char* vbuf = kbuf + S::TILE_BYTES;
+    // ---- scores: 2 n-tiles of 8 keys ------------------------------------------------
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      const int mat = lane >> 3, row = (mat >> 1) * 8 + (lane & 7), ch = 2 * kk + (mat & 1);
+      unsigned b0, b1, b2, b3;
+      ldmatrix_x4(b0, b1, b2, b3, kbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
+      mma_bf16(sc[0], qa[kk], b0, b1);
+      mma_bf16(sc[1], qa[kk], b2, b3);
+    }
+    // ---- mask, online softmax -------------------------------------------------------
+    const int base = w_begin + it * DEC_TILE;
+    float mx[2] = {m[0], m[1]};
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = base + t * 8 + (lane & 3) * 2 + (e & 1);
+        const float v = key < w_end ? sc[t][e] * scale_log2 : -INFINITY;
+        sc[t][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      alpha[r] = mx[r] == -INFINITY ? 1.f : exp2f(m[r] - mx[r]);
+      m[r] = mx[r];
+      l[r] *= alpha[r];
+    }
+    unsigned pa[4];
+    {
+      float p[2][4];
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[t][e] = m[e >> 1] == -INFINITY ? 0.f : exp2f(sc[t][e] - m[e >> 1]);
+          l[e >> 1] += p[t][e];
+        }
+      pa[0] = pack_bf16(p[0][0], p[0][1]);
+      pa[1] = pack_bf16(p[0][2], p[0][3]);
+      pa[2] = pack_bf16(p[1][0], p[1][1]);
+      pa[3] = pack_bf16(p[1][2], p[1][3]);
+    }
+    // ---- O = alpha O + P V ------------------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < NT_O; j += 2) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+      o[j + 1][0] *= alpha[0]; o[j + 1][1] *= alpha[0]; o[j + 1][2] *= alpha[1]; o[j + 1][3] *= alpha[1];
+      const int mat = lane >> 3, row = (mat & 1) * 8 + (lane & 7), ch = j + (mat >> 1);
+      unsigned b0, b1, b2, b3;
+      ldmatrix_x4_trans(b0, b1, b2, b3, vbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
+      mma_bf16(o[j], pa, b0, b1);
+      mma_bf16(o[j + 1], pa, b2, b3);
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+
+  // ---- merge the four warps in shared memory -----------------------------------------
+  __syncthreads();
+  float* mo = reinterpret_cast<float*>(smem);  // [warp][row 16][D + 2]
+  {
+    float* mine = mo + warp * 16 * (D + 2);
+    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) {
+      mine[r0 * (D + 2) + j * 8 + c] = o[j][0];
+      mine[r0 * (D + 2) + j * 8 + c + 1] = o[j][1];
+      mine[r1 * (D + 2) + j * 8 + c] = o[j][2];
+      mine[r1 * (D + 2) + j * 8 + c + 1] = o[j][3];
+    }
+    if ((lane & 3) == 0) {
+      mine[r0 * (D + 2) + D] = m[0];
+      mine[r0 * (D + 2) + D + 1] = l[0];
+      mine[r1 * (D + 2) + D] = m[1];
+      mine[r1 * (D + 2) + D + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * D; idx += blockDim.x) {
+    const int r = idx / D, d = idx - r * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, mo[(w * 16 + r) * (D + 2) + D]);
+    float ll = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float mw = mo[(w * 16 + r) * (D + 2) + D];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      ll += mo[(w * 16 + r) * (D + 2) + D + 1] * f;
+      acc += mo[(w * 16 + r) * (D + 2) + d] * f;
+    }
+    const int h = kh * group + r;
+    if (num_splits == 1) {
+      out[((long long)b * num_q + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    } else {
+      const long long p = ((long long)b * num_q + h) * num_splits + split;
+      part_o[p * D + d] = acc;
+      if (d == 0) {
+        part_ml[p * 2] = mm;
+        part_ml[p * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+// out[b, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+template <int D>
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, int num_splits) {
+  const long long bh = blockIdx.x;
+  const int d = threadIdx.x;
+  if (d >= D) return;
+  float mm = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, part_ml[(bh * num_splits + s) * 2]);
+  float ll = 0.f, acc = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float ms = part_ml[(bh * num_splits + s) * 2];
+    const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+    ll += part_ml[(bh * num_splits + s) * 2 + 1] * f;
+    acc += part_o[(bh * num_splits + s) * D + d] * f;
+  }
+  out[bh * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+}
+
+static int g_decode_attr_set[2] = {0, 0};
+
+template <int D>
+static int launch_decode(int which, const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
+                         const int* block_table, int max_pages, const int* req_slots, const int* kv_len, void* out,
+                         float* part_o, float* part_ml, int batch, int num_q, int num_kv, int page_size, int window,
+                         float scale, int num_splits, long long num_pages, int* status, cudaStream_t st) {
+  using S = DecodeSmem<D>;
+  if (!g_decode_attr_set[which]) {
+    if (cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
+        cudaSuccess)
+      return ULLM_ERR_LAUNCH;
+    g_decode_attr_set[which] = 1;
+  }
+  dim3 grid(num_splits, num_kv, batch);
+  decode_attention_kernel<D><<<grid, DEC_WARPS * 32, S::BYTES, st>>>(
+      (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
+      max_pages, req_slots, kv_len, (__nv_bfloat16*)out, part_o, part_ml, num_q, num_kv, page_size, window,
+      scale * 1.4426950408889634f, num_pages, status);
+  if (cudaGetLastError() != cudaSuccess) return ULLM_ERR_LAUNCH;
+  if (num_splits > 1) {
+    decode_merge_kernel<D><<<batch * num_q, D, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, num_splits);
+  }
+  return ullm_launch_status();
+}
+
+// Sizes this kernel takes: bfloat16, head_dim 64 or 128, at most 16 query heads per kv head.
+extern "C" int ullm_decode_attention_supported(int head_dim, int num_q, int num_kv) {
+  if (num_kv <= 0 || num_q % num_kv) return 0;
+  return (head_dim == 64 || head_dim == 128) && (num_q / num_kv) <= 16;
+}
+
+// Floats of scratch the split partials need: part_o then part_ml.
+extern "C" long long ullm_decode_attention_scratch_floats(int batch, int num_q, int head_dim, int num_splits) {
+  return (long long)batch * num_q * num_splits * (head_dim + 2);
+}
+
+extern "C" int ullm_decode_attention(const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
+                                     const int* block_table, int max_pages, const int* req_slots, const int* kv_len,
+                                     void* out, float* scratch, int batch, int num_q, int num_kv, int head_dim,
+                                     int page_size, int window, float scale, int num_splits, long long num_pages,
+                                     int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (batch < 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || num_splits <= 0 || window < 0)
+    return ULLM_ERR_BAD_SIZE;
+  if (!ullm_decode_attention_supported(head_dim, num_q, num_kv)) return ULLM_ERR_UNSUPPORTED;
+  if (num_splits > 1 && scratch == nullptr) return ULLM_ERR_BAD_SIZE;
+  if (batch == 0) return ULLM_OK;
+  float* part_o = scratch;
+  float* part_ml = scratch != nullptr ? scratch + (long long)batch * num_q * num_splits * head_dim : nullptr;
+  if (head_dim == 64)
+    return launch_decode<64>(0, q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out,
+                             part_o, part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages,
+                             status, st);
+  return launch_decode<128>(1, q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, part_o,
+                            part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages, status, st);
+}

@@ -74,6 +74,7 @@ class Kernels:
         self._declare()
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._f32_out_mm = None
+        self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
     # -- ctypes signatures --------------------------------------------------
@@ -88,6 +89,8 @@ class Kernels:
             "ullm_cast_bf16_f32": [P, P, LL, P],
             "ullm_qk_norm_rope_store": [I, P, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, LL, P, P],
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
+            "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P],
         }
@@ -95,6 +98,10 @@ class Kernels:
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        L.ullm_decode_attention_supported.argtypes = [I, I, I]
+        L.ullm_decode_attention_supported.restype = c_int
+        L.ullm_prefill_attention_supported.argtypes = [I, I, I]
+        L.ullm_prefill_attention_supported.restype = c_int
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
@@ -233,6 +240,30 @@ class Kernels:
         if k_pages.shape[-3:] != (page_size, num_kv, head_dim):
             raise KernelError(f"paged_attention: pages {tuple(k_pages.shape)} != [*, {page_size}, {num_kv}, {head_dim}]")
         num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
+        if (ctx is not None and ctx.decode_only and T == ctx.num_requests and qkv.dtype == torch.bfloat16
+                and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
+            # one token per request: stream the pages once, split over the key range
+            splits = max(1, min(32, -(-592 // (T * num_kv))))
+            scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32)
+            self._check(self.lib.ullm_decode_attention(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+                int(window), float(scale), splits, num_pages, _ptr(self.status), _stream()),
+                f"decode_attention (head_dim {head_dim})")
+            if splits > 1:
+                self.launches += 1  # the merge of the splits
+            self.attention_path = "decode"
+            return
+        if (ctx is not None and qkv.dtype == torch.bfloat16
+                and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv)):
+            self._check(self.lib.ullm_prefill_attention(
+                _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q, num_kv,
+                head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
+                f"prefill_attention (head_dim {head_dim})")
+            self.attention_path = "prefill"
+            return
+        self.attention_path = "generic"
         self._check(self.lib.ullm_paged_attention_generic(
             _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
             block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), _ptr(token_req), T, num_q, num_kv, head_dim, page_size,
