@@ -230,8 +230,8 @@ def run_ours(args) -> dict:
     for pb in (1, 64):
         pms, _pw, _pl, _pc = time_decode(pb, f"b{pb}_", max(8, K // 2), max(3, W))
         points[f"decode_b{pb}"] = round(pb / (pms / 1e3), 1)
-    h2d = runner.staging.layout(runner.staging.max_tokens, runner.staging.max_requests)["_end"][0] * 4 \
-        + eng.sampler.host.numel() * 4
+    st = runner.decode_staging
+    h2d = st.layout(st.max_tokens, st.max_requests)["_end"][0] * 4 + eng.sampler.host.numel() * 4
     out = {
         "metric": "decode tok/s at batch 8, Qwen3-8B shape (also batch 1/64 and 2048-token prefill)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,

@@ -1,0 +1,242 @@
+"""Each part alone against its plain counterpart, and a toy mixer with state of
+its own that is registered, built and stepped without touching the framework."""
+
+import pytest
+import torch
+
+import plain_model as pm
+from conftest import device
+from helpers import TOL, assert_close, errors, random_ids, weights_for, write_model_dir
+
+pytestmark = pytest.mark.gpu
+
+
+def runner_for(tmp_path, tag, dtype, **kw):
+    from ullm_b200.engine import ModelRunner
+
+    cfg, w, page = weights_for(tag, dtype)
+    d = write_model_dir(str(tmp_path / f"m{tag}{dtype}"), cfg, w)
+    r = ModelRunner(d, dtype=dtype, device=device(), page_size=page, num_pages=32, max_requests=4,
+                    max_context=cfg["max_position_embeddings"], max_step_tokens=64, poison_cache=True, **kw)
+    return r, cfg, {k: v.float() for k, v in w.items()}
+
+
+def rand(shape, seed, dtype, scale=1.0):
+    t = torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+    return t.to(dtype).to(device())
+
+
+def part_close(got, ref, dtype, what):
+    mx, _ = errors(got, ref)
+    assert mx <= (2e-5 if dtype == "float32" else 2e-2), f"{what}: max err {mx:.2e} of scale"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(tmp_path, dtype):
+    r, cfg, w = runner_for(tmp_path, "B", dtype)
+    norm = r.model.blocks[1].mixer_norm
+    td = r.dtype
+    x, res = rand((11, 80), 1, td), rand((11, 80), 2, td)
+    s = x.float().cpu() + res.float().cpu()
+    ref = pm.rms_norm(s, w["model.layers.1.input_layernorm.weight"], cfg["rms_norm_eps"])
+    res2 = res.clone()
+    out = norm.forward(x.clone(), res2)
+    part_close(out, ref, dtype, "fused add + norm")
+    assert torch.equal(res2.cpu(), s.to(td))
+    part_close(norm.forward(x.clone()), pm.rms_norm(x.float().cpu(), w["model.layers.1.input_layernorm.weight"],
+                                                   cfg["rms_norm_eps"]), dtype, "norm alone")
+
+
+def test_position_part_tables():
+    from ullm_b200.parts.position import RotaryPositions
+
+    p = RotaryPositions(rotary_dim=48, theta=50000.0, max_positions=300)
+    p.build_tables("cpu")
+    cos, sin = pm.rope_table(48, 50000.0, 300)
+    assert torch.equal(p.tables()["cos"], cos) and torch.equal(p.tables()["sin"], sin)
+    with pytest.raises(ValueError):
+        RotaryPositions(rotary_dim=7, theta=1.0, max_positions=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_feed_forward_and_head_parts(tmp_path, dtype):
+    from ullm_b200.engine.batch import Workspace
+
+    r, cfg, w = runner_for(tmp_path, "C", dtype)
+    td = r.dtype
+
+    class Ctx:
+        workspace = Workspace(r.device)
+
+    ids = torch.tensor(random_ids(cfg["vocab_size"], 9, 3), dtype=torch.int32, device=r.device)
+    emb = torch.empty(9, cfg["hidden_size"], dtype=td, device=r.device)
+    r.model.embedding.forward(ids, emb)
+    assert torch.equal(emb.float().cpu(), pm.embed(ids.cpu(), w["model.embed_tokens.weight"]))
+    x = rand((13, cfg["hidden_size"]), 4, td)
+    y = r.model.blocks[2].feed_forward.forward(x, Ctx())
+    part_close(y, pm.gated_mlp(x.float().cpu(), w, "model.layers.2.mlp."), dtype, "gated mlp")
+    lg = torch.empty(13, cfg["vocab_size"], dtype=torch.float32, device=r.device)
+    r.model.head.forward(x, lg)
+    part_close(lg, pm.lm_head(x.float().cpu(), w, cfg), dtype, "head")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layer", [0, 3])
+def test_attention_part_and_block_alone(tmp_path, dtype, layer):
+    """The mixer and the whole block of one layer (layer 3 of C is windowed), fed
+    with random activations in two steps: 40 tokens, then 9 more."""
+    from ullm_b200.engine import StepEntry
+
+    r, cfg, w = runner_for(tmp_path, "C", dtype)
+    td, H = r.dtype, cfg["hidden_size"]
+    x_all = rand((49, H), 5 + layer, td, 0.5)
+    res_all = rand((49, H), 6 + layer, td, 0.5)
+    pre = f"model.layers.{layer}."
+    pos = torch.arange(49)
+    # plain: attention over the whole 49 tokens, then the block
+    ref_attn, _ = pm.attention_block(x_all.float().cpu(), w, pre + "self_attn.", pm.normalized(cfg), pos,
+                                     pm.layer_window(cfg, layer))
+    stream = x_all.float().cpu() + res_all.float().cpu()
+    ref_stream, _ = pm.decoder_layer(stream, w, layer, pm.normalized(cfg), pos)
+    got_attn, got_y, got_res = [], [], []
+    ids = random_ids(cfg["vocab_size"], 49, 7)
+    # the mixer alone and the whole block write different keys: each gets a request (pages) of its own
+    for rid in ("mixer", "block"):
+        r.add_request(rid)
+        for a, b in ((0, 40), (40, 49)):
+            entries = [StepEntry(rid, ids[a:b], [])]
+            ctx = r.prepare(entries)
+            caches = r.cache.layer_caches(ctx.groups)
+            if rid == "mixer":
+                out = r.model.blocks[layer].mixer.forward(x_all[a:b].clone(), ctx, caches[layer])
+                got_attn.append(out.float().cpu().clone())
+            else:
+                res = res_all[a:b].clone()
+                y, res = r.model.blocks[layer].forward(x_all[a:b].clone(), res, ctx, caches[layer])
+                got_y.append(y.float().cpu().clone())
+                got_res.append(res.float().cpu().clone())
+            r.commit(entries)
+    r.check_device_status()
+    part_close(torch.cat(got_attn), ref_attn, dtype, "attention part")
+    part_close(torch.cat(got_y) + torch.cat(got_res), ref_stream, dtype, "block")
+
+
+# ---------------------------------------------------------------------------------------
+# a toy mixer with per-request state, defined here
+# ---------------------------------------------------------------------------------------
+def _register_toy():
+    from ullm_b200.config import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                                  ScheduleEntry, register_architecture)
+    from ullm_b200.parts import Mixer, ParamDecl, StateNeed, register_mixer
+
+    @register_mixer("running_mean")
+    class RunningMean(Mixer):
+        """out_t = mean(x_0 .. x_t) W^T.  State per request: the running sum (hidden floats) and the count."""
+
+        def __init__(self, hidden_size: int):
+            super().__init__()
+            self.hidden_size = hidden_size
+
+        def param_decls(self):
+            return {"mix.weight": ParamDecl((self.hidden_size, self.hidden_size))}
+
+        def state_need(self):
+            return StateNeed((self.hidden_size + 1,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            H = self.hidden_size
+            out = ctx.workspace.get("toy.out", x.shape[0], H, x.dtype)
+            W = self.tensors["mix.weight"].float()
+            for b in range(ctx.num_requests):
+                lo, hi = ctx.cu_q_host[b], ctx.cu_q_host[b + 1]
+                row = cache.state[ctx.req_slots_host[b]]
+                sums = torch.cumsum(x[lo:hi].float(), 0) + row[:H]
+                counts = row[H] + torch.arange(1, hi - lo + 1, device=x.device, dtype=torch.float32)
+                out[lo:hi] = ((sums / counts[:, None]) @ W.t()).to(x.dtype)
+                row[:H] = sums[-1]
+                row[H] = counts[-1]
+            return out
+
+    def parse(d):
+        return d
+
+    def spec(d):
+        H = d["hidden_size"]
+        norm = NormSpec("rmsnorm", H, d["eps"])
+        ff = FeedForwardSpec("gated_mlp", dict(hidden_size=H, intermediate_size=d["intermediate_size"], activation="silu"))
+        names = dict(mixer="mixer.", feed_forward="mlp.", mixer_norm="norm1.", feed_forward_norm="norm2.")
+        toy = LayerSpec("prenorm_residual", MixerSpec("running_mean", dict(hidden_size=H)), ff, norm, norm, names)
+        att = LayerSpec("prenorm_residual", MixerSpec("paged_attention", dict(
+            hidden_size=H, num_heads=d["heads"], num_kv_heads=d["kv_heads"], head_dim=d["head_dim"],
+            qk_norm=NormSpec("rmsnorm", d["head_dim"], d["eps"]),
+            position=PositionSpec("rope", d["head_dim"], d["theta"], d["max_positions"]))), ff, norm, norm, names)
+        return ModelSpec(architecture="ToyForCausalLM", hidden_size=H, vocab_size=d["vocab_size"], layers=[toy, att, toy],
+                         schedule=[ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2)], final_norm=norm,
+                         tie_embeddings=True, max_positions=d["max_positions"], dtype="float32",
+                         embedding_name="emb.", layer_name="layers.{}.", final_norm_name="final_norm.", head_name="head.")
+
+    register_architecture("ToyForCausalLM", parse, spec)
+
+
+TOY = dict(architectures=["ToyForCausalLM"], hidden_size=48, intermediate_size=72, vocab_size=97, heads=4, kv_heads=2,
+           head_dim=16, eps=1e-5, theta=10000.0, max_positions=128)
+
+
+def toy_plain(ids, w):
+    """Whole-sequence reference of the toy model."""
+    T = len(ids)
+    x = w["emb.weight"][torch.tensor(ids)]
+    cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5, rope_theta=10000.0)
+    for l in range(3):
+        p = f"layers.{l}."
+        h = pm.rms_norm(x, w[p + "norm1.weight"], 1e-5)
+        if l == 1:
+            a, _ = pm.attention_block(h, w, p + "mixer.", cfg, torch.arange(T))
+        else:
+            means = torch.cumsum(h, 0) / torch.arange(1, T + 1)[:, None]
+            a = means @ w[p + "mixer.mix.weight"].T
+        x = x + a
+        h = pm.rms_norm(x, w[p + "norm2.weight"], 1e-5)
+        x = x + pm.gated_mlp(h, w, p + "mlp.")
+    return pm.rms_norm(x, w["final_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    from ullm_b200.config import ARCHITECTURES
+    from ullm_b200.engine import ModelRunner, StepEntry
+    from ullm_b200.parts import MIXERS
+
+    _register_toy()
+    try:
+        r = ModelRunner(config=TOY, dtype=dtype, device=device(), page_size=8, num_pages=16, max_requests=3,
+                        max_context=128, max_step_tokens=64, load_format="random", seed=3, random_std=0.2,
+                        random_norm_std=0.1)
+        assert r.cache.tree is None, "prefix reuse is off for a model with per-request state"
+        assert sorted(r.cache.states) == [0, 2] and r.cache.states[0].shape == (3, 49)
+        w = {n: t.float().cpu() for n, t in r.model.all_tensors().items()}
+        a, b = random_ids(97, 60, 1), random_ids(97, 41, 2)
+        ra, rb = toy_plain(a, w), toy_plain(b, w)
+        r.add_request("a")
+        r.add_request("b")
+        got_a, got_b = [], []
+        # portions of a beside portions and single tokens of b
+        plan = [(7, 2), (2, 30), (20, 1), (1, 1), (30, 7)]
+        ia = ib = 0
+        for na, nb in plan:
+            lg = r.step([StepEntry("a", a[ia:ia + na], list(range(na))), StepEntry("b", b[ib:ib + nb], list(range(nb)))])
+            got_a.append(lg[:na].float().cpu().clone())
+            got_b.append(lg[na:].float().cpu().clone())
+            ia += na
+            ib += nb
+        r.check_device_status()
+        assert_close(torch.cat(got_a), ra[:ia], dtype, "toy a")
+        assert_close(torch.cat(got_b), rb[:ib], dtype, "toy b")
+        # a slot that is handed out again starts from zeroed state
+        r.end_request("a")
+        r.add_request("c")
+        lg = r.step([StepEntry("c", a[:10], list(range(10)))])
+        assert_close(lg.float().cpu(), ra[:10], dtype, "toy c on a reused slot")
+    finally:
+        ARCHITECTURES.pop("ToyForCausalLM", None)
+        MIXERS.pop("running_mean", None)

@@ -42,14 +42,14 @@ class DecodeGraphs:
 
     def _signature(self) -> tuple:
         r = self.runner
-        return (r.workspace.generation, r.staging.dev.data_ptr(), self.sampler.dev.data_ptr())
+        return (r.workspace.generation, r.decode_staging.dev.data_ptr(), self.sampler.dev.data_ptr())
 
     def run(self, entries: list[StepEntry], params, seeds, counters) -> list[int]:
         """One decode step for `entries` (one token each); returns their sampled ids."""
         r = self.runner
         B = len(entries)
         Bp = self.padded(B)
-        ctx = r.prepare(entries, pad_to=Bp)
+        ctx = r.prepare(entries, pad_to=Bp, staging=r.decode_staging)
         self.sampler.stage(params, seeds, counters)
         held = self.graphs.get(Bp)
         if held is None or held[1] != self._signature():

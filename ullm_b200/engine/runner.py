@@ -95,6 +95,8 @@ class ModelRunner:
             enable_prefix_cache=enable_prefix_cache, poison=poison_cache,
         )
         self.staging = StepStaging(self.device, max_step_tokens, max_requests, len(self.cache.groups))
+        # decode steps have few integers: a small buffer of their own keeps their copy small
+        self.decode_staging = StepStaging(self.device, max_requests, max_requests, len(self.cache.groups))
         self.workspace = Workspace(self.device)
         self.steps_run = 0
         self._staged = torch.cuda.Event() if self.device.type == "cuda" else None
@@ -144,7 +146,7 @@ class ModelRunner:
         return request_id in self.cache.requests
 
     # -- the step -------------------------------------------------------------------
-    def prepare(self, entries: list[StepEntry], pad_to: int | None = None) -> StepContext:
+    def prepare(self, entries: list[StepEntry], pad_to: int | None = None, staging=None) -> StepContext:
         """Reserves pages for the step's tokens and stages its integers on the
         device.  Raises OutOfPages (nothing of the step has run then; pages
         reserved for earlier entries stay with their requests).
@@ -185,8 +187,8 @@ class ModelRunner:
         for e, rc in zip(entries, rcs):
             cache.reserve(rc, len(e.tokens))
 
-        st = self.staging
-        st.ensure(T, B)
+        st = staging if staging is not None else self.staging
+        st.ensure(max(T, pad_to or 0), max(B, pad_to or 0))
         lay = st.layout(st.max_tokens, st.max_requests)
         if self._staged is not None:
             self._staged.synchronize()  # the previous step's copy out of the pinned buffer is done
