@@ -352,3 +352,38 @@ extern "C" int ullm_decode_attention(const void* q, long long q_row_stride, cons
   return launch_decode<128>(1, q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, part_o,
                             part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages, status, st);
 }
+
+// ---------------------------------------------------------------------------
+// The variant for callers that cannot allocate (declared in no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Scratch for the split partials, resident on every device that loads the library.
+static __device__ __align__(256) float g_static_scratch[ULLM_STATIC_SCRATCH_FLOATS];
+
+// In host code `g_static_scratch` is only a handle for the symbol; the device
+// address comes from cudaGetSymbolAddress, looked up once per device.
+#define ULLM_MAX_DEVICES 64
+static float* g_static_scratch_addr[ULLM_MAX_DEVICES] = {nullptr};
+
+extern "C" long long ullm_decode_attention_static_capacity(void) { return ULLM_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int ullm_decode_attention_static(const void* q, long long q_row_stride, const void* k_cache,
+                                            const void* v_cache, const int* block_table, int max_pages,
+                                            const int* req_slots, const int* kv_len, void* out, int batch, int num_q,
+                                            int num_kv, int head_dim, int page_size, int window, float scale,
+                                            int num_splits, long long num_pages, int* status, void* stream) {
+  if (batch < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || num_splits <= 0) return ULLM_ERR_BAD_SIZE;
+  if (ullm_decode_attention_scratch_floats(batch, num_q, head_dim, num_splits) > ULLM_STATIC_SCRATCH_FLOATS)
+    return ULLM_ERR_SCRATCH_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= ULLM_MAX_DEVICES) return ULLM_ERR_LAUNCH;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_static_scratch) != cudaSuccess || p == nullptr) return ULLM_ERR_LAUNCH;
+    g_static_scratch_addr[dev] = p;
+  }
+  return ullm_decode_attention(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out,
+                               g_static_scratch_addr[dev], batch, num_q, num_kv, head_dim, page_size, window, scale,
+                               num_splits, num_pages, status, stream);
+}
