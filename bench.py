@@ -258,6 +258,40 @@ def run_ours(args) -> dict:
     return out
 
 
+def run_probe(args) -> int:
+    """A few eager steps at the benchmark's layer sizes, for profilers: `--probe decode` runs `--steps` decode
+    steps of `--batch` requests that each hold `--context` tokens (the held context is reserved, not computed: a
+    profile needs its size, not its content); `--probe prefill` runs `--steps` prompts of 2,048 tokens."""
+    import torch
+
+    from ullm_b200.engine import ModelRunner, StepEntry
+
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = args.layers or 2
+    B, ctx = args.batch, args.context
+    r = ModelRunner(config=cfg, dtype="bfloat16", page_size=PAGE_SIZE, num_pages=B * (ctx // PAGE_SIZE + 8) + 160,
+                    max_requests=B + 1, max_context=CONTEXT_LEN, max_step_tokens=max(B, PREFILL_TOKENS),
+                    load_format="random")
+    ids = []
+    for i in range(B):
+        rc = r.add_request(f"r{i}")
+        r.cache.reserve(rc, ctx)
+        r.cache.commit(rc, ctx)
+        ids.append(f"r{i}")
+    if args.probe == "prefill":
+        for s in range(args.steps):
+            r.add_request(f"p{s}")
+            r.step([StepEntry(f"p{s}", [1 + s] * PREFILL_TOKENS, [PREFILL_TOKENS - 1])])
+            r.end_request(f"p{s}")
+    else:
+        for s in range(args.steps):
+            r.step([StepEntry(i, [5 + s], [0]) for i in ids])
+    torch.cuda.synchronize()
+    r.check_device_status()
+    print(f"probe {args.probe}: {args.steps} steps, {cfg['num_hidden_layers']} layers, batch {B}, context {ctx}")
+    return 0
+
+
 def run_reference(args) -> dict:
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "ullm")):
@@ -274,12 +308,16 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--probe", default=None, choices=["decode", "prefill"], help="a few eager steps for a profiler")
+    ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.probe:
+        return run_probe(args)
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0
