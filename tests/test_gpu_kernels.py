@@ -415,3 +415,41 @@ def test_prefill_attention_bf16_mixed_batch(Hq, Hkv, D, page, window):
     got = out.view(T, Hq, D).float().cpu()
     assert torch.isfinite(got).all()
     close(got, ref, dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (1, 128, 64), (8, 256, 128), (8, 4096, 4096), (8, 6144, 4096), (8, 4096, 12288), (3, 24576, 4096),
+    (16, 1000, 520), (17, 331, 80), (64, 4096, 4096), (33, 777, 4104), (5, 151936, 1024), (48, 130, 72),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_small_m_linear_tcgen05(M, N, K, out_dtype):
+    """The tcgen05/TMA product for decode-sized batches against a float32
+    reference, with and without bias; sizes that are no multiple of the tile
+    (128 rows, 64 columns) and K splits across a cluster."""
+    x = rnd(M, K, seed=50, dtype=torch.bfloat16)
+    w = rnd(N, K, seed=51, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(N, seed=52, dtype=torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for b in (None, bias):
+        out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+        took = K_().small_m_linear(x, w, out, b)
+        K_().raise_on_status()
+        assert took
+        r = ref + (b.float() if b is not None else 0)
+        err = (out.float() - r).abs().max().item() / max(r.abs().max().item(), 1e-6)
+        assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * K ** 0.5), f"max err {err:.3e} of scale"
+
+
+def K_():
+    return K()
+
+
+def test_small_m_linear_refuses_what_it_does_not_take():
+    x = rnd(70, 64, seed=1, dtype=torch.bfloat16)
+    w = rnd(128, 64, seed=2, dtype=torch.bfloat16)
+    assert not K().small_m_linear(x, w, torch.empty(70, 128, dtype=torch.bfloat16, device="cuda"))
+    x = rnd(4, 60, seed=1, dtype=torch.bfloat16)  # rows of 120 bytes: no 16-byte stride for TMA
+    w = rnd(128, 60, seed=2, dtype=torch.bfloat16)
+    assert not K().small_m_linear(x, w, torch.empty(4, 128, dtype=torch.bfloat16, device="cuda"))
+    xf = rnd(4, 64, seed=1)
+    assert not K().small_m_linear(xf, rnd(128, 64, seed=2), torch.empty(4, 128, device="cuda"))

@@ -74,6 +74,8 @@ class Kernels:
         self._declare()
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._f32_out_mm = None
+        self.use_small_m_linear = False  # the tcgen05 kernel for decode-sized products
+        self.small_m_rows = 64
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
@@ -91,6 +93,7 @@ class Kernels:
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P],
         }
@@ -102,6 +105,8 @@ class Kernels:
         L.ullm_decode_attention_supported.restype = c_int
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
+        L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
+        L.ullm_linear_tcgen05_supported.restype = c_int
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
@@ -119,11 +124,32 @@ class Kernels:
             raise KernelError(f"a kernel refused an index: {msg}")
 
     # -- library matrix products ---------------------------------------------
+    def small_m_linear(self, x, weight, out, bias=None) -> bool:
+        """The hand-written tcgen05/TMA product for few rows (decode steps):
+        bfloat16 operands, out bfloat16 or float32.  False when the shape is not
+        one it takes (the caller then uses the library)."""
+        M, K = x.shape
+        N = weight.shape[0]
+        if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous()
+                or not weight.is_contiguous() or not out.is_contiguous() or weight.shape[1] != K
+                or out.shape != (M, N) or out.dtype not in (torch.bfloat16, torch.float32)
+                or (bias is not None and bias.dtype != torch.bfloat16)
+                or not self.lib.ullm_linear_tcgen05_supported(M, N, K)
+                or x.data_ptr() % 16 or weight.data_ptr() % 16):
+            return False
+        self._check(self.lib.ullm_linear_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
+                                                 1 if out.dtype == torch.float32 else 0, _ptr(self.status),
+                                                 _stream()), f"linear_tcgen05 ({M}x{K} . {N}x{K})")
+        return True
+
     def linear(self, x, weight, out, bias=None):
-        """out = x @ weight.T (+ bias).  The vendor library's matrix product,
-        float32 without any reduced-precision mode."""
+        """out = x @ weight.T (+ bias).  Few bfloat16 rows: the hand-written
+        tcgen05 kernel.  Otherwise the vendor library's matrix product, float32
+        without any reduced-precision mode."""
         _need(x, "x")
         _need(out, "out")
+        if self.use_small_m_linear and x.shape[0] <= self.small_m_rows and self.small_m_linear(x, weight, out, bias):
+            return out
         if bias is not None:
             torch.addmm(bias, x, weight.t(), out=out)
         else:
@@ -135,6 +161,8 @@ class Kernels:
         _need(out, "out", torch.float32)
         if x.dtype == torch.float32:
             torch.mm(x, weight.t(), out=out)
+            return out
+        if self.use_small_m_linear and x.shape[0] <= self.small_m_rows and self.small_m_linear(x, weight, out):
             return out
         if self._f32_out_mm is None:
             try:
