@@ -77,6 +77,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
                         float* __restrict__ part_ml, int num_q, int num_kv, int page_size, int window,
                         float scale_log2, long long num_pages, int* status) {
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;       // k-steps of the score product
   constexpr int NT_O = D / 8;          // n-tiles of the output
@@ -280,6 +282,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int num_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
   if (d >= D) return;
@@ -310,15 +314,15 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
     g_decode_attr_set[which] = 1;
   }
   dim3 grid(num_splits, num_kv, batch);
-  decode_attention_kernel<D><<<grid, DEC_WARPS * 32, S::BYTES, st>>>(
+  int rc = ullm_launch_kernel(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
       max_pages, req_slots, kv_len, (__nv_bfloat16*)out, part_o, part_ml, num_q, num_kv, page_size, window,
       scale * 1.4426950408889634f, num_pages, status);
-  if (cudaGetLastError() != cudaSuccess) return ULLM_ERR_LAUNCH;
-  if (num_splits > 1) {
-    decode_merge_kernel<D><<<batch * num_q, D, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, num_splits);
-  }
-  return ullm_launch_status();
+  if (rc != ULLM_OK) return rc;
+  if (num_splits > 1)
+    rc = ullm_launch_kernel(decode_merge_kernel<D>, dim3(batch * num_q), dim3(D), 0, st, (const float*)part_o,
+                            (const float*)part_ml, (__nv_bfloat16*)out, num_splits);
+  return rc;
 }
 
 // Sizes this kernel takes: bfloat16, head_dim 64 or 128, at most 16 query heads per kv head.

@@ -32,6 +32,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
                                                int head_dim, int page_size, int window, float scale,
                                                long long num_pages, int* status) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HEAD_DIM];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * ATT_WARPS + warp;
   if (unit >= (long long)tokens * num_q) return;
@@ -114,16 +116,17 @@ static int launch_generic(const void* q, long long q_row_stride, void* out, cons
   const long long blocks = (units + ATT_WARPS - 1) / ATT_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
 #define LAUNCH(OREGS)                                                                                             \
-  paged_attention_generic_kernel<T, OREGS><<<(int)blocks, ATT_WARPS * 32, 0, st>>>(                                \
+  rc = ullm_launch_kernel(paged_attention_generic_kernel<T, OREGS>, dim3((int)blocks), dim3(ATT_WARPS * 32), 0, st, \
       (const T*)q, q_row_stride, (T*)out, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, req_slots,  \
       cu_q, kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status)
+  int rc = ULLM_OK;
   if (head_dim <= 32) LAUNCH(1);
   else if (head_dim <= 64) LAUNCH(2);
   else if (head_dim <= 128) LAUNCH(4);
   else if (head_dim <= 256) LAUNCH(8);
   else LAUNCH(16);
 #undef LAUNCH
-  return ullm_launch_status();
+  return rc;
 }
 
 extern "C" int ullm_paged_attention_generic(int dtype, const void* q, long long q_row_stride, void* out,

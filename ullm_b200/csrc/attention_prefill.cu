@@ -70,6 +70,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len, int num_requests, int num_q,
                          int num_kv, int page_size, int window, float scale_log2, long long num_pages, int* status) {
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int CHUNKS = D / 8, KSTEPS = D / 16, NT_O = D / 8, NT_S = PRE_N / 8;
   using S = PrefillSmem<D>;
   unsigned char* q_s = smem;
@@ -296,7 +298,7 @@ static int launch_prefill(int which, const void* q, long long q_row_stride, void
   const int tpt = PRE_M / (num_q / num_kv);
   // at most ceil(tokens / tpt) + num_requests token tiles exist, however the tokens are spread
   dim3 grid((tokens + tpt - 1) / tpt + num_requests, num_kv);
-  prefill_attention_kernel<D><<<grid, PRE_WARPS * 32, S::BYTES, st>>>(
+  return ullm_launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, block_table, max_pages, req_slots, cu_q, kv_len, num_requests, num_q, num_kv,
       page_size, window, scale * 1.4426950408889634f, num_pages, status);

@@ -79,6 +79,39 @@ __device__ __host__ __forceinline__ bool rows_are_16B(const void* p, long long c
          ((row_stride * sizeof(T)) % 16 == 0);
 }
 
+// Programmatic dependent launch.  Every kernel of this library starts with
+//   pdl_launch_dependents();  the next kernel in the stream may be scheduled as soon as all blocks of
+//                             this one are running (its blocks then wait in their own pdl_wait)
+//   pdl_wait();               blocks until the previous kernel in the stream has completed and its
+//                             writes are visible; nothing that depends on it may be touched before
+// so that launch latency and per-block set-up of a kernel overlap with the tail of the one before it.
+// A kernel may do work that does not depend on its predecessor (reading weights) before pdl_wait().
+// Launches carry the attribute only while ullm_set_pdl(1) is in force; without it both calls are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_ullm_pdl;
+
+template <typename... KArgs, typename... Args>
+static inline int ullm_launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_ullm_pdl ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) != cudaSuccess) {
+    cudaGetLastError();
+    return ULLM_ERR_LAUNCH;
+  }
+  return ULLM_OK;
+}
+
 static inline int ullm_launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? ULLM_OK : ULLM_ERR_LAUNCH;

@@ -3,6 +3,9 @@
 // moved in 16-byte pieces are, others go element by element.
 #include "common.cuh"
 
+int g_ullm_pdl = 0;
+extern "C" void ullm_set_pdl(int on) { g_ullm_pdl = on ? 1 : 0; }
+
 // ---------------------------------------------------------------------------
 // row copies: out[r, :] = src[index[r], :]
 // ---------------------------------------------------------------------------
@@ -10,6 +13,8 @@ template <typename T>
 __global__ void gather_rows_kernel(const int* __restrict__ index, const T* __restrict__ src, T* __restrict__ out,
                                    int rows, int cols, long long src_stride, long long out_stride, int src_rows,
                                    int status_code, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= rows) return;
   const int s = index[r];
@@ -36,9 +41,8 @@ static int gather_rows_launch(const int* index, const void* src, void* out, int 
   if (rows == 0) return ULLM_OK;
   int threads = 256;
   if (cols * (int)sizeof(T) <= 16 * 64) threads = 64;
-  gather_rows_kernel<T><<<rows, threads, 0, st>>>(index, (const T*)src, (T*)out, rows, cols, src_stride, out_stride,
-                                                   src_rows, code, status);
-  return ullm_launch_status();
+  return ullm_launch_kernel(gather_rows_kernel<T>, dim3(rows), dim3(threads), 0, st, index, (const T*)src, (T*)out, rows,
+                            cols, src_stride, out_stride, src_rows, code, status);
 }
 
 extern "C" int ullm_embedding(int dtype, const int* ids, const void* table, void* out, int tokens, int hidden,
@@ -79,6 +83,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(const T* x, T* residual, const float* __restrict__ w, T* out, int cols,
                                    float eps) {  // out may be x
   extern __shared__ float row[];  // cols floats, then 33 for the reduction
+  pdl_launch_dependents();
+  pdl_wait();
   float* scratch = row + cols;
   const long long base = (long long)blockIdx.x * cols;
   float acc = 0.f;
@@ -112,8 +118,8 @@ static int add_rmsnorm_launch(int which, const void* x, void* residual, const fl
   }
   int threads = 32;
   while (threads < 1024 && threads * 4 < cols) threads <<= 1;
-  add_rmsnorm_kernel<T><<<rows, threads, smem, st>>>((const T*)x, (T*)residual, w, (T*)out, cols, eps);
-  return ullm_launch_status();
+  return ullm_launch_kernel(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), smem, st, (const T*)x, (T*)residual, w,
+                            (T*)out, cols, eps);
 }
 
 extern "C" int ullm_add_rmsnorm(int dtype, const void* x, void* residual, const float* weight, void* out, int rows,
@@ -137,6 +143,8 @@ __device__ __forceinline__ float act_gelu_tanh(float g) {
 
 template <typename T, int ACT>
 __global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long n = rows * inter;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / inter;
@@ -152,6 +160,8 @@ __global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, lo
 template <int ACT>
 __global__ void act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                       long long rows, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int per_row = inter / 8;
   const long long n = rows * per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -185,27 +195,23 @@ extern "C" int ullm_act_mul(int dtype, int act, const void* gate_up, void* out, 
     long long blocks = (n / 8 + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (act == 0)
-      act_mul_bf16x8_kernel<0><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
-                                                               rows, inter);
+      return ullm_launch_kernel(act_mul_bf16x8_kernel<0>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
     else
-      act_mul_bf16x8_kernel<1><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
-                                                               rows, inter);
+      return ullm_launch_kernel(act_mul_bf16x8_kernel<1>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
     return ullm_launch_status();
   }
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == ULLM_DTYPE_F32) {
     if (act == 0)
-      act_mul_kernel<float, 0><<<(int)blocks, threads, 0, st>>>((const float*)gate_up, (float*)out, rows, inter);
+      return ullm_launch_kernel(act_mul_kernel<float, 0>, dim3((int)blocks), dim3(threads), 0, st, (const float*)gate_up, (float*)out, (long long)rows, inter);
     else
-      act_mul_kernel<float, 1><<<(int)blocks, threads, 0, st>>>((const float*)gate_up, (float*)out, rows, inter);
+      return ullm_launch_kernel(act_mul_kernel<float, 1>, dim3((int)blocks), dim3(threads), 0, st, (const float*)gate_up, (float*)out, (long long)rows, inter);
   } else if (dtype == ULLM_DTYPE_BF16) {
     if (act == 0)
-      act_mul_kernel<__nv_bfloat16, 0><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up,
-                                                                       (__nv_bfloat16*)out, rows, inter);
+      return ullm_launch_kernel(act_mul_kernel<__nv_bfloat16, 0>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
     else
-      act_mul_kernel<__nv_bfloat16, 1><<<(int)blocks, threads, 0, st>>>((const __nv_bfloat16*)gate_up,
-                                                                       (__nv_bfloat16*)out, rows, inter);
+      return ullm_launch_kernel(act_mul_kernel<__nv_bfloat16, 1>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
   } else {
     return ULLM_ERR_BAD_DTYPE;
   }
@@ -216,6 +222,8 @@ extern "C" int ullm_act_mul(int dtype, int act, const void* gate_up, void* out, 
 // bf16 -> f32 cast of a contiguous array (logits for the sampler and the host)
 // ---------------------------------------------------------------------------
 __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = __bfloat162float(in[i]);
 }
@@ -225,6 +233,6 @@ extern "C" int ullm_cast_bf16_f32(const void* in, float* out, long long n, void*
   if (n == 0) return ULLM_OK;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  cast_bf16_f32_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)in, out, n);
-  return ullm_launch_status();
+  return ullm_launch_kernel(cast_bf16_f32_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream,
+                            (const __nv_bfloat16*)in, out, n);
 }

@@ -24,6 +24,7 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -120,6 +121,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                       const LinParams p) {
   extern __shared__ unsigned char lin_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], accum_bar;
+  pdl_launch_dependents();
   __shared__ uint32_t tmem_base_slot;
   unsigned char* tiles = (unsigned char*)(((uintptr_t)lin_smem_raw + 1023) & ~(uintptr_t)1023);
   const int a_bytes = LIN_BM * 128, b_bytes = p.m_pad * 128, stage_bytes = a_bytes + ((b_bytes + 1023) & ~1023);
@@ -138,6 +140,14 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
     mbar_init(&accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+    // requested at once, before tensor memory is set up and before pdl_wait().
+    const int first = min(p.stages, my_blocks);
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(&full_bar[i], a_bytes + b_bytes);
+      tma_load_2d(tiles + i * stage_bytes, &map_w, &full_bar[i], (kb_begin + i) * LIN_BK, n0);
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lin_smem(&tmem_base_slot)),
@@ -152,7 +162,15 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
   if (warp == 0 && lane == 0) {
     // ---- producer: TMA loads ---------------------------------------------------------------
-    for (int i = 0; i < my_blocks; ++i) {
+    // (the first ring of weight tiles was requested at the top) the activation tiles follow once the
+    // kernel before this one is complete
+    const int first = min(p.stages, my_blocks);
+    pdl_wait();
+    for (int i = 0; i < first; ++i) {
+      unsigned char* b = tiles + i * stage_bytes + a_bytes;
+      tma_load_2d(b, &map_x, &full_bar[i], (kb_begin + i) * LIN_BK, 0);
+    }
+    for (int i = first; i < my_blocks; ++i) {
       const int s = i % p.stages;
       const uint32_t parity = ((i / p.stages) & 1) ^ 1;  // a fresh barrier passes a wait on parity 1
       if (!mbar_wait(&empty_bar[s], parity)) {
@@ -171,6 +189,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.m_pad >> 3) << 17) |
                            ((uint32_t)(LIN_BM >> 4) << 24);
     bool ok = true;
+    pdl_wait();  // the bounded waits below then cover TMA latency only, not the kernel before this one
     for (int i = 0; i < my_blocks && ok; ++i) {
       const int s = i % p.stages;
       const uint32_t parity = (i / p.stages) & 1;
@@ -195,6 +214,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
   // ---- epilogue: all four warps; warp w owns accumulator lanes 32w .. 32w+31 ------------------------
   __syncwarp();
+  pdl_wait();  // nothing of the previous kernel's may be overwritten before it is complete
   bool have = my_blocks > 0;
   if (have) {
     if (!mbar_wait(&accum_bar, 0)) {
@@ -361,8 +381,15 @@ extern "C" int ullm_linear_tcgen05(const void* x, const void* w, const void* bia
   p.splits = splits;
   const int b_bytes = ((p.m_pad * 128) + 1023) & ~1023;
   const int stage_bytes = LIN_BM * 128 + b_bytes;
-  // as many stages as let two blocks share an SM (227 KB)
-  int stages = (112 * 1024 - 1024) / stage_bytes;
+  // Stages: the ring is what a block holds in flight, and what it has prefetched while it waits for
+  // the kernel before it.  ULLM_B200_LIN_SMEM_KB bounds a block's ring (default 112 KB: two blocks per SM).
+  static int ring_kb = 0;
+  if (ring_kb == 0) {
+    const char* e = getenv("ULLM_B200_LIN_SMEM_KB");
+    ring_kb = e != nullptr ? atoi(e) : 112;
+    if (ring_kb < 40 || ring_kb > 200) ring_kb = 112;
+  }
+  int stages = (ring_kb * 1024 - 1024) / stage_bytes;
   const int kb_per = (p.k_blocks + splits - 1) / splits;
   if (stages > kb_per) stages = kb_per < 2 ? 2 : kb_per;
   if (stages > 8) stages = 8;
@@ -383,13 +410,15 @@ extern "C" int ullm_linear_tcgen05(const void* x, const void* w, const void* bia
   cfg.blockDim = dim3(LIN_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = splits;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_ullm_pdl ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, linear_tcgen05_kernel, map_w, map_x, p) != cudaSuccess) {
     cudaGetLastError();
     return ULLM_ERR_LAUNCH;

@@ -74,7 +74,12 @@ class Kernels:
         self._declare()
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._f32_out_mm = None
-        self.use_small_m_linear = False  # the tcgen05 kernel for decode-sized products
+        import os
+
+        self.pdl = False
+        if os.environ.get("ULLM_B200_PDL", "0") == "1":
+            self.set_pdl(True)
+        self.use_small_m_linear = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0") == "1"  # the tcgen05 kernel
         self.small_m_rows = 64
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
@@ -105,6 +110,8 @@ class Kernels:
         L.ullm_decode_attention_supported.restype = c_int
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
+        L.ullm_set_pdl.argtypes = [I]
+        L.ullm_set_pdl.restype = None
         L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
         L.ullm_linear_tcgen05_supported.restype = c_int
 
@@ -112,6 +119,12 @@ class Kernels:
         self.launches += 1
         if code != 0:
             raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+
+    def set_pdl(self, on: bool) -> None:
+        """Programmatic dependent launch for every kernel of the library: a kernel's launch and
+        set-up overlap the tail of the kernel before it in the stream."""
+        self.lib.ullm_set_pdl(1 if on else 0)
+        self.pdl = bool(on)
 
     # -- status word ----------------------------------------------------------
     def raise_on_status(self) -> None:

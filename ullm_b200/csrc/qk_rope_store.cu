@@ -23,6 +23,8 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
                                           const int* __restrict__ slot_mapping, T* k_cache, T* v_cache,
                                           long long num_slots, int* status) {
   __shared__ float sh[QK_WARPS][QK_MAX_HEAD_DIM];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = num_q + 2 * num_kv;
   const long long unit = (long long)blockIdx.x * QK_WARPS + warp;
@@ -103,11 +105,11 @@ extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num
   const long long blocks = (units + QK_WARPS - 1) / QK_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
   if (dtype == ULLM_DTYPE_F32)
-    qk_norm_rope_store_kernel<float><<<(int)blocks, QK_WARPS * 32, 0, st>>>(
+    return ullm_launch_kernel(qk_norm_rope_store_kernel<float>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (float*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
         positions, slot_mapping, (float*)k_cache, (float*)v_cache, num_slots, status);
   else if (dtype == ULLM_DTYPE_BF16)
-    qk_norm_rope_store_kernel<__nv_bfloat16><<<(int)blocks, QK_WARPS * 32, 0, st>>>(
+    return ullm_launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (__nv_bfloat16*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
         positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status);
   else

@@ -98,6 +98,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   __shared__ int sh_remaining;
   __shared__ int sh_result;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (long long)r * row_stride;
   const float temp = temperature != nullptr ? temperature[r] : 0.f;
@@ -262,6 +264,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab, int* __restrict__ out) {
   __shared__ ArgMax sh_arg[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const ArgMax a = block_argmax(logits + (long long)blockIdx.x * row_stride, vocab, 1.f, sh_arg);
   if (threadIdx.x == 0) out[blockIdx.x] = a.i;
 }
@@ -269,8 +273,8 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
 extern "C" int ullm_argmax(const float* logits, long long row_stride, int rows, int vocab, int* out, void* stream) {
   if (rows < 0 || vocab <= 0) return ULLM_ERR_BAD_SIZE;
   if (rows == 0) return ULLM_OK;
-  argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, out);
-  return ullm_launch_status();
+  return ullm_launch_kernel(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, row_stride,
+                            vocab, out);
 }
 
 extern "C" int ullm_sample(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
@@ -278,7 +282,6 @@ extern "C" int ullm_sample(const float* logits, long long row_stride, int rows, 
                            float* probs_out, void* stream) {
   if (rows < 0 || vocab <= 0) return ULLM_ERR_BAD_SIZE;
   if (rows == 0) return ULLM_OK;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, temperature, top_k,
-                                                                   top_p, min_p, uniform, out, probs_out);
-  return ullm_launch_status();
+  return ullm_launch_kernel(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, row_stride,
+                            vocab, temperature, top_k, top_p, min_p, uniform, out, probs_out);
 }
