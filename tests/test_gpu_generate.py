@@ -167,3 +167,27 @@ def test_long_decoding_bf16_tracks_the_plain_logits(tmp_path):
     for i, tok in enumerate(o.token_ids):
         row = lg[len(p) - 1 + i]
         assert row.max().item() - row[tok].item() <= 2 * TOL["bfloat16"] * scale, f"token {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_with_head_size_64_through_decode_graphs(tmp_path, dtype):
+    """Config D (head size 64): bfloat16 decode steps run the split tensor-core attention inside CUDA
+    graphs, float32 the general kernel; both follow the plain implementation."""
+    from helpers import TOL
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "D", dtype=dtype, max_bs=5, max_num_batched_tokens=48)
+    prompts = [random_ids(777, n, 30 + n) for n in (3, 50, 17, 130, 64)]
+    outs = llm.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=24, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 24
+        if dtype == "float32":
+            assert o.token_ids == pm.greedy_generate(p, w, cfg, 24)
+        else:
+            lg = pm.forward_logits(p + o.token_ids, w, cfg)
+            scale = lg.abs().max().item()
+            for i, tok in enumerate(o.token_ids):
+                row = lg[len(p) - 1 + i]
+                assert row.max().item() - row[tok].item() <= 2 * TOL[dtype] * scale, f"token {i}"
+    if device() != "cpu":
+        assert llm.engine.decode_graphs.replays > 0

@@ -15,8 +15,8 @@ from helpers import SHARPEN, assert_close, first_bad_row, plain_logits, random_i
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-CASES = [("A", "float32"), ("B", "float32"), ("C", "float32"), ("A", "bfloat16"), ("B", "bfloat16"), ("C", "bfloat16")]
-LENGTHS = {"A": 100, "B": 200, "C": 180}
+CASES = [(t, d) for d in ("float32", "bfloat16") for t in "ABCDE"]
+LENGTHS = {"A": 100, "B": 200, "C": 180, "D": 300, "E": 230}
 
 
 def make_runner(tmp_path, tag, dtype, num_pages, sharpen=1.0, max_requests=4, **kw):
@@ -164,7 +164,7 @@ def test_far_key_and_window_edge_with_sharp_attention(tmp_path, dtype):
     """q_norm weights scaled up make the softmax peaky, so that a single wrong
     or missing key (a far one, one at the window's edge, one on a page edge)
     moves the logits far beyond the tolerance."""
-    for tag, n in (("B", 250), ("C", 300)):
+    for tag, n in (("B", 250), ("C", 300), ("D", 400), ("E", 330)):
         runner, cfg, w, page = make_runner(tmp_path, tag, dtype, num_pages=-(-n // ALL_PAGE(tag)) + 1, sharpen=SHARPEN[dtype])
         ids = random_ids(cfg["vocab_size"], n, 31)
         ref = plain_logits(ids, w, cfg)
@@ -215,3 +215,51 @@ def test_trace_run_program(tmp_path, dtype):
     assert_close(read(1), rb[[39]], dtype, "step 1")
     assert_close(read(2), ra[[68]], dtype, "step 2")
     assert_close(read(3), ra[[69]], dtype, "step 3")
+
+
+@pytest.mark.needs_cuda
+def test_bf16_engine_uses_the_tensor_core_attention_kernels(tmp_path):
+    """With head sizes 64 and 128 in bfloat16 the engine's attention goes through the tensor-core kernels:
+    the prefill kernel for portions, the split decode kernel for one-token steps."""
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine import StepEntry
+
+    for tag in ("D", "E"):
+        runner, cfg, w, page = make_runner(tmp_path, tag, "bfloat16", num_pages=8)
+        ids = random_ids(cfg["vocab_size"], 40, 3)
+        runner.add_request("a")
+        runner.step([StepEntry("a", ids[:39], [38])])
+        assert kernels().attention_path == "prefill"
+        runner.step([StepEntry("a", ids[39:], [0])])
+        assert kernels().attention_path == "decode"
+        runner, cfg, w, page = make_runner(tmp_path, tag, "float32", num_pages=8)
+        runner.add_request("a")
+        runner.step([StepEntry("a", ids[:39], [38])])
+        assert kernels().attention_path == "generic"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_widths_two_layers(tmp_path, dtype):
+    """Two layers at the widths of Qwen3-0.6B (hidden 1024, 16 heads, 8 kv heads, head size 128, 3072
+    feed-forward, the 151,936-token vocabulary, tied head): a 48-token prompt, its last 8 tokens one by one."""
+    from ullm_b200.engine import ModelRunner
+
+    import plain_model as pm
+    from conftest import device
+
+    cfg = {
+        "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 1024, "num_attention_heads": 16,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 3072, "vocab_size": 151936,
+        "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": True,
+        "max_position_embeddings": 4096, "torch_dtype": "float32",
+    }
+    w = pm.random_weights(cfg, seed=21, std=0.02, norm_std=0.05)
+    if dtype == "bfloat16":
+        w = {n: t.to(torch.bfloat16) for n, t in w.items()}
+    d = write_model_dir(str(tmp_path / "wide"), cfg, w)
+    runner = ModelRunner(d, dtype=dtype, device=device(), page_size=16, num_pages=8, max_requests=2, max_context=128,
+                         max_step_tokens=64, poison_cache=True)
+    ids = random_ids(cfg["vocab_size"], 48, 9)
+    ref = plain_logits(ids, w, cfg)
+    got = run_cut(runner, "a", ids, [40] + [1] * 8)
+    assert_close(got, ref, dtype, "0.6B widths")

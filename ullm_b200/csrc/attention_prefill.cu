@@ -10,14 +10,17 @@
 // all heads that share them.  Row i of a block: token j0 + i / G, head kh * G +
 // i % G, position start + j0 + i / G; it sees keys max(0, pos - window + 1) ..
 // pos.  K and V tiles are gathered from the pages with cp.async into a two-stage
-// ring shared by the block's eight warps (16-byte chunks, XOR-swizzled by row);
+// ring shared by the block's four warps (16-byte chunks, XOR-swizzled by row);
+// each warp owns 32 rows, so a K or V fragment read from shared memory feeds two
+// 16-row tiles;
 // keys beyond the block's last position are zero-filled, never read.  A warp
 // skips a key tile that lies wholly above its rows' diagonal or wholly below
 // their window.
 #include "common.cuh"
 
-#define PRE_WARPS 8
-#define PRE_M 128
+#define PRE_WARPS 4
+#define PRE_ROWS_PER_WARP 32
+#define PRE_M (PRE_WARPS * PRE_ROWS_PER_WARP)
 #define PRE_N 64
 
 __device__ __forceinline__ void pre_cp_async_16(void* smem, const void* gmem, bool pred) {
@@ -63,7 +66,7 @@ struct PrefillSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(PRE_WARPS * 32)
+__global__ void __launch_bounds__(PRE_WARPS * 32, 2)
 prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, __nv_bfloat16* __restrict__ out,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_slots,
@@ -83,15 +86,17 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   const int tpt = PRE_M / G;  // tokens per block
 
   // ---- which request and which of its token tiles is this block? --------------------
+  // Blocks are numbered from the back: the last tiles of a prompt see the most keys and start first.
+  const int tile_id = (int)gridDim.x - 1 - (int)blockIdx.x;
   int r = -1, first = 0, q_len = 0, q_begin = 0;
   {
     int running = 0;
     for (int i = 0; i < num_requests; ++i) {
       const int b = cu_q[i], n = cu_q[i + 1] - b;
       const int nt = (n + tpt - 1) / tpt;
-      if ((int)blockIdx.x < running + nt) {
+      if (tile_id < running + nt) {
         r = i;
-        first = ((int)blockIdx.x - running) * tpt;
+        first = (tile_id - running) * tpt;
         q_len = n;
         q_begin = b;
         break;
@@ -103,9 +108,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   const int kvl = kv_len[r];
   const int ntok = min(tpt, q_len - first);
   const int rows_valid = ntok * G;
-  const int start = kvl - q_len;                  // position of the portion's first token
+  const int start = kvl - q_len;                     // position of the portion's first token
   const int p0 = start + first, p1 = p0 + ntok - 1;  // positions of this block's tokens
-  if (kvl <= 0 || p0 < 0) {                       // padding request: zeros
+  if (kvl <= 0 || p0 < 0) {                          // padding request: zeros
     for (int i = tid; i < rows_valid * D; i += blockDim.x) {
       const int row = i / D, d = i - row * D;
       out[((long long)(q_begin + first + row / G) * num_q + kh * G + row % G) * D + d] = __float2bfloat16_rn(0.f);
@@ -121,7 +126,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   for (int c = tid; c < PRE_M * CHUNKS; c += blockDim.x) {
     const int row = c / CHUNKS, ch = c % CHUNKS;
     const bool ok = row < rows_valid;
-    const long long off = ok ? ((long long)(q_begin + first + row / G) * q_row_stride + (long long)(kh * G + row % G) * D + ch * 8) : 0;
+    const long long off =
+        ok ? ((long long)(q_begin + first + row / G) * q_row_stride + (long long)(kh * G + row % G) * D + ch * 8) : 0;
     pre_cp_async_16(q_s + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16), q + off, ok);
   }
   pre_commit();
@@ -155,21 +161,32 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
     }
   };
 
-  // rows of this thread: warp * 16 + lane / 4 and + 8
-  const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
-  const int pos_a = row_a < rows_valid ? p0 + row_a / G : -1;
-  const int pos_b = row_b < rows_valid ? p0 + row_b / G : -1;
-  const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
-  // this warp's rows span positions [wp_min, wp_max]
-  const int w_first = warp * 16, w_last = min(rows_valid, warp * 16 + 16) - 1;
-  const bool warp_live = w_first < rows_valid;
-  const int wp_max = warp_live ? p0 + w_last / G : -1;
-  const int wp_lo = (warp_live && window > 0) ? p0 + w_first / G - window + 1 : 0;
-
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[NT_O][4];
+  // A warp owns 32 rows, two 16-row tiles; a thread's rows in tile mt: base + lane / 4 and + 8.
+  // K and V fragments are loaded once per warp and used for both tiles.
+  const int wrow = warp * PRE_ROWS_PER_WARP;
+  int pos[2][2], lo[2][2];
 #pragma unroll
-  for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = wrow + mt * 16 + (lane >> 2) + h * 8;
+      pos[mt][h] = row < rows_valid ? p0 + row / G : -1;
+      lo[mt][h] = window > 0 ? pos[mt][h] - window + 1 : 0;
+    }
+  const int w_last = min(rows_valid, wrow + PRE_ROWS_PER_WARP) - 1;
+  const bool warp_live = wrow < rows_valid;
+  const int wp_max = warp_live ? p0 + w_last / G : -1;
+  const int wp_lo = (warp_live && window > 0) ? p0 + wrow / G - window + 1 : 0;
+
+  float m[2][2], l[2][2];
+  float o[2][NT_O][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+    m[mt][0] = m[mt][1] = -INFINITY;
+    l[mt][0] = l[mt][1] = 0.f;
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) o[mt][j][0] = o[mt][j][1] = o[mt][j][2] = o[mt][j][3] = 0.f;
+  }
 
   issue(0);
   pre_commit();
@@ -182,102 +199,112 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
     if (warp_live && kb <= wp_max && kb + PRE_N - 1 >= wp_lo) {
       const unsigned char* kbuf = kv_s + (it & 1) * 2 * S::TILE_BYTES;
       const unsigned char* vbuf = kbuf + S::TILE_BYTES;
-      float sc[NT_S][4];
+      float sc[2][NT_S][4];
 #pragma unroll
-      for (int t = 0; t < NT_S; ++t) sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int t = 0; t < NT_S; ++t) sc[mt][t][0] = sc[mt][t][1] = sc[mt][t][2] = sc[mt][t][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
-        unsigned qa[4];
-        {
-          const int mat = lane >> 3, row = warp * 16 + (mat & 1) * 8 + (lane & 7), ch = 2 * kk + (mat >> 1);
-          pre_ldsm4(qa[0], qa[1], qa[2], qa[3], q_s + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
+        unsigned qa[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          const int mat = lane >> 3, row = wrow + mt * 16 + (mat & 1) * 8 + (lane & 7), ch = 2 * kk + (mat >> 1);
+          pre_ldsm4(qa[mt][0], qa[mt][1], qa[mt][2], qa[mt][3], q_s + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
         }
 #pragma unroll
         for (int t = 0; t < NT_S; t += 2) {
           const int mat = lane >> 3, row = t * 8 + (mat >> 1) * 8 + (lane & 7), ch = 2 * kk + (mat & 1);
           unsigned b0, b1, b2, b3;
           pre_ldsm4(b0, b1, b2, b3, kbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
-          pre_mma(sc[t], qa, b0, b1);
-          pre_mma(sc[t + 1], qa, b2, b3);
+          pre_mma(sc[0][t], qa[0], b0, b1);
+          pre_mma(sc[0][t + 1], qa[0], b2, b3);
+          pre_mma(sc[1][t], qa[1], b0, b1);
+          pre_mma(sc[1][t + 1], qa[1], b2, b3);
         }
       }
       // ---- mask and online softmax -----------------------------------------------------
-      float mx[2] = {m[0], m[1]};
+      float alpha[2][2];
 #pragma unroll
-      for (int t = 0; t < NT_S; ++t) {
+      for (int mt = 0; mt < 2; ++mt) {
+        float mx[2] = {m[mt][0], m[mt][1]};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1);
-          const int pos = (e >> 1) ? pos_b : pos_a;
-          const int lo = (e >> 1) ? lo_b : lo_a;
-          const float v = (key <= pos && key >= lo) ? sc[t][e] * scale_log2 : -INFINITY;
-          sc[t][e] = v;
-          mx[e >> 1] = fmaxf(mx[e >> 1], v);
-        }
-      }
+        for (int t = 0; t < NT_S; ++t) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      }
-      float alpha[2];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        alpha[i] = mx[i] == -INFINITY ? 1.f : exp2f(m[i] - mx[i]);
-        m[i] = mx[i];
-        l[i] *= alpha[i];
-      }
-#pragma unroll
-      for (int t = 0; t < NT_S; ++t)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p = m[e >> 1] == -INFINITY ? 0.f : exp2f(sc[t][e] - m[e >> 1]);
-          sc[t][e] = p;
-          l[e >> 1] += p;
+          for (int e = 0; e < 4; ++e) {
+            const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1);
+            const float v = (key <= pos[mt][e >> 1] && key >= lo[mt][e >> 1]) ? sc[mt][t][e] * scale_log2 : -INFINITY;
+            sc[mt][t][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
         }
 #pragma unroll
-      for (int j = 0; j < NT_O; ++j) {
-        o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+        for (int i = 0; i < 2; ++i) {
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+          mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+          alpha[mt][i] = mx[i] == -INFINITY ? 1.f : exp2f(m[mt][i] - mx[i]);
+          m[mt][i] = mx[i];
+          l[mt][i] *= alpha[mt][i];
+        }
+#pragma unroll
+        for (int t = 0; t < NT_S; ++t)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p = m[mt][e >> 1] == -INFINITY ? 0.f : exp2f(sc[mt][t][e] - m[mt][e >> 1]);
+            sc[mt][t][e] = p;
+            l[mt][e >> 1] += p;
+          }
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) {
+          o[mt][j][0] *= alpha[mt][0];
+          o[mt][j][1] *= alpha[mt][0];
+          o[mt][j][2] *= alpha[mt][1];
+          o[mt][j][3] *= alpha[mt][1];
+        }
       }
       // ---- O += P V ---------------------------------------------------------------------
 #pragma unroll
       for (int ks = 0; ks < PRE_N / 16; ++ks) {
-        unsigned pa[4];
-        pa[0] = pre_pack(sc[2 * ks][0], sc[2 * ks][1]);
-        pa[1] = pre_pack(sc[2 * ks][2], sc[2 * ks][3]);
-        pa[2] = pre_pack(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
-        pa[3] = pre_pack(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+        unsigned pa[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          pa[mt][0] = pre_pack(sc[mt][2 * ks][0], sc[mt][2 * ks][1]);
+          pa[mt][1] = pre_pack(sc[mt][2 * ks][2], sc[mt][2 * ks][3]);
+          pa[mt][2] = pre_pack(sc[mt][2 * ks + 1][0], sc[mt][2 * ks + 1][1]);
+          pa[mt][3] = pre_pack(sc[mt][2 * ks + 1][2], sc[mt][2 * ks + 1][3]);
+        }
 #pragma unroll
         for (int j = 0; j < NT_O; j += 2) {
           const int mat = lane >> 3, row = ks * 16 + (mat & 1) * 8 + (lane & 7), ch = j + (mat >> 1);
           unsigned b0, b1, b2, b3;
           pre_ldsm4t(b0, b1, b2, b3, vbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
-          pre_mma(o[j], pa, b0, b1);
-          pre_mma(o[j + 1], pa, b2, b3);
+          pre_mma(o[0][j], pa[0], b0, b1);
+          pre_mma(o[0][j + 1], pa[0], b2, b3);
+          pre_mma(o[1][j], pa[1], b0, b1);
+          pre_mma(o[1][j + 1], pa[1], b2, b3);
         }
       }
     }
     __syncthreads();
   }
   pre_wait<0>();
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
-    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
-  }
-  const float inv_a = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_b = l[1] > 0.f ? 1.f / l[1] : 0.f;
   const int c = (lane & 3) * 2;
-  if (row_a < rows_valid) {
-    __nv_bfloat16* op = out + ((long long)(q_begin + first + row_a / G) * num_q + kh * G + row_a % G) * D;
 #pragma unroll
-    for (int j = 0; j < NT_O; ++j)
-      *reinterpret_cast<unsigned*>(op + j * 8 + c) = pre_pack(o[j][0] * inv_a, o[j][1] * inv_a);
-  }
-  if (row_b < rows_valid) {
-    __nv_bfloat16* op = out + ((long long)(q_begin + first + row_b / G) * num_q + kh * G + row_b % G) * D;
+  for (int mt = 0; mt < 2; ++mt) {
 #pragma unroll
-    for (int j = 0; j < NT_O; ++j)
-      *reinterpret_cast<unsigned*>(op + j * 8 + c) = pre_pack(o[j][2] * inv_b, o[j][3] * inv_b);
+    for (int h = 0; h < 2; ++h) {
+      float ls = l[mt][h];
+      ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+      ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+      const float inv = ls > 0.f ? 1.f / ls : 0.f;
+      const int row = wrow + mt * 16 + (lane >> 2) + h * 8;
+      if (row < rows_valid) {
+        __nv_bfloat16* op = out + ((long long)(q_begin + first + row / G) * num_q + kh * G + row % G) * D;
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j)
+          *reinterpret_cast<unsigned*>(op + j * 8 + c) = pre_pack(o[mt][j][2 * h] * inv, o[mt][j][2 * h + 1] * inv);
+      }
+    }
   }
 }
 

@@ -102,7 +102,53 @@ __global__ void add_rmsnorm_kernel(const T* x, T* residual, const float* __restr
   for (int c = threadIdx.x; c < cols; c += blockDim.x) out[base + c] = from_f32<T>(row[c] * rstd * w[c]);
 }
 
-static int g_rmsnorm_smem_set[2] = {0, 0};
+// bf16 rows of a multiple of 8 elements on 16-byte boundaries: 8 elements per thread and step.
+// Same arithmetic and the same order of additions inside a thread's 8-element groups.
+__global__ void add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* x, __nv_bfloat16* residual, const float* __restrict__ w,
+                                          __nv_bfloat16* out, int cols, float eps) {  // out may be x
+  extern __shared__ float row[];
+  float* scratch = row + cols;
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long base = (long long)blockIdx.x * cols;
+  const int groups = cols / 8;
+  float acc = 0.f;
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + base + g * 8);
+    const __nv_bfloat16* xe = reinterpret_cast<const __nv_bfloat16*>(&xv);
+    float s[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s[k] = __bfloat162float(xe[k]);
+    if (residual != nullptr) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(residual + base + g * 8);
+      const __nv_bfloat16* re = reinterpret_cast<const __nv_bfloat16*>(&rv);
+      uint4 ov;
+      __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        s[k] += __bfloat162float(re[k]);
+        oe[k] = __float2bfloat16_rn(s[k]);
+      }
+      *reinterpret_cast<uint4*>(residual + base + g * 8) = ov;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      row[g * 8 + k] = s[k];
+      acc += s[k] * s[k];
+    }
+  }
+  const float total = block_sum(acc, scratch);
+  const float rstd = rsqrtf(total / (float)cols + eps);
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    uint4 ov;
+    __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16_rn(row[g * 8 + k] * rstd * w[g * 8 + k]);
+    *reinterpret_cast<uint4*>(out + base + g * 8) = ov;
+  }
+}
+
+static int g_rmsnorm_smem_set[3] = {0, 0, 0};
 
 template <typename T>
 static int add_rmsnorm_launch(int which, const void* x, void* residual, const float* w, void* out, int rows, int cols,
@@ -115,6 +161,19 @@ static int add_rmsnorm_launch(int which, const void* x, void* residual, const fl
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
     g_rmsnorm_smem_set[which] = 1;
+  }
+  if (sizeof(T) == 2 && cols % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+      (residual == nullptr || (uintptr_t)residual % 16 == 0)) {
+    if (smem > 48 * 1024 && !g_rmsnorm_smem_set[2]) {
+      if (cudaFuncSetAttribute(add_rmsnorm_bf16x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+          cudaSuccess)
+        return ULLM_ERR_LAUNCH;
+      g_rmsnorm_smem_set[2] = 1;
+    }
+    int threads = 32;
+    while (threads < 512 && threads * 8 < cols) threads <<= 1;
+    return ullm_launch_kernel(add_rmsnorm_bf16x8_kernel, dim3(rows), dim3(threads), smem, st,
+                              (const __nv_bfloat16*)x, (__nv_bfloat16*)residual, w, (__nv_bfloat16*)out, cols, eps);
   }
   int threads = 32;
   while (threads < 1024 && threads * 4 < cols) threads <<= 1;
