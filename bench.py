@@ -292,12 +292,125 @@ def run_probe(args) -> int:
     return 0
 
 
+def _write_reference_model(path: str, cfg: dict) -> None:
+    """A model folder the reference can open: random weights (this repo's seeded writer), and a synthetic
+    byte-level tokenizer (its LLM loads a tokenizer unconditionally; ids go in and out as integers here, the
+    tokenizer only has to exist and to know every id)."""
+    from ullm_b200.weights import write_random_model
+
+    write_random_model(path, cfg, seed=0, std=0.02, norm_std=0.0, dtype="bfloat16")
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+    cs, n = bs[:], 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    vocab = {chr(c): i for i, c in enumerate(cs)}
+    i = 0
+    while len(vocab) < cfg["vocab_size"]:
+        t = f"tok{i}"
+        i += 1
+        if t not in vocab:
+            vocab[t] = len(vocab)
+    with open(os.path.join(path, "vocab.json"), "w") as f:
+        json.dump(vocab, f)
+    with open(os.path.join(path, "merges.txt"), "w") as f:
+        f.write("#version: 0.2\n")
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "Qwen2Tokenizer", "eos_token": "tok0", "pad_token": "tok0",
+                   "model_max_length": 40960}, f)
+    with open(os.path.join(path, "config.json")) as f:
+        c = json.load(f)
+    c["model_type"] = "qwen3"
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(c, f)
+
+
 def run_reference(args) -> dict:
+    """izmttk/ullm itself, unmodified, from baseline/_ref, through its own `LLM.generate`: the same metric
+    (decode tokens per second at the given batch, requests holding 2,048 tokens) by the wall clock between
+    streamed tokens.  Requests are started one after the other, each once the one before has its first token:
+    the reference's default (asynchronous) scheduling raises on a prefill step that holds several requests
+    (ullm/core/input_batch.py:185 broadcasts [tokens] against [requests])."""
+    import asyncio
+
     ref = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref, "ullm")):
-        return {"impl": "reference", "unavailable": "izmttk/ullm is not installed under baseline/_ref (offline install failed or was not done)"}
-    return {"impl": "reference", "unavailable":
-            "izmttk/ullm needs a tokenizer and FlashInfer JIT downloads for its engine; neither is available offline"}
+    if not os.path.isdir(os.path.join(ref, "ullm", "core")):
+        return {"impl": "reference", "unavailable": "izmttk/ullm is not installed under baseline/_ref"}
+    sys.path.insert(0, ref)
+    cfg = dict(QWEN3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
+    K, W, B = args.steps, args.warmup, args.batch
+    # the reference logs to standard output, from child processes too: send descriptor 1 to standard error
+    # while it runs, so that this program's standard output holds the one JSON line only
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        import torch
+
+        tmp = tempfile.mkdtemp(prefix="ullm_ref_model_")
+        _write_reference_model(tmp, cfg)
+        from ullm import LLM, EngineConfig, SamplingParams  # the reference's public API
+
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, cfg["vocab_size"], (START_CONTEXT,), generator=g).tolist() for _ in range(B + 1)]
+        stamps: list[list[float]] = [[] for _ in prompts]
+        result: dict = {}
+
+        async def main_async():
+            llm = LLM(EngineConfig(model=tmp, gpu_memory_utilization=0.8, max_bs=max(B, 8), tp_size=1, pp_size=1,
+                                   nccl_port=29533, device_ids=[0], context_len=CONTEXT_LEN))
+            first = [asyncio.Event() for _ in prompts]
+
+            async def run(i, n_new):
+                sp = SamplingParams(temperature=1.0, top_k=1, ignore_eos=True, max_new_tokens=n_new)
+                async for _out in llm.generate(prompts[i], sp):
+                    stamps[i].append(time.perf_counter())
+                    first[i].set()
+
+            # prefill of one 2,048-token prompt: submit -> first token (after one untimed run, which also
+            # pays for the attention library's just-in-time compilation)
+            await run(B, 1)
+            stamps[B].clear()
+            t0 = time.perf_counter()
+            await run(B, 1)
+            result["prefill_s"] = stamps[B][0] - t0
+            tasks = []
+            for i in range(B):
+                tasks.append(asyncio.create_task(run(i, 2 * B + W + K + 8)))
+                await first[i].wait()
+            await asyncio.gather(*tasks)
+            await llm.shutdown()
+
+        asyncio.run(main_async())
+        # the window in which all B requests decode: from token (B + W) of the last-started request on
+        start = max(s[-(K + 1)] for s in stamps[:B])
+        end = max(s[-1] for s in stamps[:B])
+        steps_ms = (end - start) / K * 1e3
+        value = B * K / (end - start)
+        return {
+            "impl": "reference", "metric": "decode tok/s at batch 8, Qwen3-8B shape", "value": round(value, 1),
+            "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(steps_ms, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random weights, uniform random token ids)",
+            "config": {"model": "Qwen3-8B shape", "global_batch": B, "seq_len": CONTEXT_LEN,
+                       "parallelism": "single-gpu", "layers": layers, "layers_of_config": full_layers,
+                       "start_context": START_CONTEXT, "timing": "wall clock between streamed tokens"},
+            "e2e": {"value": round(value, 1), "unit": "tok/s"},
+            "prefill": {"value": round(PREFILL_TOKENS / result["prefill_s"], 1), "tokens": PREFILL_TOKENS,
+                        "ms": round(result["prefill_s"] * 1e3, 3)},
+        }
+    except BaseException as e:  # the reference kills its process tree on errors; report, do not propagate
+        msg = f"{type(e).__name__}: {e}".splitlines()[0][:300]
+        return {"impl": "reference", "unavailable": f"izmttk/ullm failed to run here: {msg}"}
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
 
 
 def main() -> int:

@@ -51,6 +51,12 @@ __device__ __forceinline__ void pre_mma(float (&c)[4], const unsigned (&a)[4], u
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x, one MUFU instruction; 2^(-inf) = 0
+__device__ __forceinline__ float pre_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pre_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -177,6 +183,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   const bool warp_live = wrow < rows_valid;
   const int wp_max = warp_live ? p0 + w_last / G : -1;
   const int wp_lo = (warp_live && window > 0) ? p0 + wrow / G - window + 1 : 0;
+  const int wp_min = p0 + wrow / G;                               // position of the warp's first row
+  const bool warp_full = wrow + PRE_ROWS_PER_WARP <= rows_valid;  // no padding rows in this warp
 
   float m[2][2], l[2][2];
   float o[2][NT_O][4];
@@ -224,36 +232,50 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
         }
       }
       // ---- mask and online softmax -----------------------------------------------------
+      // Scores stay raw (unscaled) until the exponential: p = 2^(s * scale_log2 - m), one fused
+      // multiply-add and one ex2 per element; m is kept in scaled units.  Only tiles that touch the
+      // diagonal, a window's edge or padding rows run the mask.
+      const bool need_mask = !warp_full || kb + PRE_N - 1 > wp_min || (window > 0 && kb < wp_max - window + 1);
       float alpha[2][2];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        float mx[2] = {m[mt][0], m[mt][1]};
+        if (need_mask) {
 #pragma unroll
-        for (int t = 0; t < NT_S; ++t) {
+          for (int t = 0; t < NT_S; ++t) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1);
-            const float v = (key <= pos[mt][e >> 1] && key >= lo[mt][e >> 1]) ? sc[mt][t][e] * scale_log2 : -INFINITY;
-            sc[mt][t][e] = v;
-            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            for (int e = 0; e < 4; ++e) {
+              const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1);
+              if (!(key <= pos[mt][e >> 1] && key >= lo[mt][e >> 1])) sc[mt][t][e] = -INFINITY;
+            }
           }
         }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int t = 0; t < NT_S; ++t) {
+          mx[0] = fmaxf(mx[0], fmaxf(sc[mt][t][0], sc[mt][t][1]));
+          mx[1] = fmaxf(mx[1], fmaxf(sc[mt][t][2], sc[mt][t][3]));
+        }
+        float neg_m[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
           mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-          alpha[mt][i] = mx[i] == -INFINITY ? 1.f : exp2f(m[mt][i] - mx[i]);
-          m[mt][i] = mx[i];
+          const float m_new = fmaxf(m[mt][i], mx[i] * scale_log2);
+          const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
+          alpha[mt][i] = pre_ex2(m[mt][i] - m_use);
+          m[mt][i] = m_new;
           l[mt][i] *= alpha[mt][i];
+          neg_m[i] = -m_use;
         }
 #pragma unroll
-        for (int t = 0; t < NT_S; ++t)
+        for (int t = 0; t < NT_S; ++t) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float p = m[mt][e >> 1] == -INFINITY ? 0.f : exp2f(sc[mt][t][e] - m[mt][e >> 1]);
+            const float p = pre_ex2(fmaf(sc[mt][t][e], scale_log2, neg_m[e >> 1]));
             sc[mt][t][e] = p;
             l[mt][e >> 1] += p;
           }
+        }
 #pragma unroll
         for (int j = 0; j < NT_O; ++j) {
           o[mt][j][0] *= alpha[mt][0];
