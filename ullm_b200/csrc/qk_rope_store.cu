@@ -90,6 +90,82 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
   }
 }
 
+// bfloat16, head sizes 64 and 128, full rotary: a lane owns D / 32 neighbouring elements (one 4- or 8-byte
+// load), the sum of squares is a warp reduction, and the rotation partner (D / 2 further) sits 16 lanes
+// away, so no shared memory is needed.  Same arithmetic as the general kernel.
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int num_kv, const float* __restrict__ q_w,
+                               const float* __restrict__ k_w, float eps, const float* __restrict__ cos_t,
+                               const float* __restrict__ sin_t, int max_positions, const int* __restrict__ positions,
+                               const int* __restrict__ slot_mapping, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                               long long num_slots, int* status) {
+  constexpr int VEC = D / 32;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = num_q + 2 * num_kv;
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (unit >= (long long)tokens * heads) return;
+  const int t = (int)(unit / heads);
+  const int h = (int)(unit - (long long)t * heads);
+  const bool is_q = h < num_q;
+  const bool is_k = !is_q && h < num_q + num_kv;
+  long long slot = -1;
+  if (!is_q) {
+    if (slot_mapping == nullptr) return;
+    slot = slot_mapping[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+      if (lane == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
+      return;
+    }
+  }
+  __nv_bfloat16* src = qkv + (long long)t * heads * D + (long long)h * D + lane * VEC;
+  __nv_bfloat16 raw[VEC];
+  if (VEC == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
+  else *reinterpret_cast<unsigned*>(raw) = *reinterpret_cast<const unsigned*>(src);
+  if (!is_q && !is_k) {
+    __nv_bfloat16* dst = v_cache + (slot * num_kv + (h - num_q - num_kv)) * D + lane * VEC;
+    if (VEC == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(raw);
+    else *reinterpret_cast<unsigned*>(dst) = *reinterpret_cast<const unsigned*>(raw);
+    return;
+  }
+  float y[VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    y[i] = __bfloat162float(raw[i]);
+    ss += y[i] * y[i];
+  }
+  const float* w = is_q ? q_w : k_w;
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) y[i] = y[i] * rstd * w[lane * VEC + i];
+  }
+  int pos = positions[t];
+  if (pos < 0 || pos >= max_positions) {
+    if (lane == 0) ullm_report(status, ULLM_STATUS_POSITION, t, pos);
+    pos = 0;
+  }
+  const int j0 = (lane & 15) * VEC;  // index into the half-size tables
+  const float* cr = cos_t + (long long)pos * (D / 2) + j0;
+  const float* sr = sin_t + (long long)pos * (D / 2) + j0;
+  __nv_bfloat16 o[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
+    const float c = cr[i], sn = sr[i];
+    const float v = lane < 16 ? y[i] * c - partner * sn : y[i] * c + partner * sn;
+    o[i] = __float2bfloat16_rn(v);
+  }
+  __nv_bfloat16* dst = is_q ? src : k_cache + (slot * num_kv + (h - num_q)) * D + lane * VEC;
+  if (VEC == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+  else *reinterpret_cast<unsigned*>(dst) = *reinterpret_cast<const unsigned*>(o);
+}
+
 extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
                                        const float* q_w, const float* k_w, float eps, const float* cos_t,
                                        const float* sin_t, int rotary_dim, int max_positions, const int* positions,
@@ -104,6 +180,20 @@ extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num
   const long long units = (long long)tokens * (num_q + 2 * num_kv);
   const long long blocks = (units + QK_WARPS - 1) / QK_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
+  if (dtype == ULLM_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128) &&
+      (uintptr_t)qkv % 8 == 0 && (slot_mapping == nullptr || ((uintptr_t)k_cache % 8 == 0 && (uintptr_t)v_cache % 8 == 0))) {
+    const int warps = 8;
+    const long long vblocks = (units + warps - 1) / warps;
+    if (head_dim == 128)
+      return ullm_launch_kernel(qk_norm_rope_store_bf16_kernel<128>, dim3((int)vblocks), dim3(warps * 32), 0, st,
+                                (__nv_bfloat16*)qkv, tokens, num_q, num_kv, q_w, k_w, eps, cos_t, sin_t, max_positions,
+                                positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots,
+                                status);
+    return ullm_launch_kernel(qk_norm_rope_store_bf16_kernel<64>, dim3((int)vblocks), dim3(warps * 32), 0, st,
+                              (__nv_bfloat16*)qkv, tokens, num_q, num_kv, q_w, k_w, eps, cos_t, sin_t, max_positions,
+                              positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots,
+                              status);
+  }
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<float>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (float*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
