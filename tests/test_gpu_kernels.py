@@ -403,9 +403,14 @@ def test_prefill_attention_bf16_mixed_batch(Hq, Hkv, D, page, window):
     token_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)]).cuda()
     out = torch.full((T, Hq * D), 9.0, dtype=dtype, device="cuda")
     scale = D ** -0.5
-    K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
-                        torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale,
-                        _MixedCtx(B))
+    old = K().use_tcgen05_attention
+    K().use_tcgen05_attention = False  # this test is about the mma.sync kernel
+    try:
+        K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
+                            torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale,
+                            _MixedCtx(B))
+    finally:
+        K().use_tcgen05_attention = old
     K().raise_on_status()
     assert K().attention_path == "prefill"
     ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(T, Hq, D),
@@ -453,3 +458,57 @@ def test_small_m_linear_refuses_what_it_does_not_take():
     assert not K().small_m_linear(x, w, torch.empty(4, 128, dtype=torch.bfloat16, device="cuda"))
     xf = rnd(4, 64, seed=1)
     assert not K().small_m_linear(xf, rnd(128, 64, seed=2), torch.empty(4, 128, device="cuda"))
+
+
+@pytest.mark.parametrize("Hq,Hkv,page,window", [(32, 8, 16, 0), (8, 8, 16, 0), (16, 1, 16, 0), (8, 2, 32, 0),
+                                                 (4, 2, 8, 0), (8, 2, 16, 100), (4, 1, 64, 37)])
+def test_prefill_attention_tcgen05_mixed_batch(Hq, Hkv, page, window):
+    """The tcgen05/TMA attention kernel (head size 128) on the same ragged batch as the mma.sync kernel:
+    whole prompts, portions that continue a context, two-token portions, single tokens; unwritten slots
+    of the pool hold NaN."""
+    dtype, D = torch.bfloat16, 128
+    q_lens = [1, 37, 1, 2, 64, 129, 300, 31, 200]
+    kv_lens = [150, 37, 1, 100, 130, 129, 700, 95, 200]
+    B, T = len(q_lens), sum(q_lens)
+    max_pages = -(-max(kv_lens) // page) + 1
+    pages = sum(-(-k // page) for k in kv_lens) + 3
+    g = torch.Generator().manual_seed(60)
+    perm = torch.randperm(pages, generator=g)
+    slots_of_req = torch.randperm(B + 2, generator=g)[:B].tolist()
+    bt = torch.full((B + 2, max_pages), -1, dtype=torch.int32)
+    used = 0
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    for r, kl in enumerate(kv_lens):
+        n = -(-kl // page)
+        bt[slots_of_req[r], :n] = perm[used:used + n].int()
+        for p in range(kl):
+            written[int(perm[used + p // page]) * page + p % page] = True
+        used += n
+    kp = rnd(pages, page, Hkv, D, seed=61, dtype=dtype)
+    vp = rnd(pages, page, Hkv, D, seed=62, dtype=dtype)
+    kp.view(-1, Hkv, D)[~written.cuda()] = float("nan")
+    vp.view(-1, Hkv, D)[~written.cuda()] = float("nan")
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, seed=63, dtype=dtype)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32).cuda()
+    token_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)]).cuda()
+    out = torch.full((T, Hq * D), 9.0, dtype=dtype, device="cuda")
+    scale = D ** -0.5
+    k = K()
+    old = k.use_tcgen05_attention
+    k.use_tcgen05_attention = True
+    try:
+        k.paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
+                          torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale,
+                          _MixedCtx(B))
+        torch.cuda.synchronize()
+        k.raise_on_status()
+    finally:
+        k.use_tcgen05_attention = old
+    assert k.attention_path == "prefill_tcgen05"
+    ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(T, Hq, D),
+                              torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),
+                              torch.nan_to_num(vp.float().cpu()).view(-1, Hkv, D), bt.long(), slots_of_req, q_lens,
+                              kv_lens, Hq, Hkv, D, page, window, scale)
+    got = out.view(T, Hq, D).float().cpu()
+    assert torch.isfinite(got).all()
+    close(got, ref, dtype)

@@ -229,7 +229,7 @@ def test_bf16_engine_uses_the_tensor_core_attention_kernels(tmp_path):
         ids = random_ids(cfg["vocab_size"], 40, 3)
         runner.add_request("a")
         runner.step([StepEntry("a", ids[:39], [38])])
-        assert kernels().attention_path == "prefill"
+        assert kernels().attention_path == ("prefill_tcgen05" if tag == "E" else "prefill")
         runner.step([StepEntry("a", ids[39:], [0])])
         assert kernels().attention_path == "decode"
         runner, cfg, w, page = make_runner(tmp_path, tag, "float32", num_pages=8)

@@ -311,6 +311,8 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
     if (cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
+    cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     g_decode_attr_set[which] = 1;
   }
   dim3 grid(num_splits, num_kv, batch);

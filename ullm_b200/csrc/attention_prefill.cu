@@ -87,13 +87,15 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   unsigned char* kv_s = smem + S::Q_BYTES;
   long long* slot_s = reinterpret_cast<long long*>(smem + S::Q_BYTES + 4 * S::TILE_BYTES);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kh = blockIdx.y;
+  // A 1-D grid, numbered so that consecutive blocks are the same token tile of all kv heads: the block
+  // scheduler then starts the heaviest tiles of EVERY head first (longest work first keeps the SMs level).
+  const int kh = (int)(blockIdx.x % num_kv);
   const int G = num_q / num_kv;
   const int tpt = PRE_M / G;  // tokens per block
 
   // ---- which request and which of its token tiles is this block? --------------------
   // Blocks are numbered from the back: the last tiles of a prompt see the most keys and start first.
-  const int tile_id = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int tile_id = (int)(gridDim.x / num_kv) - 1 - (int)(blockIdx.x / num_kv);
   int r = -1, first = 0, q_len = 0, q_begin = 0;
   {
     int running = 0;
@@ -342,11 +344,13 @@ static int launch_prefill(int which, const void* q, long long q_row_stride, void
     if (cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
+    cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     g_prefill_attr_set[which] = 1;
   }
   const int tpt = PRE_M / (num_q / num_kv);
   // at most ceil(tokens / tpt) + num_requests token tiles exist, however the tokens are spread
-  dim3 grid((tokens + tpt - 1) / tpt + num_requests, num_kv);
+  dim3 grid(((tokens + tpt - 1) / tpt + num_requests) * num_kv);
   return ullm_launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, block_table, max_pages, req_slots, cu_q, kv_len, num_requests, num_q, num_kv,

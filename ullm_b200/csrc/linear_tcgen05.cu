@@ -403,6 +403,8 @@ extern "C" int ullm_linear_tcgen05(const void* x, const void* w, const void* bia
     if (cudaFuncSetAttribute(linear_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
+    cudaFuncSetAttribute(linear_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     g_lin_attr_set = 1;
   }
   cudaLaunchConfig_t cfg = {};

@@ -79,6 +79,7 @@ class Kernels:
         self.pdl = False
         if os.environ.get("ULLM_B200_PDL", "0") == "1":
             self.set_pdl(True)
+        self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
         self.use_small_m_linear = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0") == "1"  # the tcgen05 kernel
         self.small_m_rows = 64
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
@@ -98,6 +99,7 @@ class Kernels:
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P],
@@ -110,6 +112,9 @@ class Kernels:
         L.ullm_decode_attention_supported.restype = c_int
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
+        L.ullm_prefill_attention_tcgen05_supported.argtypes = [I, I, I, I]
+        L.ullm_prefill_attention_tcgen05_supported.restype = c_int
+        L.ullm_prefill_attention_tcgen05_blocks_per_sm.restype = c_int
         L.ullm_set_pdl.argtypes = [I]
         L.ullm_set_pdl.restype = None
         L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
@@ -294,6 +299,17 @@ class Kernels:
             if splits > 1:
                 self.launches += 1  # the merge of the splits
             self.attention_path = "decode"
+            return
+        if (ctx is not None and qkv.dtype == torch.bfloat16 and self.use_tcgen05_attention
+                and self.lib.ullm_prefill_attention_tcgen05_supported(head_dim, num_q, num_kv, page_size)
+                and qkv.stride(0) % head_dim == 0):
+            self._check(self.lib.ullm_prefill_attention_tcgen05(
+                _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q, num_kv,
+                head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
+                f"prefill_attention_tcgen05 (head_dim {head_dim})")
+            self.attention_path = "prefill_tcgen05"
+            self.tcgen05_attention_blocks_per_sm = self.lib.ullm_prefill_attention_tcgen05_blocks_per_sm()
             return
         if (ctx is not None and qkv.dtype == torch.bfloat16
                 and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv)):
