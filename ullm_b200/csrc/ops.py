@@ -79,6 +79,7 @@ class Kernels:
         self.pdl = False
         if os.environ.get("ULLM_B200_PDL", "0") == "1":
             self.set_pdl(True)
+        self.decode_split_target = int(os.environ.get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
         self.use_small_m_linear = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0") == "1"  # the tcgen05 kernel
         self.small_m_rows = 64
@@ -289,7 +290,7 @@ class Kernels:
         if (ctx is not None and ctx.decode_only and T == ctx.num_requests and qkv.dtype == torch.bfloat16
                 and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
             # one token per request: stream the pages once, split over the key range
-            splits = max(1, min(32, -(-592 // (T * num_kv))))
+            splits = max(1, min(32, -(-self.decode_split_target // (T * num_kv))))
             scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32)
             self._check(self.lib.ullm_decode_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
