@@ -35,9 +35,14 @@ class CpuKernels:
         out.copy_(x.float() @ weight.float().t())
         return out
 
-    def embedding(self, ids, table, out):
+    def embedding(self, ids, table, out, last_tokens=None, token_req=None, req_slots=None):
         self._count("embedding")
-        out.copy_(table[ids[: out.shape[0]].long()])
+        idx = ids[: out.shape[0]].long().clone()
+        if last_tokens is not None:
+            for t in (idx < 0).nonzero().flatten().tolist():
+                b = int(token_req[t])
+                idx[t] = int(last_tokens[int(req_slots[b])]) if b >= 0 else 0
+        out.copy_(table[idx])
 
     def gather_rows(self, src, rows, out):
         self._count("gather_rows")
@@ -124,15 +129,18 @@ class CpuKernels:
     def argmax(self, logits, out):
         out[: logits.shape[0]] = torch.argmax(logits, -1).to(torch.int32)
 
-    def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None):
+    def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None, row_slots=None,
+               last_tokens=None):
         import plain_model as pm
 
         for r in range(logits.shape[0]):
             t = float(temperature[r])
             if t <= 0:
                 out[r] = int(torch.argmax(logits[r]))
-                continue
-            probs = pm.filtered_distribution(logits[r], t, int(top_k[r]), float(top_p[r]), float(min_p[r]))
-            out[r] = pm.inverse_cdf_draw(probs, float(uniform[r]))
-            if probs_out is not None:
-                probs_out[r] = probs
+            else:
+                probs = pm.filtered_distribution(logits[r], t, int(top_k[r]), float(top_p[r]), float(min_p[r]))
+                out[r] = pm.inverse_cdf_draw(probs, float(uniform[r]))
+                if probs_out is not None:
+                    probs_out[r] = probs
+            if row_slots is not None and last_tokens is not None and int(row_slots[r]) >= 0:
+                last_tokens[int(row_slots[r])] = out[r]

@@ -99,6 +99,37 @@ def test_finish_rules(tmp_path):
     assert o.prompt_token_ids == long[-40:] and len(o.token_ids) == 1
 
 
+@pytest.mark.parametrize("eager", [True, False])
+def test_steps_launched_ahead_give_the_same_tokens_as_steps_read_one_by_one(tmp_path, eager):
+    """Decode steps are launched before the tokens of the step before are read.  Requests that stop on an eos
+    token at different times (their extra step is dropped), by length, and a request that arrives late must
+    give what the synchronous engine gives, and every page comes back."""
+    from ullm_b200 import SamplingParams
+
+    prompts = [random_ids(331, n, 40 + n) for n in (3, 18, 9, 30, 5)]
+    outs = {}
+    for sync in (True, False):
+        llm, cfg, w = make_llm(tmp_path, "B", max_bs=3, max_num_batched_tokens=16, enforce_eager=eager,
+                               disable_async_scheduling=sync)
+        refs = [pm.greedy_generate(p, w, cfg, 20) for p in prompts]
+        sps = [SamplingParams(temperature=0.0, max_new_tokens=20, eos_token_id=r[k])
+               for r, k in zip(refs, (2, 19, 7, 11, 0))]
+        sps[1] = SamplingParams(temperature=0.0, max_new_tokens=13, ignore_eos=True)
+        got = llm.generate_batch(prompts, sps)
+        for p, r, sp, o in zip(prompts, refs, sps, got):
+            if sp.ignore_eos:
+                want, reason = r[:13], "LENGTH"
+            else:
+                want, reason = r[:r.index(sp.eos_token_id) + 1], "STOP"
+            assert o.token_ids == want and o.finish_reason.name == reason, f"prompt of {len(p)}, sync={sync}"
+        assert llm.engine._inflight is None
+        cache = llm.engine.runner.cache
+        cache.check_invariants()
+        assert not cache.requests, "every request gave its pages back"
+        outs[sync] = [o.token_ids for o in got]
+    assert outs[True] == outs[False]
+
+
 def test_async_generate_streams_tokens(tmp_path):
     from ullm_b200 import SamplingParams
 

@@ -107,7 +107,7 @@ class EngineConfig:
         parser.add_argument("--profile", action="store_true", help="Print per-step timing")
         parser.add_argument("--profile-dir", type=str, default="./profiles", help="Directory to save profiling results")
         parser.add_argument("--disable-async-scheduling", action="store_true",
-                            help="Accepted for compatibility; scheduling is synchronous")
+                            help="Disable asynchronous scheduling (read every step before launching the next)")
         parser.add_argument("--page-size", type=int, default=16, help="Tokens per KV page")
         parser.add_argument("--max-num-batched-tokens", type=int, default=2048, help="Token budget of one step")
         parser.add_argument("--dtype", type=str, default=None, help="bfloat16 or float32 (default: config.json's)")

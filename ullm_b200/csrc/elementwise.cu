@@ -12,12 +12,19 @@ extern "C" void ullm_set_pdl(int on) { g_ullm_pdl = on ? 1 : 0; }
 template <typename T>
 __global__ void gather_rows_kernel(const int* __restrict__ index, const T* __restrict__ src, T* __restrict__ out,
                                    int rows, int cols, long long src_stride, long long out_stride, int src_rows,
-                                   int status_code, int* status) {
+                                   int status_code, int* status, const int* __restrict__ last_tokens,
+                                   const int* __restrict__ token_req, const int* __restrict__ req_slots) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
   if (r >= rows) return;
-  const int s = index[r];
+  int s = index[r];
+  // An id of -1 stands for "the token this request sampled last": it is still on the device only
+  // (last_tokens[request slot]), because the host has launched this step before reading it.
+  if (s < 0 && last_tokens != nullptr) {
+    const int b = token_req[r];
+    s = b >= 0 ? last_tokens[req_slots[b]] : 0;
+  }
   if (s < 0 || s >= src_rows) {
     if (threadIdx.x == 0) ullm_report(status, status_code, r, s);
     for (int c = threadIdx.x; c < cols; c += blockDim.x) out[(long long)r * out_stride + c] = from_f32<T>(0.f);
@@ -37,24 +44,30 @@ __global__ void gather_rows_kernel(const int* __restrict__ index, const T* __res
 
 template <typename T>
 static int gather_rows_launch(const int* index, const void* src, void* out, int rows, int cols, long long src_stride,
-                              long long out_stride, int src_rows, int code, int* status, cudaStream_t st) {
+                              long long out_stride, int src_rows, int code, int* status, cudaStream_t st,
+                              const int* last_tokens = nullptr, const int* token_req = nullptr,
+                              const int* req_slots = nullptr) {
   if (rows == 0) return ULLM_OK;
   int threads = 256;
   if (cols * (int)sizeof(T) <= 16 * 64) threads = 64;
   return ullm_launch_kernel(gather_rows_kernel<T>, dim3(rows), dim3(threads), 0, st, index, (const T*)src, (T*)out, rows,
-                            cols, src_stride, out_stride, src_rows, code, status);
+                            cols, src_stride, out_stride, src_rows, code, status, last_tokens, token_req, req_slots);
 }
 
+// `last_tokens`, `token_req`, `req_slots` (all three or none): an id of -1 is replaced by
+// last_tokens[req_slots[token_req[row]]].
 extern "C" int ullm_embedding(int dtype, const int* ids, const void* table, void* out, int tokens, int hidden,
-                              int vocab, int* status, void* stream) {
+                              int vocab, const int* last_tokens, const int* token_req, const int* req_slots,
+                              int* status, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || hidden <= 0 || vocab <= 0) return ULLM_ERR_BAD_SIZE;
+  if (last_tokens != nullptr && (token_req == nullptr || req_slots == nullptr)) return ULLM_ERR_BAD_SIZE;
   if (dtype == ULLM_DTYPE_F32)
     return gather_rows_launch<float>(ids, table, out, tokens, hidden, hidden, hidden, vocab, ULLM_STATUS_TOKEN_ID,
-                                     status, st);
+                                     status, st, last_tokens, token_req, req_slots);
   if (dtype == ULLM_DTYPE_BF16)
     return gather_rows_launch<__nv_bfloat16>(ids, table, out, tokens, hidden, hidden, hidden, vocab,
-                                             ULLM_STATUS_TOKEN_ID, status, st);
+                                             ULLM_STATUS_TOKEN_ID, status, st, last_tokens, token_req, req_slots);
   return ULLM_ERR_BAD_DTYPE;
 }
 

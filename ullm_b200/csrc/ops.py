@@ -91,7 +91,7 @@ class Kernels:
         L = self.lib
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
         sig = {
-            "ullm_embedding": [I, P, P, P, I, I, I, P, P],
+            "ullm_embedding": [I, P, P, P, I, I, I, P, P, P, P, P],
             "ullm_gather_rows": [I, P, P, P, I, I, I, P, P],
             "ullm_add_rmsnorm": [I, P, P, P, P, I, I, F, P],
             "ullm_act_mul": [I, I, P, P, I, I, P],
@@ -103,7 +103,7 @@ class Kernels:
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
-            "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P],
+            "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -197,15 +197,21 @@ class Kernels:
         return out
 
     # -- hand-written kernels ----------------------------------------------------
-    def embedding(self, ids, table, out):
+    def embedding(self, ids, table, out, last_tokens=None, token_req=None, req_slots=None):
+        """out[t] = table[ids[t]].  With `last_tokens` (and the batch row of each token and the request
+        slot of each batch row), an id of -1 means the token that request sampled last."""
         _need(ids, "ids", torch.int32)
         _need(table, "table")
         _need(out, "out", table.dtype)
         T, H = out.shape
         if ids.numel() < T or table.shape[1] != H:
             raise KernelError(f"embedding: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
+        if last_tokens is not None:
+            for t_, n_ in ((last_tokens, "last_tokens"), (token_req, "token_req"), (req_slots, "req_slots")):
+                _need(t_, n_, torch.int32)
         self._check(self.lib.ullm_embedding(_DT[table.dtype], _ptr(ids), _ptr(table), _ptr(out), T, H,
-                                            table.shape[0], _ptr(self.status), _stream()), "embedding")
+                                            table.shape[0], _ptr(last_tokens), _ptr(token_req), _ptr(req_slots),
+                                            _ptr(self.status), _stream()), "embedding")
 
     def gather_rows(self, src, rows, out):
         _need(src, "src")
@@ -336,7 +342,8 @@ class Kernels:
             raise KernelError("argmax: logits rows must be contiguous and out must hold one id per row")
         self._check(self.lib.ullm_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
 
-    def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None):
+    def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None, row_slots=None,
+               last_tokens=None):
         _need(logits, "logits", torch.float32, contiguous=False)
         R, V = logits.shape
         if logits.stride(1) != 1:
@@ -353,4 +360,4 @@ class Kernels:
                 raise KernelError("sample: probs_out must be [rows, vocab]")
         self._check(self.lib.ullm_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k),
                                          _ptr(top_p), _ptr(min_p), _ptr(uniform), _ptr(out), _ptr(probs_out),
-                                         _stream()), "sample")
+                                         _ptr(row_slots), _ptr(last_tokens), _stream()), "sample")

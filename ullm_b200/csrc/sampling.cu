@@ -88,7 +88,8 @@ __device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
-              const float* __restrict__ uniform, int* __restrict__ out, float* __restrict__ probs_out) {
+              const float* __restrict__ uniform, int* __restrict__ out, float* __restrict__ probs_out,
+              const int* __restrict__ row_slots, int* __restrict__ last_tokens) {
   __shared__ ArgMax sh_arg[33];
   __shared__ unsigned long long sh_u64[33];
   __shared__ unsigned long long hist_mass[256];
@@ -107,7 +108,11 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
 
   if (!(temp > 0.f)) {  // greedy
     const ArgMax a = block_argmax(row, vocab, 1.f, sh_arg);
-    if (threadIdx.x == 0) out[r] = a.i;
+    if (threadIdx.x == 0) {
+      out[r] = a.i;
+      // the request's newest token stays findable on the device for a step launched before the host reads it
+      if (row_slots != nullptr && last_tokens != nullptr && row_slots[r] >= 0) last_tokens[row_slots[r]] = a.i;
+    }
     if (pout != nullptr)
       for (int i = threadIdx.x; i < vocab; i += blockDim.x) pout[i] = i == a.i ? 1.f : 0.f;
     return;
@@ -250,6 +255,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     int res = sh_result;
     if (res < 0) res = top.i;  // cannot happen: the maximum always has mass 2^40
     out[r] = res;
+    if (row_slots != nullptr && last_tokens != nullptr && row_slots[r] >= 0) last_tokens[row_slots[r]] = res;
   }
   if (pout != nullptr) {
     const float inv = total > 0ull ? 1.f / (float)total : 0.f;
@@ -279,9 +285,9 @@ extern "C" int ullm_argmax(const float* logits, long long row_stride, int rows, 
 
 extern "C" int ullm_sample(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
                            const int* top_k, const float* top_p, const float* min_p, const float* uniform, int* out,
-                           float* probs_out, void* stream) {
+                           float* probs_out, const int* row_slots, int* last_tokens, void* stream) {
   if (rows < 0 || vocab <= 0) return ULLM_ERR_BAD_SIZE;
   if (rows == 0) return ULLM_OK;
   return ullm_launch_kernel(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, row_stride,
-                            vocab, temperature, top_k, top_p, min_p, uniform, out, probs_out);
+                            vocab, temperature, top_k, top_p, min_p, uniform, out, probs_out, row_slots, last_tokens);
 }

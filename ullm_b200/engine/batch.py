@@ -82,6 +82,7 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     decode_only: bool = False
+    last_tokens: torch.Tensor | None = None  # int32 [request slots]: what each request sampled last (for id -1)
 
 
 class StepStaging:

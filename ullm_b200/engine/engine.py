@@ -46,7 +46,11 @@ class Engine:
                     cache.num_pages, cache.page_size, cache.num_pages * cache.page_size)
         self.context_len = min(config.context_len, self.runner.max_context)
         self.scheduler = Scheduler(cache, config.max_bs, config.max_num_batched_tokens, self.context_len)
-        self.sampler = Sampler(self.runner.device, max(config.max_bs, 1), self.runner.spec.vocab_size)
+        self.sampler = Sampler(self.runner.device, max(config.max_bs, 1), self.runner.spec.vocab_size,
+                               self.runner.last_tokens)
+        self._cuda = self.runner.device.type == "cuda"
+        self.async_decode = not config.disable_async_scheduling
+        self._inflight = None
         self.decode_graphs = None
         if not config.enforce_eager and self.runner.device.type == "cuda":
             from .graph import DecodeGraphs
@@ -84,73 +88,115 @@ class Engine:
         logger.debug("Aborted sequence %s.", sequence_id)
 
     def has_unfinished_sequences(self) -> bool:
-        return self.scheduler.has_unfinished_sequences()
+        return self.scheduler.has_unfinished_sequences() or self._inflight is not None
 
     # -- one step ---------------------------------------------------------------------
     def step(self) -> list[EngineStepResult]:
-        """Schedules a batch, runs it, samples, updates the sequences
-        (ullm/core/engine.py:101-119)."""
+        """Schedules a batch, runs it, samples, updates the sequences (ullm/core/engine.py:101-119).
+
+        Decode steps are launched ahead: a step that holds one token per request is started before the
+        tokens of the step before it have been read (each request's newest token stays on the device, the
+        host passes -1 for it), and the results of the step before are read while this one runs.  What the
+        reference calls asynchronous scheduling (ullm/core/engine.py:121-136) works the same way; as there, a
+        request that stops on its eos token runs one more step whose output is dropped, while stops by length
+        are known in advance and cost nothing.  `disable_async_scheduling` reads every step before the next.
+        """
+        results: list[EngineStepResult] = []
+        if self._inflight is not None and self._must_read_first():
+            results += self._collect(self._inflight)
+            self._inflight = None
         sched = self.scheduler.schedule()
-        results = [
+        results += [
             EngineStepResult(seq.seq_id, -1, True, reason, seq.num_prompt_tokens, seq.num_generated_tokens)
             for seq, reason in sched.finished
         ]
         if not sched.scheduled:
+            if self._inflight is not None:
+                results += self._collect(self._inflight)
+                self._inflight = None
             return results
         t0 = time.perf_counter() if self.profile_steps else 0.0
         sampling = [s for s in sched.scheduled if s.samples]
         params = [s.seq.sampling_params for s in sampling]
         seeds = [s.seq.seed for s in sampling]
         counters = [s.seq.num_generated_tokens for s in sampling]
+        entries = [
+            StepEntry(s.seq.seq_id, s.seq.token_ids[s.start:s.start + s.num_tokens],
+                      [s.num_tokens - 1] if s.samples else [])
+            for s in sched.scheduled
+        ]
         decode_only = all(s.num_tokens == 1 and s.samples for s in sched.scheduled)
-        if decode_only and self.decode_graphs is not None and self.decode_graphs.takes(len(sched.scheduled)):
-            entries = [StepEntry(s.seq.seq_id, [s.seq.token_ids[s.start]], [0]) for s in sched.scheduled]
-            token_ids = self.decode_graphs.run(entries, params, seeds, counters)
+        if decode_only and self.decode_graphs is not None and self.decode_graphs.takes(len(entries)):
+            handle = self.decode_graphs.launch(entries, params, seeds, counters)
         else:
-            entries = [
-                StepEntry(s.seq.seq_id, s.seq.token_ids[s.start:s.start + s.num_tokens],
-                          [s.num_tokens - 1] if s.samples else [])
-                for s in sched.scheduled
-            ]
             logits = self.runner.step(entries)
-            token_ids = []
+            handle = None
             if sampling:
-                self.sampler.stage(params, seeds, counters)
+                cache = self.runner.cache
+                self.sampler.stage(params, seeds, counters, [cache.requests[s.seq.seq_id].slot for s in sampling])
                 self.sampler.run(logits, len(sampling))
-                token_ids = self.sampler.fetch(len(sampling))
-            else:
-                torch.cuda.synchronize() if self.runner.device.type == "cuda" else None
-        self.runner.check_device_status()
-        it = iter(token_ids)
+                from ..csrc import kernels
+
+                handle = self.sampler.fetch_async(len(sampling), kernels().status if self._cuda else None)
+        # bookkeeping that needs no token value: the portion is computed, the sampled token is a placeholder
+        pending = []
         for s in sched.scheduled:
             self.scheduler.on_step_done(s)
-            if not s.samples:
-                continue
-            tok = next(it)
-            seq = s.seq
-            if seq.status != SequenceStatus.RUNNING:
-                continue
-            self.scheduler.append_token(seq, tok)
-            finished, reason = self._is_sequence_finished(seq)
-            if finished:
-                self.scheduler.finish_sequence(seq, reason)
-            results.append(EngineStepResult(seq.seq_id, tok, finished, reason, seq.num_prompt_tokens,
-                                            seq.num_generated_tokens))
-        if self.profile_steps:
-            self.step_times.append((len(sched.scheduled), sched.num_tokens, time.perf_counter() - t0))
+            if s.samples:
+                idx = self.scheduler.append_placeholder(s.seq)
+                s.seq.will_finish = self._length_reached(s.seq, idx + 1)
+                pending.append((s.seq, idx))
+        this_step = (handle, pending, len(sched.scheduled), sched.num_tokens, t0) if handle is not None else None
+        if self._inflight is not None:  # read the step before while this one runs
+            results += self._collect(self._inflight)
+            self._inflight = None
+        if this_step is not None:
+            if self.async_decode and decode_only:
+                self._inflight = this_step
+            else:
+                results += self._collect(this_step)
         return results
 
-    def _is_sequence_finished(self, seq: Sequence) -> tuple[bool, FinishReason | None]:
-        """ullm/core/engine.py:175-200, same order: eos, max_tokens (total
-        length), max_new_tokens, context length."""
+    def _must_read_first(self) -> bool:
+        """The step in flight has to be read before the next is scheduled when scheduling may preempt (a
+        preempted sequence is recomputed from its tokens, which must all be known)."""
+        cache = self.runner.cache
+        return any(s.cache is not None and not cache.can_reserve(s.cache, 2) for s in self.scheduler.running)
+
+    def _collect(self, step) -> list[EngineStepResult]:
+        handle, pending, n_seqs, n_tokens, t0 = step
+        ids, status = self.sampler.wait(handle)
+        if status:
+            self.runner.check_device_status()
+        results = []
+        for (seq, idx), tok in zip(pending, ids):
+            if seq.status != SequenceStatus.RUNNING:
+                continue  # finished or aborted meanwhile: the token is dropped
+            self.scheduler.fill_placeholder(seq, idx, tok)
+            finished, reason = self._is_sequence_finished(seq, idx + 1, tok)
+            if finished:
+                del seq.token_ids[idx + 1:]  # a step launched ahead left a placeholder behind
+                seq.num_inflight = 0
+                self.scheduler.finish_sequence(seq, reason)
+            results.append(EngineStepResult(seq.seq_id, tok, finished, reason, seq.num_prompt_tokens,
+                                            idx + 1 - seq.num_prompt_tokens))
+        if self.profile_steps:
+            self.step_times.append((n_seqs, n_tokens, time.perf_counter() - t0))
+        return results
+
+    def _length_reached(self, seq: Sequence, length: int) -> bool:
         p = seq.sampling_params
-        if seq.token_ids[-1] == p.eos_token_id and not p.ignore_eos:
+        return bool((p.max_tokens and length >= p.max_tokens)
+                    or (p.max_new_tokens and length - seq.num_prompt_tokens >= p.max_new_tokens)
+                    or length >= self.context_len)
+
+    def _is_sequence_finished(self, seq: Sequence, length: int, token: int) -> tuple[bool, FinishReason | None]:
+        """ullm/core/engine.py:175-200, same order: eos, max_tokens (total length), max_new_tokens, context
+        length.  `length`: tokens of the sequence up to and including `token`."""
+        p = seq.sampling_params
+        if token == p.eos_token_id and not p.ignore_eos:
             return True, FinishReason.STOP
-        if p.max_tokens and seq.num_tokens >= p.max_tokens:
-            return True, FinishReason.LENGTH
-        if p.max_new_tokens and seq.num_generated_tokens >= p.max_new_tokens:
-            return True, FinishReason.LENGTH
-        if seq.num_tokens >= self.context_len:
+        if self._length_reached(seq, length):
             return True, FinishReason.LENGTH
         return False, None
 

@@ -54,11 +54,21 @@ class DecodeGraphs:
 
     def run(self, entries: list[StepEntry], params, seeds, counters) -> list[int]:
         """One decode step for `entries` (one token each); returns their sampled ids."""
+        ids, status = self.sampler.wait(self.launch(entries, params, seeds, counters))
+        if status:
+            from ..csrc import kernels
+
+            kernels().raise_on_status()
+        return ids
+
+    def launch(self, entries: list[StepEntry], params, seeds, counters):
+        """Starts one decode step and the copy of its sampled ids to the host; returns a handle for
+        `sampler.wait`.  Nothing is waited for: the caller may prepare the next step meanwhile."""
         r = self.runner
         B = len(entries)
         Bp = self.padded(B)
         ctx = r.prepare(entries, pad_to=Bp, staging=r.decode_staging)
-        self.sampler.stage(params, seeds, counters)
+        self.sampler.stage(params, seeds, counters, [r.cache.requests[e.request_id].slot for e in entries])
         held = self.graphs.get(Bp)
         if held is None or held[1] != self._signature():
             # warm up eagerly (sizes every workspace buffer), then record
@@ -83,6 +93,6 @@ class DecodeGraphs:
         from ..csrc import kernels as _k
 
         _k().launches += held[2]
-        ids = self.sampler.fetch(B)
+        handle = self.sampler.fetch_async(B, _k().status)
         r.commit(entries)
-        return ids
+        return handle

@@ -98,6 +98,8 @@ class ModelRunner:
         # decode steps have few integers: a small buffer of their own keeps their copy small
         self.decode_staging = StepStaging(self.device, max_requests, max_requests, len(self.cache.groups))
         self.workspace = Workspace(self.device)
+        # per-request state of fixed size: the token each request sampled last, by request slot
+        self.last_tokens = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self._staged = torch.cuda.Event() if self.device.type == "cuda" else None
 
@@ -177,8 +179,10 @@ class ModelRunner:
             if rc.num_tokens + n > self.max_context:
                 raise ValueError(
                     f"request {e.request_id!r}: {rc.num_tokens} + {n} tokens exceed the context of {self.max_context}")
-            bad = [t for t in e.tokens if not 0 <= t < V]
-            if bad:
+            if n == 1 and e.tokens[0] == -1:
+                pass  # "the token this request sampled last": resolved on the device
+            elif min(e.tokens) < 0 or max(e.tokens) >= V:
+                bad = [t for t in e.tokens if not 0 <= t < V]
                 raise ValueError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary of {V}")
             badw = [w for w in e.want if not 0 <= w < n]
             if badw:
@@ -261,7 +265,7 @@ class ModelRunner:
             groups=groups, workspace=self.workspace,
             cu_q_host=cu, req_slots_host=[rc.slot for rc in rcs] + [0] * (B - len(rcs)),
             start_positions_host=starts + [0] * (B - len(rcs)),
-            max_q_len=max_q, max_kv_len=max_kv, decode_only=(max_q == 1),
+            max_q_len=max_q, max_kv_len=max_kv, decode_only=(max_q == 1), last_tokens=self.last_tokens,
         )
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:

@@ -62,6 +62,15 @@ class Sequence:
     finish_reason: FinishReason | None = None
     num_preemptions: int = 0
     num_cached_prompt_tokens: int = 0
+    # Steps may be launched before the host has read the token of the step before (the device keeps it):
+    # such a token is a placeholder (-1) at the end of token_ids until it is read
+    # (ullm/core/common.py:79,168-179 keeps `num_placeholder_tokens` for the same purpose).
+    num_inflight: int = 0
+    will_finish: bool = False  # a length limit is reached by a token that is still in flight
+
+    @property
+    def num_known_tokens(self) -> int:
+        return len(self.token_ids) - self.num_inflight
 
     @property
     def num_tokens(self) -> int:
@@ -136,8 +145,9 @@ class Scheduler:
 
         # 1. running requests, decoding ones first, each in order of admission
         order = [s for s in self.running if s.num_pending == 1] + [s for s in self.running if s.num_pending > 1]
+        order = [s for s in order if s.num_pending > 0]
         for seq in order:
-            if seq.status != SequenceStatus.RUNNING or budget <= 0:
+            if seq.status != SequenceStatus.RUNNING or budget <= 0 or seq.will_finish:
                 continue
             n = min(seq.num_pending, budget)
             while not self.cache.can_reserve(seq.cache, n):
@@ -238,6 +248,8 @@ class Scheduler:
         pages stay in the prefix tree), everything it generated is kept."""
         if seq.status != SequenceStatus.RUNNING:
             return
+        if seq.num_inflight:
+            raise RuntimeError("a sequence with a token in flight cannot be preempted: read its step first")
         self.running.remove(seq)
         self.cache.release(seq.cache, seq.token_ids[: seq.num_computed])
         seq.cache = None
@@ -253,12 +265,23 @@ class Scheduler:
         if seq.status != SequenceStatus.RUNNING:
             return
         seq.num_computed += sched.num_tokens
-        self.cache.publish(seq.cache, seq.token_ids[: seq.num_computed])
+        if self.cache.tree is not None:
+            self.cache.publish(seq.cache, seq.token_ids[: min(seq.num_computed, seq.num_known_tokens)])
 
     def append_token(self, seq: Sequence, token_id: int) -> None:
         """ullm/core/scheduler.py:191-202."""
         if seq.status == SequenceStatus.RUNNING:
             seq.token_ids.append(int(token_id))
+
+    def append_placeholder(self, seq: Sequence) -> int:
+        """The step that samples this sequence's next token has been launched; returns the token's index."""
+        seq.token_ids.append(-1)
+        seq.num_inflight += 1
+        return len(seq.token_ids) - 1
+
+    def fill_placeholder(self, seq: Sequence, index: int, token_id: int) -> None:
+        seq.token_ids[index] = int(token_id)
+        seq.num_inflight -= 1
 
     def finish_sequence(self, seq: Sequence, reason: FinishReason | None = None) -> None:
         """ullm/core/scheduler.py:204-222: out of the queues, pages to the prefix
@@ -269,7 +292,7 @@ class Scheduler:
             self.waiting.remove(seq)
         elif seq.status == SequenceStatus.RUNNING:
             self.running.remove(seq)
-            self.cache.release(seq.cache, seq.token_ids[: seq.num_computed])
+            self.cache.release(seq.cache, seq.token_ids[: min(seq.num_computed, seq.num_known_tokens)])
             seq.cache = None
         seq.status = SequenceStatus.FINISHED
         seq.finish_reason = reason

@@ -18,8 +18,13 @@ class TokenEmbedding(Part):
     def param_decls(self):
         return {"weight": ParamDecl((self.vocab_size, self.hidden_size))}
 
-    def forward(self, token_ids, out):
-        kernels().embedding(token_ids, self.tensors["weight"], out)
+    def forward(self, token_ids, out, ctx=None):
+        """An id of -1 stands for the token its request sampled last, when the step's context carries the
+        device array that holds those (`ctx.last_tokens`)."""
+        if ctx is not None and ctx.last_tokens is not None:
+            kernels().embedding(token_ids, self.tensors["weight"], out, ctx.last_tokens, ctx.token_req, ctx.req_slots)
+        else:
+            kernels().embedding(token_ids, self.tensors["weight"], out)
         return out
 
 

@@ -67,7 +67,7 @@ class DecoderModel(Part):
         last feed-forward output and the residual stream, before the final norm."""
         T = ctx.num_tokens
         x = ctx.workspace.get("model.hidden", T, self.spec.hidden_size, self.dtype)
-        self.embedding.forward(ctx.token_ids, x)
+        self.embedding.forward(ctx.token_ids, x, ctx)
         residual = None
         for i, e in enumerate(self.schedule):
             x, residual = self.blocks[e.layer].forward(x, residual, ctx, caches[i])
