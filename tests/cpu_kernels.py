@@ -30,6 +30,11 @@ class CpuKernels:
         out.copy_(y.to(out.dtype))
         return out
 
+    def linear_act_mul(self, x, weight, out, gate_up, act=0):
+        self.linear(x, weight, gate_up)
+        self.act_mul(gate_up, out, act)
+        return out
+
     def linear_f32_out(self, x, weight, out):
         self._count("linear")
         out.copy_(x.float() @ weight.float().t())

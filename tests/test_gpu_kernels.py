@@ -428,9 +428,9 @@ def test_prefill_attention_bf16_mixed_batch(Hq, Hkv, D, page, window):
 ])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_small_m_linear_tcgen05(M, N, K, out_dtype):
-    """The tcgen05/TMA product for decode-sized batches against a float32
-    reference, with and without bias; sizes that are no multiple of the tile
-    (128 rows, 64 columns) and K splits across a cluster."""
+    """The tcgen05/TMA product for decode-sized batches against a float32 reference, with and without bias;
+    sizes that are no multiple of the tile (128 rows, 64 columns); shapes whose tiles are shared by many blocks
+    (few tiles, long K), by two, or owned whole; the second launch finds the tile counters reset."""
     x = rnd(M, K, seed=50, dtype=torch.bfloat16)
     w = rnd(N, K, seed=51, dtype=torch.bfloat16, scale=0.05)
     bias = rnd(N, seed=52, dtype=torch.bfloat16)
@@ -447,6 +447,45 @@ def test_small_m_linear_tcgen05(M, N, K, out_dtype):
 
 def K_():
     return K()
+
+
+@pytest.mark.parametrize("M,I,Kd,act", [
+    (1, 64, 64, 0), (8, 12288, 4096, 0), (16, 200, 520, 1), (33, 331, 264, 0), (64, 1536, 2048, 0), (5, 96, 8192, 1),
+])
+def test_small_m_linear_with_fused_gate_activation(M, I, Kd, act):
+    """act(x Wg^T) * (x Wu^T) in the product's epilogue, against float32; I no multiple of 64 (the last
+    tile's gate box runs into the up rows and is masked), tiles split over many blocks (long K)."""
+    x = rnd(M, Kd, seed=60, dtype=torch.bfloat16)
+    w = rnd(2 * I, Kd, seed=61, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(2 * I, seed=62, dtype=torch.bfloat16)
+    for b in (None, bias):
+        y = x.float() @ w.float().t() + (b.float() if b is not None else 0)
+        g, u = y[:, :I], y[:, I:]
+        ref = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, I), 7.0, dtype=out_dtype, device="cuda")
+            assert K().small_m_linear(x, w, out, b, act)
+            K().raise_on_status()
+            err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+            assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+
+
+def test_small_m_linear_is_deterministic_and_independent_of_other_rows():
+    """Partial sums of a tile are added in block order whoever arrives last: repeated launches give the same
+    bits; a row's result does not depend on how many other rows the batch has."""
+    x = rnd(16, 4096, seed=70, dtype=torch.bfloat16)
+    w = rnd(512, 4096, seed=71, dtype=torch.bfloat16, scale=0.05)
+    outs = []
+    for _ in range(5):
+        out = torch.empty(16, 512, dtype=torch.float32, device="cuda")
+        assert K().small_m_linear(x, w, out)
+        outs.append(out)
+    one = torch.empty(1, 512, dtype=torch.float32, device="cuda")
+    assert K().small_m_linear(x[:1].contiguous(), w, one)
+    K().raise_on_status()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    assert torch.equal(one[0], outs[0][0])
 
 
 def test_small_m_linear_refuses_what_it_does_not_take():

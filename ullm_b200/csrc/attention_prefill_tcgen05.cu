@@ -495,6 +495,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
+  __syncwarp();  // the lanes of the single-thread role wait here for their lane 0 (the barrier counts warps)
   __syncthreads();
   if (warp == 5) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

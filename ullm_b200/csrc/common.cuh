@@ -71,6 +71,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Gate activations of a gated feed-forward (codes 0 and 1 of ullm_act_mul), in 32-bit.
+__device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
+__device__ __forceinline__ float act_gelu_tanh(float g) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * g * (1.f + tanhf(k * (g + 0.044715f * g * g * g)));
+}
+
 // True when rows of `cols` elements of T starting at `p` can be moved in
 // 16-byte pieces.
 template <typename T>

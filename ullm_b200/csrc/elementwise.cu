@@ -207,11 +207,6 @@ extern "C" int ullm_add_rmsnorm(int dtype, const void* x, void* residual, const 
 // ---------------------------------------------------------------------------
 // gated activation: out[t, i] = act(gu[t, i]) * gu[t, I + i], in 32-bit
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
-__device__ __forceinline__ float act_gelu_tanh(float g) {
-  const float k = 0.7978845608028654f;
-  return 0.5f * g * (1.f + tanhf(k * (g + 0.044715f * g * g * g)));
-}
 
 template <typename T, int ACT>
 __global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int inter) {

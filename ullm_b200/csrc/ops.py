@@ -74,6 +74,8 @@ class Kernels:
         self._declare()
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._f32_out_mm = None
+        self._lin_ws = None  # partial sums and tile counters of the tcgen05 product, made at its first use
+        self._lin_counters = None
         import os
 
         self.pdl = False
@@ -101,7 +103,7 @@ class Kernels:
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
-            "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, P, P],
+            "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -120,6 +122,7 @@ class Kernels:
         L.ullm_set_pdl.restype = None
         L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
         L.ullm_linear_tcgen05_supported.restype = c_int
+        L.ullm_linear_tcgen05_blocks.restype = c_int
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
@@ -139,26 +142,39 @@ class Kernels:
         s = self.status.tolist()
         if s[0] != 0:
             self.status.zero_()
+            if self._lin_counters is not None:
+                self._lin_counters.zero_()  # a product that gave up may have left tiles half counted
             msg = STATUS_MESSAGES.get(s[0], "status {code}").format(index=s[1], value=s[2], code=s[0])
             raise KernelError(f"a kernel refused an index: {msg}")
 
     # -- library matrix products ---------------------------------------------
-    def small_m_linear(self, x, weight, out, bias=None) -> bool:
-        """The hand-written tcgen05/TMA product for few rows (decode steps):
-        bfloat16 operands, out bfloat16 or float32.  False when the shape is not
-        one it takes (the caller then uses the library)."""
+    def small_m_linear(self, x, weight, out, bias=None, act: int | None = None) -> bool:
+        """The hand-written tcgen05/TMA product for few rows (decode steps): bfloat16 operands, out bfloat16
+        or float32; with `act` (0 silu, 1 gelu_tanh) weight stacks gate rows on up rows and out is
+        act(gate) * up.  False when the shape is not one it takes (the caller then uses the library)."""
         M, K = x.shape
         N = weight.shape[0]
+        n_out = N // 2 if act is not None else N
         if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous()
                 or not weight.is_contiguous() or not out.is_contiguous() or weight.shape[1] != K
-                or out.shape != (M, N) or out.dtype not in (torch.bfloat16, torch.float32)
-                or (bias is not None and bias.dtype != torch.bfloat16)
+                or out.shape != (M, n_out) or out.dtype not in (torch.bfloat16, torch.float32)
+                or (bias is not None and bias.dtype != torch.bfloat16) or (act is not None and N % 2)
                 or not self.lib.ullm_linear_tcgen05_supported(M, N, K)
                 or x.data_ptr() % 16 or weight.data_ptr() % 16):
             return False
-        self._check(self.lib.ullm_linear_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
-                                                 1 if out.dtype == torch.float32 else 0, _ptr(self.status),
-                                                 _stream()), f"linear_tcgen05 ({M}x{K} . {N}x{K})")
+        if self._lin_ws is None:
+            blocks = self.lib.ullm_linear_tcgen05_blocks()
+            if blocks <= 0:
+                raise KernelError("linear_tcgen05: cannot read the device's SM count")
+            self._lin_ws = torch.empty(blocks * 2 * 64 * 128, dtype=torch.float32, device="cuda")
+            self._lin_counters = torch.zeros(16384, dtype=torch.int32, device="cuda")
+        code = self.lib.ullm_linear_tcgen05(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
+                                            1 if out.dtype == torch.float32 else 0, 0 if act is None else act + 1,
+                                            _ptr(self._lin_ws), self._lin_ws.numel(), _ptr(self._lin_counters),
+                                            self._lin_counters.numel(), _ptr(self.status), _stream())
+        if code == 4:  # more tiles than counters: the library takes it
+            return False
+        self._check(code, f"linear_tcgen05 ({M}x{K} . {N}x{K})")
         return True
 
     def linear(self, x, weight, out, bias=None):
@@ -173,6 +189,19 @@ class Kernels:
             torch.addmm(bias, x, weight.t(), out=out)
         else:
             torch.mm(x, weight.t(), out=out)
+        return out
+
+    def linear_act_mul(self, x, weight, out, gate_up, act: int = 0):
+        """out[T, I] = act(x @ Wg.T) * (x @ Wu.T) for weight = [Wg; Wu] ([2 I, K]).  Few bfloat16 rows: one
+        kernel, the activation in the product's epilogue (gate and up never leave the chip).  Otherwise the
+        product into `gate_up` [T, 2 I] and the activation kernel."""
+        _need(x, "x")
+        _need(out, "out")
+        if (self.use_small_m_linear and x.shape[0] <= self.small_m_rows
+                and self.small_m_linear(x, weight, out, None, act)):
+            return out
+        self.linear(x, weight, gate_up)
+        self.act_mul(gate_up, out, act)
         return out
 
     def linear_f32_out(self, x, weight, out):

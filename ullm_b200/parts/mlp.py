@@ -41,9 +41,8 @@ class GatedMLP(FeedForward):
         T = x.shape[0]
         I = self.intermediate_size
         gu = ctx.workspace.get("mlp.gate_up", T, 2 * I, x.dtype)
-        linear(x, self.w_gate_up, gu)
         act = ctx.workspace.get("mlp.act", T, I, x.dtype)
-        kernels().act_mul(gu, act, _ACTIVATIONS[self.activation])
+        kernels().linear_act_mul(x, self.w_gate_up, act, gu, _ACTIVATIONS[self.activation])
         out = ctx.workspace.get("ffn.out", T, self.hidden_size, x.dtype)
         linear(act, self.tensors["down_proj.weight"], out)
         return out
