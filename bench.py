@@ -310,6 +310,66 @@ def run_probe(args) -> int:
     return 0
 
 
+def run_linear_probe(args) -> int:
+    """`--probe linear`: the decode step's five matrix products (Qwen3-8B sizes) alone, for `--batch` rows: the
+    vendor library against this repo's two few-row kernels, each timed as 40 launches over rotating weight copies
+    (more than L2 holds) inside one CUDA graph, so that no launch cost of the host is in the figure."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+
+    K = kernels()
+    H, I, V = QWEN3_8B["hidden_size"], QWEN3_8B["intermediate_size"], QWEN3_8B["vocab_size"]
+    qkv = (QWEN3_8B["num_attention_heads"] + 2 * QWEN3_8B["num_key_value_heads"]) * QWEN3_8B["head_dim"]
+    shapes = {"qkv": (qkv, H), "o": (H, H), "gate_up": (2 * I, H), "down": (H, I), "head": (V, H)}
+    M = args.batch
+    pk = peaks()
+
+    def timeit(fn, copies, iters=20):
+        for i in range(copies):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i % copies)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (2 * iters) * 1000.0
+
+    print(f"rows {M}; microseconds per product (weights streamed at the copy peak: 'ideal')")
+    for name, (N, Kd) in shapes.items():
+        nbytes = N * Kd * 2
+        copies = max(2, int(300e6 // nbytes) + 1)
+        ws = [torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t = {"library": timeit(lambda i: torch.mm(x, ws[i].t(), out=out), copies)}
+        if M <= 64:
+            t["tcgen05"] = timeit(lambda i: K.small_m_linear(x, ws[i], out), copies)
+        if M <= 32:
+            t["skinny"] = timeit(lambda i: K.skinny_linear(x, ws[i], out), copies)
+        line = "  ".join(f"{k} {v:7.1f} ({nbytes / v / 1e6:4.2f} TB/s)" for k, v in t.items())
+        print(f"{name:8s} N={N:6d} K={Kd:5d}  {line}  ideal {nbytes / (pk['hbm_gbs'] * 1e9) * 1e6:6.1f}")
+        if name == "gate_up":
+            act = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+            t = {"library+act_mul": timeit(lambda i: (torch.mm(x, ws[i].t(), out=out), K.act_mul(out, act, 0)), copies)}
+            if M <= 64:
+                t["tcgen05 fused"] = timeit(lambda i: K.small_m_linear(x, ws[i], act, None, 0), copies)
+            if M <= 32:
+                t["skinny fused"] = timeit(lambda i: K.skinny_linear(x, ws[i], act, None, 0), copies)
+            print("         with the gate activation:  " + "  ".join(f"{k} {v:7.1f}" for k, v in t.items()))
+        del ws
+    K.raise_on_status()
+    return 0
+
+
 def _write_reference_model(path: str, cfg: dict) -> None:
     """A model folder the reference can open: random weights (this repo's seeded writer), and a synthetic
     byte-level tokenizer (its LLM loads a tokenizer unconditionally; ids go in and out as integers here, the
@@ -439,7 +499,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--probe", default=None, choices=["decode", "prefill"], help="a few eager steps for a profiler")
+    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear"],
+                    help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -447,6 +508,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.probe == "linear":
+        return run_linear_probe(args)
     if args.probe:
         return run_probe(args)
     if args.impl == "reference":

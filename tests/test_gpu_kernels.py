@@ -470,6 +470,63 @@ def test_small_m_linear_with_fused_gate_activation(M, I, Kd, act):
             assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
 
 
+@pytest.mark.parametrize("M,N,Kd", [
+    (1, 16, 8), (1, 128, 64), (8, 4096, 4096), (8, 6144, 4096), (3, 4096, 12288), (16, 1000, 520), (17, 331, 80),
+    (32, 777, 4104), (5, 151936, 1024), (24, 130, 72), (9, 24576, 4096),
+])
+def test_skinny_linear(M, N, Kd):
+    """The streaming mma.sync product for decode-sized batches against a float32 reference, with and without
+    bias, both output types; sizes that are no multiple of the 16-row tile or of the 32-wide k chunk, k ranges
+    that divide unevenly over the warps."""
+    x = rnd(M, Kd, seed=80, dtype=torch.bfloat16)
+    w = rnd(N, Kd, seed=81, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(N, seed=82, dtype=torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for b in (None, bias):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+            assert K().skinny_linear(x, w, out, b)
+            r = ref + (b.float() if b is not None else 0)
+            err = (out.float() - r).abs().max().item() / max(r.abs().max().item(), 1e-6)
+            assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+
+
+@pytest.mark.parametrize("M,I,Kd,act", [
+    (1, 16, 32, 0), (8, 12288, 4096, 0), (16, 200, 520, 1), (31, 331, 264, 0), (5, 96, 8192, 1),
+])
+def test_skinny_linear_with_fused_gate_activation(M, I, Kd, act):
+    x = rnd(M, Kd, seed=90, dtype=torch.bfloat16)
+    w = rnd(2 * I, Kd, seed=91, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(2 * I, seed=92, dtype=torch.bfloat16)
+    for b in (None, bias):
+        y = x.float() @ w.float().t() + (b.float() if b is not None else 0)
+        g, u = y[:, :I], y[:, I:]
+        ref = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, I), 7.0, dtype=out_dtype, device="cuda")
+            assert K().skinny_linear(x, w, out, b, act)
+            err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+            assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+
+
+def test_skinny_linear_is_deterministic_and_refuses_what_it_does_not_take():
+    x = rnd(16, 4096, seed=70, dtype=torch.bfloat16)
+    w = rnd(512, 4096, seed=71, dtype=torch.bfloat16, scale=0.05)
+    outs = []
+    for _ in range(3):
+        out = torch.empty(16, 512, dtype=torch.float32, device="cuda")
+        assert K().skinny_linear(x, w, out)
+        outs.append(out)
+    one = torch.empty(1, 512, dtype=torch.float32, device="cuda")
+    assert K().skinny_linear(x[:1].contiguous(), w, one)
+    assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])
+    assert torch.equal(one[0], outs[0][0]), "a row's result does not depend on the other rows of the batch"
+    assert not K().skinny_linear(rnd(40, 64, seed=1, dtype=torch.bfloat16), rnd(128, 64, seed=2, dtype=torch.bfloat16),
+                                 torch.empty(40, 128, dtype=torch.bfloat16, device="cuda"))
+    assert not K().skinny_linear(rnd(4, 60, seed=1, dtype=torch.bfloat16), rnd(128, 60, seed=2, dtype=torch.bfloat16),
+                                 torch.empty(4, 128, dtype=torch.bfloat16, device="cuda"))
+
+
 def test_small_m_linear_is_deterministic_and_independent_of_other_rows():
     """Partial sums of a tile are added in block order whoever arrives last: repeated launches give the same
     bits; a row's result does not depend on how many other rows the batch has."""

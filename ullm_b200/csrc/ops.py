@@ -81,10 +81,16 @@ class Kernels:
         self.pdl = False
         if os.environ.get("ULLM_B200_PDL", "0") == "1":
             self.set_pdl(True)
+        if os.environ.get("ULLM_B200_MAX_SMEM_CARVEOUT", "0") == "1":
+            self.lib.ullm_set_max_smem_carveout(1)
         self.decode_split_target = int(os.environ.get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
-        self.use_small_m_linear = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0") == "1"  # the tcgen05 kernel
-        self.small_m_rows = 64
+        # few-row products: "0" the library, "skinny" the mma.sync streaming kernel (M <= 32), "tcgen05" (or "1")
+        # the stream-K tcgen05 kernel (M <= 64)
+        mode = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0")
+        self.small_m_mode = {"1": "tcgen05", "0": None, "": None}.get(mode, mode)
+        if self.small_m_mode not in (None, "tcgen05", "skinny"):
+            raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: 0, skinny or tcgen05")
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
@@ -104,6 +110,7 @@ class Kernels:
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
+            "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -120,9 +127,13 @@ class Kernels:
         L.ullm_prefill_attention_tcgen05_blocks_per_sm.restype = c_int
         L.ullm_set_pdl.argtypes = [I]
         L.ullm_set_pdl.restype = None
+        L.ullm_set_max_smem_carveout.argtypes = [I]
+        L.ullm_set_max_smem_carveout.restype = None
         L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
         L.ullm_linear_tcgen05_supported.restype = c_int
         L.ullm_linear_tcgen05_blocks.restype = c_int
+        L.ullm_linear_skinny_supported.argtypes = [I, I, I]
+        L.ullm_linear_skinny_supported.restype = c_int
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
@@ -177,13 +188,38 @@ class Kernels:
         self._check(code, f"linear_tcgen05 ({M}x{K} . {N}x{K})")
         return True
 
+    def skinny_linear(self, x, weight, out, bias=None, act: int | None = None) -> bool:
+        """The streaming mma.sync product for very few rows (M <= 32), same contract as `small_m_linear`."""
+        M, K = x.shape
+        N = weight.shape[0]
+        n_out = N // 2 if act is not None else N
+        if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous()
+                or not weight.is_contiguous() or not out.is_contiguous() or weight.shape[1] != K
+                or out.shape != (M, n_out) or out.dtype not in (torch.bfloat16, torch.float32)
+                or (bias is not None and bias.dtype != torch.bfloat16) or (act is not None and N % 2)
+                or not self.lib.ullm_linear_skinny_supported(M, N, K)
+                or x.data_ptr() % 16 or weight.data_ptr() % 16):
+            return False
+        self._check(self.lib.ullm_linear_skinny(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
+                                                1 if out.dtype == torch.float32 else 0,
+                                                0 if act is None else act + 1, _stream()),
+                    f"linear_skinny ({M}x{K} . {N}x{K})")
+        return True
+
+    def _own_linear(self, x, weight, out, bias=None, act=None) -> bool:
+        """Tries the hand-written few-row product that the mode names; False: the caller uses the library."""
+        if self.small_m_mode == "skinny":
+            return x.shape[0] <= 32 and self.skinny_linear(x, weight, out, bias, act)
+        if self.small_m_mode == "tcgen05":
+            return x.shape[0] <= 64 and self.small_m_linear(x, weight, out, bias, act)
+        return False
+
     def linear(self, x, weight, out, bias=None):
-        """out = x @ weight.T (+ bias).  Few bfloat16 rows: the hand-written
-        tcgen05 kernel.  Otherwise the vendor library's matrix product, float32
-        without any reduced-precision mode."""
+        """out = x @ weight.T (+ bias).  Few bfloat16 rows: a hand-written kernel when one is switched on.
+        Otherwise the vendor library's matrix product, float32 without any reduced-precision mode."""
         _need(x, "x")
         _need(out, "out")
-        if self.use_small_m_linear and x.shape[0] <= self.small_m_rows and self.small_m_linear(x, weight, out, bias):
+        if self._own_linear(x, weight, out, bias):
             return out
         if bias is not None:
             torch.addmm(bias, x, weight.t(), out=out)
@@ -197,8 +233,7 @@ class Kernels:
         product into `gate_up` [T, 2 I] and the activation kernel."""
         _need(x, "x")
         _need(out, "out")
-        if (self.use_small_m_linear and x.shape[0] <= self.small_m_rows
-                and self.small_m_linear(x, weight, out, None, act)):
+        if self._own_linear(x, weight, out, None, act):
             return out
         self.linear(x, weight, gate_up)
         self.act_mul(gate_up, out, act)
@@ -210,7 +245,7 @@ class Kernels:
         if x.dtype == torch.float32:
             torch.mm(x, weight.t(), out=out)
             return out
-        if self.use_small_m_linear and x.shape[0] <= self.small_m_rows and self.small_m_linear(x, weight, out):
+        if self._own_linear(x, weight, out):
             return out
         if self._f32_out_mm is None:
             try:
