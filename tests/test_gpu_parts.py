@@ -240,3 +240,159 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
     finally:
         ARCHITECTURES.pop("ToyForCausalLM", None)
         MIXERS.pop("running_mean", None)
+
+
+# ---------------------------------------------------------------------------------------
+# a toy feed-forward with routing and a toy position encoding, defined here
+# ---------------------------------------------------------------------------------------
+def _register_toy_routing():
+    from ullm_b200.config import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                                  ScheduleEntry, register_architecture)
+    from ullm_b200.parts import (FeedForward, ParamDecl, PositionEncoding, register_feed_forward,
+                                 register_position_encoding)
+
+    @register_position_encoding("slow_partial_rope")
+    class SlowPartialRope(PositionEncoding):
+        """Rotates the first `rotary_dim` elements of a head only, with positions divided by `factor`."""
+
+        def __init__(self, rotary_dim, theta, max_positions, factor=1.0):
+            super().__init__()
+            self.rotary_dim, self.theta, self.max_positions, self.factor = rotary_dim, theta, max_positions, factor
+            self._tables = {}
+
+        def build_tables(self, device):
+            inv = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim))
+            ang = (torch.arange(self.max_positions, dtype=torch.float32) / self.factor)[:, None] * inv[None, :]
+            self._tables = {"cos": ang.cos().contiguous().to(device), "sin": ang.sin().contiguous().to(device)}
+
+        def tables(self):
+            return self._tables
+
+    @register_feed_forward("top1_experts")
+    class Top1Experts(FeedForward):
+        """Each token goes to the expert whose router logit (32-bit) is largest; experts are small gated MLPs."""
+
+        def __init__(self, hidden_size, intermediate_size, num_experts):
+            super().__init__()
+            self.H, self.I, self.E = hidden_size, intermediate_size, num_experts
+
+        def param_decls(self):
+            d = {"router.weight": ParamDecl((self.E, self.H))}
+            for e in range(self.E):
+                d[f"experts.{e}.gate_up.weight"] = ParamDecl((2 * self.I, self.H))
+                d[f"experts.{e}.down.weight"] = ParamDecl((self.H, self.I))
+            return d
+
+        def forward(self, x, ctx):
+            out = ctx.workspace.get("toy.ffn_out", x.shape[0], self.H, x.dtype)
+            xf = x.float()
+            choice = (xf @ self.tensors["router.weight"].float().t()).argmax(-1)
+            for e in range(self.E):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                gu = xf[rows] @ self.tensors[f"experts.{e}.gate_up.weight"].float().t()
+                act = torch.nn.functional.silu(gu[:, :self.I]) * gu[:, self.I:]
+                out[rows] = (act.to(x.dtype).float() @ self.tensors[f"experts.{e}.down.weight"].float().t()).to(x.dtype)
+            return out
+
+    def spec(d):
+        H = d["hidden_size"]
+        norm = NormSpec("rmsnorm", H, d["eps"])
+        names = dict(mixer="mixer.", feed_forward="mlp.", mixer_norm="norm1.", feed_forward_norm="norm2.")
+        att = MixerSpec("paged_attention", dict(
+            hidden_size=H, num_heads=d["heads"], num_kv_heads=d["kv_heads"], head_dim=d["head_dim"],
+            qk_norm=NormSpec("rmsnorm", d["head_dim"], d["eps"]),
+            position=PositionSpec("slow_partial_rope", d["rotary_dim"], d["theta"], d["max_positions"],
+                                  dict(factor=d["factor"]))))
+        routed = FeedForwardSpec("top1_experts", dict(hidden_size=H, intermediate_size=d["intermediate_size"],
+                                                      num_experts=d["experts"]))
+        dense = FeedForwardSpec("gated_mlp", dict(hidden_size=H, intermediate_size=d["intermediate_size"],
+                                                  activation="silu"))
+        layers = [LayerSpec("prenorm_residual", att, routed, norm, norm, names),
+                  LayerSpec("prenorm_residual", att, dense, norm, norm, names)]
+        return ModelSpec(architecture="ToyRoutedForCausalLM", hidden_size=H, vocab_size=d["vocab_size"], layers=layers,
+                         schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm, tie_embeddings=True,
+                         max_positions=d["max_positions"], dtype="float32", embedding_name="emb.",
+                         layer_name="layers.{}.", final_norm_name="final_norm.", head_name="head.")
+
+    register_architecture("ToyRoutedForCausalLM", lambda d: d, spec)
+
+
+TOY_ROUTED = dict(architectures=["ToyRoutedForCausalLM"], hidden_size=40, intermediate_size=56, vocab_size=83, heads=4,
+                  kv_heads=1, head_dim=16, rotary_dim=8, factor=4.0, experts=3, eps=1e-5, theta=100.0, max_positions=96)
+
+
+def toy_routed_plain(ids, w, round_to=None):
+    """Whole-sequence reference of the routed toy model.  `round_to`: the engine's dtype, applied where the toy
+    feed-forward itself rounds (its activation), so that routing ties are the only thing left to differ."""
+    d = TOY_ROUTED
+    T, D, r = len(ids), d["head_dim"], d["rotary_dim"]
+    x = w["emb.weight"][torch.tensor(ids)]
+    inv = 1.0 / (d["theta"] ** (torch.arange(0, r, 2, dtype=torch.float32) / r))
+    ang = (torch.arange(T, dtype=torch.float32) / d["factor"])[:, None] * inv[None, :]
+
+    def rot(t):  # [T, heads, D]: the first r elements rotate, the rest pass
+        return torch.cat((pm.apply_rope(t[..., :r], ang.cos(), ang.sin()), t[..., r:]), -1)
+
+    for l in range(2):
+        p = f"layers.{l}."
+        h = pm.rms_norm(x, w[p + "norm1.weight"], d["eps"])
+        m = p + "mixer."
+        q = pm.rms_norm((h @ w[m + "q_proj.weight"].T).view(T, d["heads"], D), w[m + "q_norm.weight"], d["eps"])
+        k = pm.rms_norm((h @ w[m + "k_proj.weight"].T).view(T, d["kv_heads"], D), w[m + "k_norm.weight"], d["eps"])
+        v = (h @ w[m + "v_proj.weight"].T).view(T, d["kv_heads"], D)
+        a = pm.causal_attention(rot(q), rot(k), v, D ** -0.5, None)
+        x = x + a.reshape(T, -1) @ w[m + "o_proj.weight"].T
+        h = pm.rms_norm(x, w[p + "norm2.weight"], d["eps"])
+        if l == 0:
+            choice = (h @ w[p + "mlp.router.weight"].T).argmax(-1)
+            y = torch.zeros_like(h)
+            for t in range(T):
+                e = int(choice[t])
+                gu = h[t] @ w[p + f"mlp.experts.{e}.gate_up.weight"].T
+                act = pm.silu_mul(gu[:d["intermediate_size"]], gu[d["intermediate_size"]:])
+                y[t] = act @ w[p + f"mlp.experts.{e}.down.weight"].T
+            x = x + y
+        else:
+            x = x + pm.gated_mlp(h, w, p + "mlp.")
+    return pm.rms_norm(x, w["final_norm.weight"], d["eps"]) @ w["emb.weight"].T
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding_register_build_and_step():
+    """A feed-forward that routes tokens to experts and a position encoding with a constant of its own
+    (positions divided by a factor, part of the head rotated), both defined here, are registered, built from a
+    specification and stepped (whole, and in portions beside another request) without a change to the package."""
+    from ullm_b200.config import ARCHITECTURES
+    from ullm_b200.engine import ModelRunner, StepEntry
+    from ullm_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS
+
+    _register_toy_routing()
+    try:
+        r = ModelRunner(config=TOY_ROUTED, dtype="float32", device=device(), page_size=8, num_pages=24, max_requests=3,
+                        max_context=96, max_step_tokens=64, load_format="random", seed=5, random_std=0.3,
+                        random_norm_std=0.1)
+        w = {n: t.float().cpu() for n, t in r.model.all_tensors().items()}
+        a, b = random_ids(83, 50, 3), random_ids(83, 33, 4)
+        ra, rb = toy_routed_plain(a, w), toy_routed_plain(b, w)
+        r.add_request("whole")
+        lg = r.step([StepEntry("whole", a, list(range(len(a))))])
+        assert_close(lg.float().cpu(), ra, "float32", "routed toy, whole")
+        r.end_request("whole")
+        r.add_request("a")
+        r.add_request("b")
+        got_a, got_b = [], []
+        ia = ib = 0
+        for na, nb in [(9, 2), (2, 20), (25, 1), (1, 1), (13, 9)]:
+            lg = r.step([StepEntry("a", a[ia:ia + na], list(range(na))), StepEntry("b", b[ib:ib + nb], list(range(nb)))])
+            got_a.append(lg[:na].float().cpu().clone())
+            got_b.append(lg[na:].float().cpu().clone())
+            ia += na
+            ib += nb
+        r.check_device_status()
+        assert_close(torch.cat(got_a), ra[:ia], "float32", "routed toy a")
+        assert_close(torch.cat(got_b), rb[:ib], "float32", "routed toy b")
+    finally:
+        ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
+        FEED_FORWARDS.pop("top1_experts", None)
+        POSITION_ENCODINGS.pop("slow_partial_rope", None)

@@ -22,10 +22,14 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
+    """`args`: further keyword arguments of the encoding's constructor (a scaling factor, say), for kinds
+    that need more than the three constants every rotary table has."""
+
     kind: str  # key in parts.registry.POSITION_ENCODINGS ("rope", "none", ...)
     rotary_dim: int = 0
     theta: float = 10000.0
     max_positions: int = 0
+    args: dict[str, Any] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)

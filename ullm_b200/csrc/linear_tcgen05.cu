@@ -170,26 +170,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-#ifdef LIN_TIMING
-__device__ unsigned long long g_lin_times[148 * 16];
-__device__ __forceinline__ void lin_stamp(int blk, int k) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
-  g_lin_times[blk * 16 + k] = t;
-}
-#define LIN_STAMP(k) lin_stamp((int)blockIdx.x, k)
-__device__ unsigned long long g_lin_units[64];
-#define LIN_UNIT_STAMP(i, which)                                     \
-  if (blockIdx.x == 70 && (i) < 32) {                                 \
-    unsigned long long tt;                                            \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tt)::"memory"); \
-    g_lin_units[(i) * 2 + (which)] = tt;                              \
-  }
-#else
-#define LIN_STAMP(k)
-#define LIN_UNIT_STAMP(i, which)
-#endif
-
 struct LinParams {
   int M, N, K;          // rows of x, rows of W, shared dimension
   int m_pad;            // M rounded up to 16
@@ -240,7 +220,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   __shared__ uint32_t tmem_base_slot;
   __shared__ int last_flag, wait_flag[2];
   pdl_launch_dependents();
-  if (threadIdx.x == 0) LIN_STAMP(0);
   unsigned char* tiles = (unsigned char*)(((uintptr_t)lin_smem_raw + 1023) & ~(uintptr_t)1023);
   const int b_bytes = p.m_pad * 128;                         // one half of the activations' tile (a multiple of 2 KB)
   const int stage_bytes = 2 * LIN_A_HALF + 2 * b_bytes;
@@ -285,7 +264,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_d = tmem_base_slot;
   pdl_wait();  // from here on the kernel before this one is complete: x may be read, out and ws written
-  if (threadIdx.x == 0) LIN_STAMP(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -339,15 +317,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const uint32_t d = tmem_d + (uint32_t)(buf * p.m_pad);
         const int q_tail = k0 + n == p.k_blocks && p.tail_halves == 1 ? n - 1 : n;  // the unit that has one half only
         for (int q = 0; q < n; ++q) {
-          LIN_UNIT_STAMP((int)(u - u0) + q, 0);
           if (!mbar_wait_addr(full_s, phase)) {
             ullm_report(p.status, ULLM_STATUS_TIMEOUT, 2, seg);
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          LIN_UNIT_STAMP((int)(u - u0) + q, 1);
-          if (seg == 0 && q == 0) LIN_STAMP(2);
           const uint32_t b_lo = a_lo + (2 * LIN_A_HALF >> 4);
           // 16 bf16 = 32 bytes further along the swizzled row: +2 in the 16-byte address field
           umma_bf16_lo<-1>(d, a_lo, b_lo, desc_hi, idesc, q > 0 ? 1u : 0u);
@@ -368,7 +343,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (ok) umma_commit(&acc_full[buf]);  // the accumulator is complete once every MMA above is
         u += n;
         k0 = 0;
-        if (u >= u1) LIN_STAMP(3);
       }
     }
   } else {
@@ -391,7 +365,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       }
       epi_bar_sync();
       if (wait_flag[seg & 1] == 0) break;
-      if (et == 0 && u >= u1) LIN_STAMP(4);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float acc[64];
 #pragma unroll
@@ -416,7 +389,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
           if (j < p.m_pad) __stcg(&mine[j * LIN_BM + f], acc[j]);
         __threadfence();
         epi_bar_sync();
-        if (et == 0 && u >= u1) LIN_STAMP(5);
         const long long tu0 = (long long)t * p.k_blocks, tu1 = tu0 + p.k_blocks - 1;  // the tile's first, last unit
         const long long b_first = ((tu0 + 1) * G + p.units - 1) / p.units - 1;         // the blocks they belong to
         const long long b_last = ((tu1 + 1) * G + p.units - 1) / p.units - 1;
@@ -429,7 +401,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
         epi_bar_sync();
         finish = last_flag != 0;
-        if (et == 0 && u >= u1) LIN_STAMP(6);
         if (finish) {
           // Parts in block order (the same sum whoever is last), four parts' loads in flight at a time.
           const float* base = p.ws + f;
@@ -463,7 +434,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
           }
         }
       }
-      if (et == 0 && u >= u1) LIN_STAMP(7);
       if (p.act == 0) {
         const int col = t * LIN_BM + f;
         if (finish && col < p.N) {
@@ -506,9 +476,6 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   __syncwarp();  // the lanes of the two single-thread roles wait here for their lane 0
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (threadIdx.x == 0) LIN_STAMP(8);
-  if (threadIdx.x == 64) LIN_STAMP(9);
-  if (threadIdx.x == 32) LIN_STAMP(10);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");

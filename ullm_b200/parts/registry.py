@@ -46,7 +46,7 @@ def build_norm(spec):
 
 def build_position_encoding(spec):
     return _lookup(POSITION_ENCODINGS, "position encoding", spec.kind)(
-        rotary_dim=spec.rotary_dim, theta=spec.theta, max_positions=spec.max_positions
+        rotary_dim=spec.rotary_dim, theta=spec.theta, max_positions=spec.max_positions, **spec.args
     )
 
 
