@@ -100,11 +100,14 @@ def test_finish_rules(tmp_path):
 
 
 @pytest.mark.parametrize("eager", [True, False])
-def test_steps_launched_ahead_give_the_same_tokens_as_steps_read_one_by_one(tmp_path, eager):
+def test_steps_launched_ahead_give_the_same_tokens_as_steps_read_one_by_one(tmp_path, eager, monkeypatch):
     """Decode steps are launched before the tokens of the step before are read.  Requests that stop on an eos
     token at different times (their extra step is dropped), by length, and a request that arrives late must
-    give what the synchronous engine gives, and every page comes back."""
+    give what the synchronous engine gives, and every page comes back.  Graphs for batches of 1, 2 and 3 are
+    recorded in mid-stream, from steps whose input token is still on the device only."""
     from ullm_b200 import SamplingParams
+
+    monkeypatch.setenv("ULLM_B200_MIN_GRAPH_BATCH", "1")
 
     prompts = [random_ids(331, n, 40 + n) for n in (3, 18, 9, 30, 5)]
     outs = {}

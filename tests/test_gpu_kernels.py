@@ -307,10 +307,11 @@ class _DecodeCtx:
     (32, 8, 128, 16, 100), (4, 2, 64, 4, 37), (9, 3, 128, 1, 0),
 ])
 @pytest.mark.parametrize("batch", [1, 3, 40])
-def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch):
-    """The split tensor-core decode kernel against the plain reference: contexts
-    of 1 token, around page and tile edges, and long ones; padding rows (length
-    0) give zeros."""
+@pytest.mark.parametrize("balanced", [False, True])
+def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, balanced):
+    """The two split tensor-core decode kernels (every request split alike; the whole batch's keys cut evenly
+    over the blocks) against the plain reference: contexts of 1 token, around page and tile edges, and long
+    ones, ragged within a batch; padding rows (length 0) give zeros."""
     dtype = torch.bfloat16
     lens = [1, 15, 16, 17, 63, 64, 65, 300, 1000, 2049, 0, 33, 129, 511, 77, 5]
     kv_lens = [lens[(i * 7 + batch) % len(lens)] for i in range(batch)]
@@ -343,11 +344,16 @@ def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch):
     out = torch.full((batch, Hq * D), 9.0, dtype=dtype, device="cuda")
     scale = D ** -0.5
     ctx = _DecodeCtx(batch)
-    before = K().launches
-    K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
-                        torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale, ctx)
+    old = K().use_balanced_decode
+    K().use_balanced_decode = balanced
+    try:
+        K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
+                            torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window,
+                            scale, ctx)
+    finally:
+        K().use_balanced_decode = old
     K().raise_on_status()
-    assert "attn.decode_scratch" in ctx.workspace.buffers, "the decode kernel was not chosen"
+    assert K().attention_path == ("decode_balanced" if balanced else "decode")
     live = [r for r, kl in enumerate(kv_lens) if kl > 0]
     ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(batch, Hq, D)[live],
                               torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),

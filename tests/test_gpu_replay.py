@@ -238,6 +238,33 @@ def test_bf16_engine_uses_the_tensor_core_attention_kernels(tmp_path):
         assert kernels().attention_path == "generic"
 
 
+@pytest.mark.needs_cuda
+@pytest.mark.parametrize("tag", ["D", "E"])
+def test_decode_batches_of_very_unequal_lengths_take_the_balanced_attention_kernel(tmp_path, tag):
+    """One request of 300 tokens beside three of about ten: the step says so (`ragged`), the decode attention
+    is the kernel that cuts the batch's keys evenly over the warps, and the logits of eight decode steps follow
+    the plain implementation for every request (E has a sliding window on its last layer)."""
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine import StepEntry
+
+    runner, cfg, w, page = make_runner(tmp_path, tag, "bfloat16", num_pages=40)
+    V = cfg["vocab_size"]
+    lens = {"long": 300, "s1": 5, "s2": 9, "s3": 14}
+    ids = {r: random_ids(V, n + 8, 40 + n) for r, n in lens.items()}
+    refs = {r: plain_logits(ids[r], w, cfg) for r in lens}
+    for r, n in lens.items():
+        runner.add_request(r)
+        for at in range(0, n, 64):
+            runner.step([StepEntry(r, ids[r][at:min(n, at + 64)], [])])
+    for k in range(8):
+        ctx_entries = [StepEntry(r, [ids[r][n + k]], [0]) for r, n in lens.items()]
+        lg = runner.step(ctx_entries)
+        assert kernels().attention_path == "decode_balanced"
+        for row, (r, n) in enumerate(lens.items()):
+            assert_close(lg[row:row + 1].float().cpu(), refs[r][[n + k]], "bfloat16", f"{r}, decode step {k}")
+    runner.check_device_status()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_real_widths_two_layers(tmp_path, dtype):
     """Two layers at the widths of Qwen3-0.6B (hidden 1024, 16 heads, 8 kv heads, head size 128, 3072

@@ -85,6 +85,11 @@ class Kernels:
             self.lib.ullm_set_max_smem_carveout(1)
         self.decode_split_target = int(os.environ.get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
+        # decode attention: the batch's keys cut evenly over the warps (True), every request split alike (False),
+        # or "auto": the first for batches of very unequal lengths (the step context says so), else the second
+        mode = os.environ.get("ULLM_B200_DECODE_BALANCED", "auto")
+        self.use_balanced_decode = {"1": True, "0": False}.get(mode, "auto")
+        self._decb = {}  # (head_dim, heads per kv head) -> (partials, prefix) of the balanced decode attention
         # few-row products: "0" the library, "skinny" the mma.sync streaming kernel (M <= 32), "tcgen05" (or "1")
         # the stream-K tcgen05 kernel (M <= 64)
         mode = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0")
@@ -107,6 +112,7 @@ class Kernels:
             "ullm_qk_norm_rope_store": [I, P, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, LL, P, P],
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
+            "ullm_decode_attention_balanced": [P, LL, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
@@ -120,6 +126,10 @@ class Kernels:
             fn.restype = c_int
         L.ullm_decode_attention_supported.argtypes = [I, I, I]
         L.ullm_decode_attention_supported.restype = c_int
+        L.ullm_decode_attention_balanced_supported.argtypes = [I, I, I, I, I]
+        L.ullm_decode_attention_balanced_supported.restype = c_int
+        L.ullm_decode_attention_balanced_scratch_floats.argtypes = [I, I]
+        L.ullm_decode_attention_balanced_scratch_floats.restype = c_longlong
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
         L.ullm_prefill_attention_tcgen05_supported.argtypes = [I, I, I, I]
@@ -359,7 +369,26 @@ class Kernels:
         num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
         if (ctx is not None and ctx.decode_only and T == ctx.num_requests and qkv.dtype == torch.bfloat16
                 and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
-            # one token per request: stream the pages once, split over the key range
+            # one token per request: stream the pages once
+            balanced = getattr(ctx, "ragged", False) if self.use_balanced_decode == "auto" else self.use_balanced_decode
+            if balanced and self.lib.ullm_decode_attention_balanced_supported(
+                    head_dim, num_q, num_kv, T, page_size):
+                key = (head_dim, num_q // num_kv)
+                if key not in self._decb:
+                    n = self.lib.ullm_decode_attention_balanced_scratch_floats(*key)
+                    if n <= 0:
+                        raise KernelError("decode_attention_balanced: cannot size its grid on this device")
+                    self._decb[key] = (torch.empty(n, dtype=torch.float32, device="cuda"),
+                                       torch.zeros(513, dtype=torch.int32, device="cuda"))
+                part, prefix = self._decb[key]
+                self._check(self.lib.ullm_decode_attention_balanced(
+                    _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                    _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(part), _ptr(prefix), T, num_q, num_kv, head_dim,
+                    page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
+                    f"decode_attention_balanced (head_dim {head_dim})")
+                self.launches += 1  # the merge of the shared pairs
+                self.attention_path = "decode_balanced"
+                return
             splits = max(1, min(32, -(-self.decode_split_target // (T * num_kv))))
             scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32)
             self._check(self.lib.ullm_decode_attention(

@@ -83,6 +83,8 @@ class StepContext:
     max_kv_len: int = 1
     decode_only: bool = False
     last_tokens: torch.Tensor | None = None  # int32 [request slots]: what each request sampled last (for id -1)
+    # decode steps: lengths differ so much that the longest request, times the batch, is well above the sum
+    ragged: bool = False
 
 
 class StepStaging:

@@ -7,8 +7,8 @@ side of a decode step: embedding to logits AND the sampling kernel.  The step's
 integers and the sampling parameters live in fixed device buffers that are
 refreshed by two small copies before each replay; block tables are on the
 device already.  Graphs are captured on first use of a batch size, from the
-live batch itself (a decode step is idempotent: it writes the same keys and
-values and the same token again).
+live batch itself: that step runs eagerly, is recorded, and the recording is
+replayed from the next step of that size on.
 """
 
 from __future__ import annotations
@@ -38,7 +38,9 @@ class DecodeGraphs:
         import os
 
         self.sizes = graph_batch_sizes(max_bs, int(os.environ.get("ULLM_B200_MIN_GRAPH_BATCH", "16")))
-        self.graphs: dict[int, tuple] = {}  # size -> (graph, signature, kernels recorded)
+        # (size, ragged) -> (graph, signature, kernels recorded): batches of very unequal lengths replay a
+        # graph that was recorded with the batch-balanced attention kernel
+        self.graphs: dict[tuple, tuple] = {}
         self.pool = None
         self.replays = 0
 
@@ -69,15 +71,19 @@ class DecodeGraphs:
         Bp = self.padded(B)
         ctx = r.prepare(entries, pad_to=Bp, staging=r.decode_staging)
         self.sampler.stage(params, seeds, counters, [r.cache.requests[e.request_id].slot for e in entries])
-        held = self.graphs.get(Bp)
+        key = (Bp, bool(ctx.ragged))
+        held = self.graphs.get(key)
+        from ..csrc import kernels
+
         if held is None or held[1] != self._signature():
-            # warm up eagerly (sizes every workspace buffer), then record
+            # This step runs eagerly (which also sizes every workspace buffer) and is then recorded for the
+            # steps to come.  The recording executes nothing, and the step is not replayed on top of its eager
+            # run: with its input token taken from `last_tokens`, which the sampling kernel has just
+            # overwritten, a second execution would be a different step.
             logits = r.run_model(ctx)
             self.sampler.run(logits, Bp)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            from ..csrc import kernels
-
             before = kernels().launches
             with torch.cuda.graph(g, pool=self.pool):
                 logits = r.run_model(ctx)
@@ -86,13 +92,12 @@ class DecodeGraphs:
             kernels().launches = before  # recording launched nothing
             if self.pool is None:
                 self.pool = g.pool()
-            self.graphs[Bp] = (g, self._signature(), captured)
-            held = self.graphs[Bp]
-        held[0].replay()
-        self.replays += 1
-        from ..csrc import kernels as _k
-
-        _k().launches += held[2]
+            self.graphs[key] = (g, self._signature(), captured)
+        else:
+            held[0].replay()
+            self.replays += 1
+            kernels().launches += held[2]
+        _k = kernels
         handle = self.sampler.fetch_async(B, _k().status)
         r.commit(entries)
         return handle
