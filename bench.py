@@ -370,6 +370,79 @@ def run_linear_probe(args) -> int:
     return 0
 
 
+def run_decode_attention_probe(args) -> int:
+    """`--probe decode-attention`: the two bfloat16 decode attention kernels alone (Qwen3-8B head sizes, pages of
+    16 tokens) on batches of equal and of very unequal lengths; microseconds per call, launched eagerly (about
+    10 us of launch cost are in every figure), L2 flushed before each call."""
+    import random
+
+    import torch
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine.batch import Workspace
+
+    K = kernels()
+    Hq, Hkv, D, page = (QWEN3_8B["num_attention_heads"], QWEN3_8B["num_key_value_heads"], QWEN3_8B["head_dim"],
+                        PAGE_SIZE)
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    class Ctx:
+        pass
+
+    def case(name, lens):
+        B = len(lens)
+        per = [-(-n // page) for n in lens]
+        pages = sum(per) + 4
+        kp = torch.randn(pages, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+        vp = torch.randn(pages, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+        bt = torch.full((B, max(per)), -1, dtype=torch.int32)
+        o = 0
+        for i, n in enumerate(per):
+            bt[i, :n] = torch.arange(o, o + n, dtype=torch.int32)
+            o += n
+        bt = bt.cuda()
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+        ctx = Ctx()
+        ctx.decode_only, ctx.num_requests, ctx.max_q_len = True, B, 1
+        ctx.workspace = Workspace(torch.device("cuda"))
+        slots = torch.arange(B, dtype=torch.int32, device="cuda")
+        cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        kvl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        res, outs = {}, []
+        for balanced in (False, True):
+            K.use_balanced_decode = balanced
+            out = torch.empty(B, Hq * D, device="cuda", dtype=torch.bfloat16)
+            ts = []
+            for _ in range(7):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                K.paged_attention(qkv, out, kp, vp, bt, slots, cu, kvl, slots, Hq, Hkv, D, page, 0, D ** -0.5, ctx)
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1000)
+            res[balanced] = statistics.median(ts[2:])
+            outs.append(out.float())
+        mb = sum(lens) * Hkv * D * 2 * 2 / 1e6
+        print(f"{name:28s} K+V {mb:7.1f} MB  at the copy peak {mb / pk['hbm_gbs'] * 1e3:6.1f} us   "
+              f"per-request splits {res[False]:7.1f} us   batch-balanced {res[True]:7.1f} us   "
+              f"(largest difference of the outputs {(outs[0] - outs[1]).abs().max().item():.1e})")
+
+    random.seed(1)
+    case("8 x 2048", [2048] * 8)
+    case("64 x 2048", [2048] * 64)
+    case("1 x 2048", [2048])
+    case("4 x 8192", [8192] * 4)
+    case("128 x 1024", [1024] * 128)
+    case("1 x 16384 + 15 x 256", [16384] + [256] * 15)
+    case("1 x 32768 + 63 x 512", [32768] + [512] * 63)
+    case("64 x uniform(64..4096)", [random.randint(64, 4096) for _ in range(64)])
+    case("32 x uniform(16..8192)", [random.randint(16, 8192) for _ in range(32)])
+    K.raise_on_status()
+    return 0
+
+
 def _write_reference_model(path: str, cfg: dict) -> None:
     """A model folder the reference can open: random weights (this repo's seeded writer), and a synthetic
     byte-level tokenizer (its LLM loads a tokenizer unconditionally; ids go in and out as integers here, the
@@ -499,7 +572,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear"],
+    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     args = ap.parse_args()
@@ -510,6 +583,8 @@ def main() -> int:
         args.warmup = 3
     if args.probe == "linear":
         return run_linear_probe(args)
+    if args.probe == "decode-attention":
+        return run_decode_attention_probe(args)
     if args.probe:
         return run_probe(args)
     if args.impl == "reference":
