@@ -92,8 +92,10 @@ __global__ void __launch_bounds__(SK_THREADS) linear_skinny_kernel(const SkParam
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[r][n][i] = 0.f;
 
-  uint4 a[SK_UNROLL][RT * 2];
-  auto load_a = [&](int c) {
+  // Two sets of weight registers: while the tensor instructions work through one, the loads of the next
+  // SK_UNROLL chunks are already in flight into the other.
+  uint4 a0[SK_UNROLL][RT * 2], a1[SK_UNROLL][RT * 2];
+  auto load_a = [&](uint4 (&a)[SK_UNROLL][RT * 2], int c) {
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; ++u) {
       const int k = (c + u) * 32 + t * 8;
@@ -103,9 +105,7 @@ __global__ void __launch_bounds__(SK_THREADS) linear_skinny_kernel(const SkParam
         a[u][q] = in && wok[q] ? sk_ld_stream(wrow[q] + (long long)(c + u) * 32) : make_uint4(0, 0, 0, 0);
     }
   };
-  if (c_begin < c_end) load_a(c_begin);
-  pdl_wait();  // x is the output of the kernel before this one
-  for (int c = c_begin; c < c_end;) {
+  auto consume = [&](const uint4 (&a)[SK_UNROLL][RT * 2], int c) {
     uint4 b[SK_UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; ++u) {
@@ -128,8 +128,15 @@ __global__ void __launch_bounds__(SK_THREADS) linear_skinny_kernel(const SkParam
         }
       }
     }
-    c += SK_UNROLL;
-    if (c < c_end) load_a(c);
+  };
+  if (c_begin < c_end) load_a(a0, c_begin);
+  pdl_wait();  // x is the output of the kernel before this one
+  for (int c = c_begin; c < c_end; c += 2 * SK_UNROLL) {
+    if (c + SK_UNROLL < c_end) load_a(a1, c + SK_UNROLL);
+    consume(a0, c);
+    if (c + SK_UNROLL >= c_end) break;
+    if (c + 2 * SK_UNROLL < c_end) load_a(a0, c + 2 * SK_UNROLL);
+    consume(a1, c + SK_UNROLL);
   }
 
   // partial sums of the 8 warps meet in shared memory: c0, c1 = [row g][cols 2t, 2t + 1], c2, c3 = [row g + 8][..]
