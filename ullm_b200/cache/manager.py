@@ -28,6 +28,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..parts.base import CacheNeed, StateNeed
@@ -223,7 +224,12 @@ class CacheManager:
         """Flat slots (page * page_size + offset) of the next n_new tokens."""
         ps = self.page_size
         pages = rc.pages[group]
-        return [pages[p // ps] * ps + p % ps for p in range(rc.num_tokens, rc.num_tokens + n_new)]
+        if n_new <= 16:
+            return [pages[p // ps] * ps + p % ps for p in range(rc.num_tokens, rc.num_tokens + n_new)]
+        pos = np.arange(rc.num_tokens, rc.num_tokens + n_new, dtype=np.int64)
+        first = rc.num_tokens // ps
+        held = np.asarray(pages[first:(rc.num_tokens + n_new - 1) // ps + 1], dtype=np.int64)
+        return held[pos // ps - first] * ps + pos % ps
 
     def commit(self, rc: RequestCache, n_new: int) -> None:
         """The step wrote n_new tokens.  Pages of windowed groups that no later

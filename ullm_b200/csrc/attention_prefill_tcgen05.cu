@@ -27,6 +27,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "tma_host.cuh"
 
 #define ULLM_STATUS_TIMEOUT 6
 #define TA_ROWS 128
@@ -506,22 +507,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*TaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static TaEncodeFn ta_encode() {
-  static TaEncodeFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (TaEncodeFn)ptr;
-  }
-  return fn;
-}
+typedef UllmTmaEncodeFn TaEncodeFn;
+static TaEncodeFn ta_encode() { return ullm_tma_encode(); }
 
 struct TaKey {
   const void* ptr;
@@ -565,28 +552,7 @@ static bool ta_map_q(const void* q, long long tokens, long long row_stride_elems
 }
 // K or V pages [pages, page_size, kv heads, 128]; a box is one page of one head, 64 columns
 static bool ta_map_kv(const void* cache, long long pages, int page_size, int num_kv, CUtensorMap* out) {
-  std::lock_guard<std::mutex> lock(g_ta_mutex);
-  TaKey key{cache, pages, page_size, num_kv};
-  auto it = g_ta_maps.find(key);
-  if (it != g_ta_maps.end()) {
-    *out = it->second;
-    return true;
-  }
-  TaEncodeFn enc = ta_encode();
-  if (enc == nullptr) return false;
-  cuuint64_t dims[4] = {TA_D, (cuuint64_t)num_kv, (cuuint64_t)page_size, (cuuint64_t)pages};
-  cuuint64_t strides[3] = {TA_D * 2, (cuuint64_t)num_kv * TA_D * 2, (cuuint64_t)page_size * num_kv * TA_D * 2};
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)page_size, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUtensorMap m;
-  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, estr,
-          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
-  if (g_ta_maps.size() > 4096) g_ta_maps.clear();
-  g_ta_maps[key] = m;
-  *out = m;
-  return true;
+  return ullm_tma_map_kv(cache, pages, page_size, num_kv, TA_D, page_size, out);
 }
 
 // bfloat16, head size 128, a power-of-two number (<= 16) of query heads per kv head, pages of 8, 16, 32 or 64 tokens

@@ -13,6 +13,7 @@ scheduler (engine.scheduler) or a replayed trace (bin/trace_run) does.
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages, RequestCache
@@ -173,7 +174,8 @@ class ModelRunner:
         V = self.spec.vocab_size
         rcs = []
         seen = set()
-        for e in entries:
+        orig_entries = entries
+        for e in list(entries):
             if e.request_id in seen:
                 raise ValueError(f"request {e.request_id!r} appears twice in one step")
             seen.add(e.request_id)
@@ -188,9 +190,19 @@ class ModelRunner:
                     f"request {e.request_id!r}: {rc.num_tokens} + {n} tokens exceed the context of {self.max_context}")
             if n == 1 and e.tokens[0] == -1:
                 pass  # "the token this request sampled last": resolved on the device
-            elif min(e.tokens) < 0 or max(e.tokens) >= V:
-                bad = [t for t in e.tokens if not 0 <= t < V]
-                raise ValueError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary of {V}")
+            elif n <= 16:
+                if min(e.tokens) < 0 or max(e.tokens) >= V:
+                    bad = [t for t in e.tokens if not 0 <= t < V]
+                    raise ValueError(f"request {e.request_id!r}: token id {bad[0]} is outside the vocabulary of {V}")
+            else:
+                arr = np.asarray(e.tokens, dtype=np.int64)
+                if int(arr.min()) < 0 or int(arr.max()) >= V:
+                    bad = arr[(arr < 0) | (arr >= V)]
+                    raise ValueError(
+                        f"request {e.request_id!r}: token id {int(bad[0])} is outside the vocabulary of {V}")
+                e = StepEntry(e.request_id, arr, e.want)  # the array is what gets copied below
+                entries = entries if entries is not orig_entries else list(orig_entries)
+                entries[len(rcs)] = e
             badw = [w for w in e.want if not 0 <= w < n]
             if badw:
                 raise ValueError(f"request {e.request_id!r}: wanted place {badw[0]} is outside its {n} tokens")
@@ -222,7 +234,7 @@ class ModelRunner:
             start = rc.num_tokens
             starts.append(start)
             h[o_ids + t:o_ids + t + n] = e.tokens
-            h[o_pos + t:o_pos + t + n] = range(start, start + n)
+            h[o_pos + t:o_pos + t + n] = np.arange(start, start + n, dtype=np.int32) if n > 16 else range(start, start + n)
             h[o_req + t:o_req + t + n] = b
             for g in range(len(cache.groups)):
                 o_sm = seg(f"slot_mapping{g}")
