@@ -200,8 +200,8 @@ def run_ours(args) -> dict:
         # the device side alone: the captured step replayed back to back (it rewrites the same cache slots)
         graph_ms = None
         dg = eng.decode_graphs
-        if dg is not None and dg.takes(B) and dg.padded(B) in dg.graphs:
-            g0 = dg.graphs[dg.padded(B)][0]
+        if dg is not None and dg.takes(B) and (dg.padded(B), False) in dg.graphs:
+            g0 = dg.graphs[(dg.padded(B), False)][0]
             torch.cuda.synchronize()
             e0.record()
             for _ in range(steps):

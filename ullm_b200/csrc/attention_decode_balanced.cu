@@ -76,7 +76,8 @@ struct DecbParams {
   __nv_bfloat16* out;
   float* part;    // [warps][2][group][D + 4]: unnormalised output, max, sum
   int* prefix;    // [batch + 1]: tiles of the requests before each (per kv head)
-  int batch, num_q, num_kv, page_size, window;
+  int* flags;     // [batch * num_q], zero between launches: set for a head whose pair was cut, cleared by the merge
+  int batch, num_q, num_kv, page_size, page_shift, window;  // page_size = 1 << page_shift
   float scale_log2;
   long long num_pages;
   int* status;
@@ -189,40 +190,52 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
   }
   DecbCursor ahead = cur;  // the cursor of the loads, two tiles ahead of the arithmetic
 
-  // Block-table entries of the request the loads are in, 32 at a time, one per lane.  A tile is one box of 16
-  // tokens when a page holds 16 or more, else 16 / page_size boxes of a whole page each; lane i asks for box i.
+  // Block-table entries of the request the loads are in, 32 at a time, one per lane.  A tile is one group of
+  // boxes of 16 tokens when a page holds 16 or more, else 16 / page_size groups of a whole page each.  A group is
+  // the K and the V box of each 64-element half of the head: 2 HALVES boxes, asked for by as many lanes in one
+  // instruction (lane = group * 2 HALVES + box).
+  const int sh = p.page_shift;
   const int box_tokens = min(p.page_size, DEC_TILE), boxes = DEC_TILE / box_tokens;
+  constexpr int PER_GROUP = 2 * HALVES;
+  const int my_group = lane / PER_GROUP, my_box = lane % PER_GROUP;  // box: (K, V) x halves
+  const CUtensorMap* my_map = my_box < HALVES ? &map_k : &map_v;
+  const int my_off = (my_box < HALVES ? 0 : KV_BYTES) + (my_box % HALVES) * DECB_SUB + my_group * box_tokens * 128;
+  const int my_x = (my_box % HALVES) * 64;
+  const uint32_t group_bytes = (uint32_t)box_tokens * 128 * PER_GROUP;
   int win_b = -1, win_base = 0, win_page = -1;
   auto issue = [&](const DecbCursor& c, int stage) {
-    unsigned char* kbuf = ring + stage * STAGE_BYTES;
-    unsigned char* vbuf = kbuf + KV_BYTES;
     const int base = (c.first + c.tile) * DEC_TILE;  // absolute position of the tile's row 0
-    const int page0 = base / p.page_size;
+    const int page0 = base >> sh;
     if (c.b != win_b || page0 + boxes - 1 > win_base + 31 || page0 < win_base) {
       win_b = c.b;
       win_base = page0;
-      const int last = (c.end - 1) / p.page_size;
+      const int last = (c.end - 1) >> sh;
       win_page = win_base + lane <= last ? p.block_table[(long long)s_slot[c.b] * p.max_pages + win_base + lane] : -1;
     }
-    const int page = __shfl_sync(0xffffffffu, win_page, lane < boxes ? page0 + lane - win_base : 0);
-    // a box is loaded if any of its keys is visible; pages in front of a window may have been given back (-1)
-    const int k0 = base + lane * box_tokens;
-    bool load = lane < boxes && k0 < c.end && k0 + box_tokens > c.lo;
-    if (load && (page < 0 || page >= p.num_pages)) {
-      ullm_report(p.status, ULLM_STATUS_PAGE, c.b, page);
-      load = false;
-    }
-    const unsigned loading = __ballot_sync(0xffffffffu, load);
-    if (lane == 0) decb_mbar_expect_tx(&full[stage], (uint32_t)__popc(loading) * box_tokens * 128 * HALVES * 2);
-    __syncwarp();
-    if (load) {
-      const int tok = p.page_size >= DEC_TILE ? base % p.page_size : 0;
-      const int off = lane * box_tokens * 128;
-#pragma unroll
-      for (int h = 0; h < HALVES; ++h) {
-        decb_tma_4d(kbuf + h * DECB_SUB + off, &map_k, &full[stage], h * 64, c.kh, tok, page);
-        decb_tma_4d(vbuf + h * DECB_SUB + off, &map_v, &full[stage], h * 64, c.kh, tok, page);
+    // a group is loaded if any of its keys is visible; pages in front of a window may have been given back (-1).
+    // 32 / PER_GROUP groups per pass (one pass unless pages are tiny): count first, then one expect_tx, then ask.
+    constexpr int GROUPS_PER_PASS = 32 / PER_GROUP;
+    int n_load = 0;
+    for (int g0 = 0; g0 < boxes; g0 += GROUPS_PER_PASS) {
+      const int grp = g0 + my_group;
+      const int page = __shfl_sync(0xffffffffu, win_page, grp < boxes ? page0 + grp - win_base : 0);
+      const int k0 = base + grp * box_tokens;
+      bool load = grp < boxes && k0 < c.end && k0 + box_tokens > c.lo;
+      if (load && (page < 0 || page >= p.num_pages)) {
+        if (my_box == 0) ullm_report(p.status, ULLM_STATUS_PAGE, c.b, page);
+        load = false;
       }
+      n_load += __popc(__ballot_sync(0xffffffffu, load && my_box == 0));
+    }
+    if (lane == 0) decb_mbar_expect_tx(&full[stage], (uint32_t)n_load * group_bytes);
+    __syncwarp();
+    for (int g0 = 0; g0 < boxes; g0 += GROUPS_PER_PASS) {
+      const int grp = g0 + my_group;
+      const int page = __shfl_sync(0xffffffffu, win_page, grp < boxes ? page0 + grp - win_base : 0);
+      const int k0 = base + grp * box_tokens;
+      if (grp < boxes && k0 < c.end && k0 + box_tokens > c.lo && page >= 0 && page < p.num_pages)
+        decb_tma_4d(ring + stage * STAGE_BYTES + my_off + g0 * box_tokens * 128, my_map, &full[stage], my_x, c.kh,
+                    p.page_size >= DEC_TILE ? base & (p.page_size - 1) : 0, page);
     }
   };
 
@@ -309,15 +322,19 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
         mma_bf16(sc[3], qa[kk], b2, b3);
       }
     }
-    // ---- mask, online softmax -------------------------------------------------------
+    // ---- mask (tiles at the ends of the visible range only), online softmax --------------------
+    const bool edge = base < cur.lo || base + nt * DEC_TILE > cur.end;
     float mx[2] = {m[0], m[1]};
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int key = base + t * 8 + (lane & 3) * 2 + (e & 1);
-        const bool on = (t < 2 || nt == 2) && key >= cur.lo && key < cur.end;
-        const float v = on ? sc[t][e] * p.scale_log2 : -INFINITY;
+        float v = sc[t][e] * p.scale_log2;
+        if (t >= 2 && nt == 1) v = -INFINITY;
+        if (edge) {
+          const int key = base + t * 8 + (lane & 3) * 2 + (e & 1);
+          if (key < cur.lo || key >= cur.end) v = -INFINITY;
+        }
         sc[t][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -327,12 +344,16 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     }
-    float alpha[2];
+    // the running maximum rarely moves after the first tiles: the output is rescaled only when it did
+    const bool moved = __any_sync(0xffffffffu, mx[0] != m[0] || mx[1] != m[1]);
+    float alpha[2] = {1.f, 1.f};
+    if (moved) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      alpha[r] = mx[r] == -INFINITY ? 1.f : exp2f(m[r] - mx[r]);
-      m[r] = mx[r];
-      l[r] *= alpha[r];
+      for (int r = 0; r < 2; ++r) {
+        alpha[r] = mx[r] == -INFINITY ? 1.f : exp2f(m[r] - mx[r]);
+        m[r] = mx[r];
+        l[r] *= alpha[r];
+      }
     }
     unsigned pa[2][4];
     {
@@ -353,10 +374,14 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
       }
     }
     // ---- O = alpha O + P V ------------------------------------------------------------
+    if (moved) {
+#pragma unroll
+      for (int j = 0; j < NT_O; ++j) {
+        o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+      }
+    }
 #pragma unroll
     for (int j = 0; j < NT_O; j += 2) {
-      o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
-      o[j + 1][0] *= alpha[0]; o[j + 1][1] *= alpha[0]; o[j + 1][2] *= alpha[1]; o[j + 1][3] *= alpha[1];
       const int mat = lane >> 3, row = (mat & 1) * 8 + (lane & 7), ch = j + (mat >> 1);
       const int at = (ch >> 3) * DECB_SUB + row * 128 + (((ch & 7) ^ (row & 7)) * 16);
       unsigned b0, b1, b2, b3;
@@ -403,6 +428,9 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
         if ((lane & 3) == 0) {
           if (r0 < group) *reinterpret_cast<float2*>(part + r0 * DECB_ROW(D) + D) = make_float2(m[0], l[0]);
           if (r1 < group) *reinterpret_cast<float2*>(part + r1 * DECB_ROW(D) + D) = make_float2(m[1], l[1]);
+          // tell the merge kernel that these heads have parts to add (every warp of a cut pair says so)
+          if (r0 < group) p.flags[cur.b * p.num_q + cur.kh * group + r0] = 1;
+          if (r1 < group) p.flags[cur.b * p.num_q + cur.kh * group + r1] = 1;
         }
       }
       ++shares;
@@ -427,6 +455,7 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
 template <int D>
 __global__ void __launch_bounds__(128) decode_balanced_merge_kernel(const float* __restrict__ part,
                                                                     const int* __restrict__ prefix,
+                                                                    int* __restrict__ flags,
                                                                     __nv_bfloat16* __restrict__ out, int batch,
                                                                     int num_q, int num_kv, long long warps) {
   constexpr int PER = D / 4;         // threads of a group
@@ -435,6 +464,11 @@ __global__ void __launch_bounds__(128) decode_balanced_merge_kernel(const float*
   __shared__ float4 s_acc[LANES][PER];
   pdl_launch_dependents();
   pdl_wait();
+  // Most heads have nothing to merge (their pair lay whole inside one warp's range, or the request holds
+  // nothing): they leave at once.  The flag is cleared for the next launch.
+  if (flags[blockIdx.x] == 0) return;
+  __syncthreads();
+  if (threadIdx.x == 0) flags[blockIdx.x] = 0;
   const int b = blockIdx.x / num_q, h = blockIdx.x % num_q;
   const int group = num_q / num_kv, kh = h / group, r = h % group;
   const int tiles = prefix[b + 1] - prefix[b];
@@ -531,12 +565,11 @@ static int decb_blocks(int which) {
   return g_decb_blocks[which];
 }
 
-// Sizes: as ullm_decode_attention_supported, at most DECB_MAX_BATCH requests, and pages of 1, 2, 4, 8 tokens or
-// a multiple of 16 (a tile of 16 tokens is then whole pages, or lies inside one).
+// Sizes: as ullm_decode_attention_supported, at most DECB_MAX_BATCH requests, and pages of a power of two of
+// tokens (a tile of 16 tokens is then whole pages, or lies inside one; positions split by shifts).
 extern "C" int ullm_decode_attention_balanced_supported(int head_dim, int num_q, int num_kv, int batch, int page_size) {
   if (num_kv <= 0 || num_q % num_kv || batch > DECB_MAX_BATCH) return 0;
-  if (!(page_size == 1 || page_size == 2 || page_size == 4 || page_size == 8 || (page_size > 0 && page_size % 16 == 0)))
-    return 0;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return 0;
   return (head_dim == 64 || head_dim == 128) && (num_q / num_kv) <= 16;
 }
 
@@ -545,7 +578,8 @@ extern "C" int ullm_decode_attention_balanced_blocks(int head_dim) {
   return head_dim == 64 ? decb_blocks<64>(0) : head_dim == 128 ? decb_blocks<128>(1) : 0;
 }
 
-// Floats of `part` a launch needs for `group` query heads per kv head (`prefix` takes batch + 1 ints).
+// Floats of `part` a launch needs for `group` query heads per kv head (`prefix` takes batch + 1 ints, `flags`
+// batch * num_q ints that are zero before the first launch).
 extern "C" long long ullm_decode_attention_balanced_scratch_floats(int head_dim, int group) {
   return (long long)ullm_decode_attention_balanced_blocks(head_dim) * DECB_WARPS * 2 * group * DECB_ROW(head_dim);
 }
@@ -553,14 +587,14 @@ extern "C" long long ullm_decode_attention_balanced_scratch_floats(int head_dim,
 extern "C" int ullm_decode_attention_balanced(const void* q, long long q_row_stride, const void* k_cache,
                                               const void* v_cache, const int* block_table, int max_pages,
                                               const int* req_slots, const int* kv_len, void* out, float* part,
-                                              int* prefix, int batch, int num_q, int num_kv, int head_dim,
+                                              int* prefix, int* flags, int batch, int num_q, int num_kv, int head_dim,
                                               int page_size, int window, float scale, long long num_pages, int* status,
                                               void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (batch < 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || window < 0) return ULLM_ERR_BAD_SIZE;
   if (!ullm_decode_attention_balanced_supported(head_dim, num_q, num_kv, batch, page_size)) return ULLM_ERR_UNSUPPORTED;
   if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return ULLM_ERR_UNSUPPORTED;
-  if (part == nullptr || prefix == nullptr) return ULLM_ERR_BAD_SIZE;
+  if (part == nullptr || prefix == nullptr || flags == nullptr) return ULLM_ERR_BAD_SIZE;
   if (batch == 0) return ULLM_OK;
   const int blocks = ullm_decode_attention_balanced_blocks(head_dim);
   if (blocks <= 0) return ULLM_ERR_LAUNCH;
@@ -576,10 +610,13 @@ extern "C" int ullm_decode_attention_balanced(const void* q, long long q_row_str
   p.out = (__nv_bfloat16*)out;
   p.part = part;
   p.prefix = prefix;
+  p.flags = flags;
   p.batch = batch;
   p.num_q = num_q;
   p.num_kv = num_kv;
   p.page_size = page_size;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.num_pages = num_pages;
@@ -596,13 +633,13 @@ extern "C" int ullm_decode_attention_balanced(const void* q, long long q_row_str
                             (size_t)decb_smem_bytes(64), st, map_k, map_v, p);
     if (rc == ULLM_OK)
       rc = ullm_launch_kernel(decode_balanced_merge_kernel<64>, dim3(batch * num_q), dim3(128), 0, st,
-                              (const float*)part, (const int*)prefix, (__nv_bfloat16*)out, batch, num_q, num_kv, warps);
+                              (const float*)part, (const int*)prefix, flags, (__nv_bfloat16*)out, batch, num_q, num_kv, warps);
   } else {
     rc = ullm_launch_kernel(decode_attention_balanced_kernel<128>, dim3(blocks), dim3(DECB_WARPS * 32),
                             (size_t)decb_smem_bytes(128), st, map_k, map_v, p);
     if (rc == ULLM_OK)
       rc = ullm_launch_kernel(decode_balanced_merge_kernel<128>, dim3(batch * num_q), dim3(128), 0, st,
-                              (const float*)part, (const int*)prefix, (__nv_bfloat16*)out, batch, num_q, num_kv, warps);
+                              (const float*)part, (const int*)prefix, flags, (__nv_bfloat16*)out, batch, num_q, num_kv, warps);
   }
   if (rc != ULLM_OK) return rc;
   return ullm_launch_status();

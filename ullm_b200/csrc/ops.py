@@ -112,7 +112,7 @@ class Kernels:
             "ullm_qk_norm_rope_store": [I, P, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, LL, P, P],
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
-            "ullm_decode_attention_balanced": [P, LL, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_decode_attention_balanced": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
@@ -165,6 +165,8 @@ class Kernels:
             self.status.zero_()
             if self._lin_counters is not None:
                 self._lin_counters.zero_()  # a product that gave up may have left tiles half counted
+            for _part, _prefix, flags in self._decb.values():
+                flags.zero_()  # likewise the merge flags of the balanced decode attention
             msg = STATUS_MESSAGES.get(s[0], "status {code}").format(index=s[1], value=s[2], code=s[0])
             raise KernelError(f"a kernel refused an index: {msg}")
 
@@ -373,17 +375,18 @@ class Kernels:
             balanced = getattr(ctx, "ragged", False) if self.use_balanced_decode == "auto" else self.use_balanced_decode
             if balanced and self.lib.ullm_decode_attention_balanced_supported(
                     head_dim, num_q, num_kv, T, page_size):
-                key = (head_dim, num_q // num_kv)
+                key = (head_dim, num_q, num_kv)
                 if key not in self._decb:
-                    n = self.lib.ullm_decode_attention_balanced_scratch_floats(*key)
+                    n = self.lib.ullm_decode_attention_balanced_scratch_floats(head_dim, num_q // num_kv)
                     if n <= 0:
                         raise KernelError("decode_attention_balanced: cannot size its grid on this device")
                     self._decb[key] = (torch.empty(n, dtype=torch.float32, device="cuda"),
-                                       torch.zeros(513, dtype=torch.int32, device="cuda"))
-                part, prefix = self._decb[key]
+                                       torch.zeros(513, dtype=torch.int32, device="cuda"),
+                                       torch.zeros(512 * num_q, dtype=torch.int32, device="cuda"))
+                part, prefix, flags = self._decb[key]
                 self._check(self.lib.ullm_decode_attention_balanced(
                     _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-                    _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(part), _ptr(prefix), T, num_q, num_kv, head_dim,
+                    _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(part), _ptr(prefix), _ptr(flags), T, num_q, num_kv, head_dim,
                     page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
                     f"decode_attention_balanced (head_dim {head_dim})")
                 self.launches += 1  # the merge of the shared pairs
