@@ -76,7 +76,7 @@ struct DecbParams {
   __nv_bfloat16* out;
   float* part;    // [warps][2][group][D + 4]: unnormalised output, max, sum
   int* prefix;    // [batch + 1]: tiles of the requests before each (per kv head)
-  int* flags;     // [batch * num_q], zero between launches: set for a head whose pair was cut, cleared by the merge
+  int* flags;     // [batch * num_kv], zero between launches: set for a pair that was cut, cleared by the merge
   int batch, num_q, num_kv, page_size, page_shift, window;  // page_size = 1 << page_shift
   float scale_log2;
   long long num_pages;
@@ -428,10 +428,8 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
         if ((lane & 3) == 0) {
           if (r0 < group) *reinterpret_cast<float2*>(part + r0 * DECB_ROW(D) + D) = make_float2(m[0], l[0]);
           if (r1 < group) *reinterpret_cast<float2*>(part + r1 * DECB_ROW(D) + D) = make_float2(m[1], l[1]);
-          // tell the merge kernel that these heads have parts to add (every warp of a cut pair says so)
-          if (r0 < group) p.flags[cur.b * p.num_q + cur.kh * group + r0] = 1;
-          if (r1 < group) p.flags[cur.b * p.num_q + cur.kh * group + r1] = 1;
         }
+        if (lane == 0) p.flags[cur.b * p.num_kv + cur.kh] = 1;  // tells the merge kernel that this pair has parts to add
       }
       ++shares;
       m[0] = m[1] = -INFINITY;
@@ -450,50 +448,50 @@ decode_attention_balanced_kernel(const __grid_constant__ CUtensorMap map_k, cons
 }
 
 // Pairs that more than one warp worked on: out[b, h, :] = sum_i O_i 2^(m_i - M) / sum_i l_i 2^(m_i - M), parts
-// in warp order.  A block per (request, head); its threads are LANES groups of D / 4 threads: a group takes
-// every LANES-th part (four output elements per thread), the groups' sums meet in shared memory.
+// in warp order.  A block of 512 threads per (request, kv head): D / 4 threads take four output elements each,
+// four such groups share a head (a group takes every fourth part; their sums meet in shared memory), and
+// 512 / D heads of the pair are merged at a time.
+#define DECB_MERGE_THREADS 512
+#define DECB_MERGE_LANES 4
 template <int D>
-__global__ void __launch_bounds__(128) decode_balanced_merge_kernel(const float* __restrict__ part,
-                                                                    const int* __restrict__ prefix,
-                                                                    int* __restrict__ flags,
-                                                                    __nv_bfloat16* __restrict__ out, int batch,
-                                                                    int num_q, int num_kv, long long warps) {
-  constexpr int PER = D / 4;         // threads of a group
-  constexpr int LANES = 128 / PER;   // groups
-  __shared__ float s_m[LANES], s_l[LANES];
-  __shared__ float4 s_acc[LANES][PER];
+__global__ void __launch_bounds__(DECB_MERGE_THREADS)
+decode_balanced_merge_kernel(const float* __restrict__ part, const int* __restrict__ prefix, int* __restrict__ flags,
+                             __nv_bfloat16* __restrict__ out, int batch, int num_q, int num_kv, long long warps) {
+  constexpr int PER = D / 4;                                             // threads that hold one row of D
+  constexpr int HEADS = DECB_MERGE_THREADS / PER / DECB_MERGE_LANES;     // heads at a time
+  __shared__ float s_m[HEADS][DECB_MERGE_LANES], s_l[HEADS][DECB_MERGE_LANES];
+  __shared__ float4 s_acc[HEADS][DECB_MERGE_LANES][PER];
   pdl_launch_dependents();
   pdl_wait();
-  // Most heads have nothing to merge (their pair lay whole inside one warp's range, or the request holds
-  // nothing): they leave at once.  The flag is cleared for the next launch.
+  // Most pairs have nothing to merge (they lay whole inside one warp's range, or the request holds nothing):
+  // their blocks leave at once.  The flag is cleared for the next launch.
   if (flags[blockIdx.x] == 0) return;
   __syncthreads();
   if (threadIdx.x == 0) flags[blockIdx.x] = 0;
-  const int b = blockIdx.x / num_q, h = blockIdx.x % num_q;
-  const int group = num_q / num_kv, kh = h / group, r = h % group;
+  const int b = blockIdx.x / num_kv, kh = blockIdx.x % num_kv;
+  const int group = num_q / num_kv;
   const int tiles = prefix[b + 1] - prefix[b];
-  if (tiles == 0) return;  // zeros are there already
+  if (tiles == 0) return;
   const long long W = (long long)num_kv * prefix[batch];
   const long long GW = decb_ranges(W, warps);
   const long long p0 = (long long)num_kv * prefix[b] + (long long)kh * tiles, p1 = p0 + tiles - 1;  // first, last tile
   const long long i_first = ((p0 + 1) * GW + W - 1) / W - 1, i_last = ((p1 + 1) * GW + W - 1) / W - 1;
-  if (i_first == i_last) return;  // one warp held the whole pair and wrote the rows
-  const int lane_g = threadIdx.x / PER, t = threadIdx.x % PER;
-  // Warp i starts at tile floor(i W / GW), kept as quotient and remainder so that the loop divides nothing.
-  const long long step_q = W / GW, step_r = W % GW;
-  long long q = i_first * W / GW, rem = i_first * W % GW;
-  float mm = -INFINITY, ll = 0.f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  int k = 0;
-  for (long long i = i_first; i <= i_last; ++i) {
-    long long qn = q + step_q, rn = rem + step_r;
-    if (rn >= GW) rn -= GW, ++qn;
-    if (qn > q) {  // the warp's range [q, qn) is not empty
-      if (k % LANES == lane_g) {
-        const int slot = q >= p0 ? 0 : 1;  // the pair is the warp's first share iff the warp starts inside it
-        const float* row = part + ((i * 2 + slot) * group + r) * DECB_ROW(D);
+  if (i_first == i_last) return;
+  // Every warp's range holds tiles (decb_ranges), and only the first warp can have begun before the pair: its
+  // part is in its slot 1 then; all the others begin inside the pair and left theirs in slot 0.
+  const int slot_first = i_first * W / GW >= p0 ? 0 : 1;
+  const int t4 = threadIdx.x % PER, sub = threadIdx.x / PER;
+  const int lane_g = sub % DECB_MERGE_LANES, hs = sub / DECB_MERGE_LANES;
+  for (int r0 = 0; r0 < group; r0 += HEADS) {  // the trip count is the same for every thread
+    const int r = r0 + hs;
+    float mm = -INFINITY, ll = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < group) {
+#pragma unroll 4
+      for (long long i = i_first + lane_g; i <= i_last; i += DECB_MERGE_LANES) {
+        const float* row = part + ((i * 2 + (i == i_first ? slot_first : 0)) * group + r) * DECB_ROW(D);
         const float mi = row[D], li = row[D + 1];
-        const float4 v = *reinterpret_cast<const float4*>(row + t * 4);
+        const float4 v = *reinterpret_cast<const float4*>(row + t4 * 4);
         const float mn = fmaxf(mm, mi);
         const float f_old = mm == -INFINITY ? 0.f : exp2f(mm - mn), f_new = mi == -INFINITY ? 0.f : exp2f(mi - mn);
         ll = ll * f_old + li * f_new;
@@ -503,36 +501,35 @@ __global__ void __launch_bounds__(128) decode_balanced_merge_kernel(const float*
         acc.w = acc.w * f_old + v.w * f_new;
         mm = mn;
       }
-      ++k;
     }
-    q = qn, rem = rn;
-  }
-  if (t == 0) {
-    s_m[lane_g] = mm;
-    s_l[lane_g] = ll;
-  }
-  s_acc[lane_g][t] = acc;
-  __syncthreads();
-  if (lane_g == 0) {
-    float M = -INFINITY;
-#pragma unroll
-    for (int g = 0; g < LANES; ++g) M = fmaxf(M, s_m[g]);
-    float L = 0.f;
-    float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int g = 0; g < LANES; ++g) {
-      const float f = s_m[g] == -INFINITY ? 0.f : exp2f(s_m[g] - M);
-      const float4 v = s_acc[g][t];
-      L += s_l[g] * f;
-      A.x += v.x * f;
-      A.y += v.y * f;
-      A.z += v.z * f;
-      A.w += v.w * f;
+    if (t4 == 0) {
+      s_m[hs][lane_g] = mm;
+      s_l[hs][lane_g] = ll;
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    __nv_bfloat16* o = out + ((long long)b * num_q + h) * D + t * 4;
-    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(A.x * inv, A.y * inv);
-    *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(A.z * inv, A.w * inv);
+    s_acc[hs][lane_g][t4] = acc;
+    __syncthreads();
+    if (lane_g == 0 && r < group) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int g = 0; g < DECB_MERGE_LANES; ++g) M = fmaxf(M, s_m[hs][g]);
+      float L = 0.f;
+      float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < DECB_MERGE_LANES; ++g) {  // in lane order: the same sum in every launch
+        const float f = s_m[hs][g] == -INFINITY ? 0.f : exp2f(s_m[hs][g] - M);
+        const float4 v = s_acc[hs][g][t4];
+        L += s_l[hs][g] * f;
+        A.x += v.x * f;
+        A.y += v.y * f;
+        A.z += v.z * f;
+        A.w += v.w * f;
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      __nv_bfloat16* o = out + ((long long)b * num_q + kh * group + r) * D + t4 * 4;
+      *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(A.x * inv, A.y * inv);
+      *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(A.z * inv, A.w * inv);
+    }
+    __syncthreads();
   }
 }
 
@@ -579,7 +576,7 @@ extern "C" int ullm_decode_attention_balanced_blocks(int head_dim) {
 }
 
 // Floats of `part` a launch needs for `group` query heads per kv head (`prefix` takes batch + 1 ints, `flags`
-// batch * num_q ints that are zero before the first launch).
+// batch * num_kv ints that are zero before the first launch).
 extern "C" long long ullm_decode_attention_balanced_scratch_floats(int head_dim, int group) {
   return (long long)ullm_decode_attention_balanced_blocks(head_dim) * DECB_WARPS * 2 * group * DECB_ROW(head_dim);
 }
@@ -632,13 +629,13 @@ extern "C" int ullm_decode_attention_balanced(const void* q, long long q_row_str
     rc = ullm_launch_kernel(decode_attention_balanced_kernel<64>, dim3(blocks), dim3(DECB_WARPS * 32),
                             (size_t)decb_smem_bytes(64), st, map_k, map_v, p);
     if (rc == ULLM_OK)
-      rc = ullm_launch_kernel(decode_balanced_merge_kernel<64>, dim3(batch * num_q), dim3(128), 0, st,
+      rc = ullm_launch_kernel(decode_balanced_merge_kernel<64>, dim3(batch * num_kv), dim3(DECB_MERGE_THREADS), 0, st,
                               (const float*)part, (const int*)prefix, flags, (__nv_bfloat16*)out, batch, num_q, num_kv, warps);
   } else {
     rc = ullm_launch_kernel(decode_attention_balanced_kernel<128>, dim3(blocks), dim3(DECB_WARPS * 32),
                             (size_t)decb_smem_bytes(128), st, map_k, map_v, p);
     if (rc == ULLM_OK)
-      rc = ullm_launch_kernel(decode_balanced_merge_kernel<128>, dim3(batch * num_q), dim3(128), 0, st,
+      rc = ullm_launch_kernel(decode_balanced_merge_kernel<128>, dim3(batch * num_kv), dim3(DECB_MERGE_THREADS), 0, st,
                               (const float*)part, (const int*)prefix, flags, (__nv_bfloat16*)out, batch, num_q, num_kv, warps);
   }
   if (rc != ULLM_OK) return rc;
