@@ -129,6 +129,63 @@ __global__ void add_rmsnorm_kernel(const T* x, T* residual, const float* __restr
   for (int c = threadIdx.x; c < cols; c += blockDim.x) out[base + c] = from_f32<T>(row[c] * rstd * w[c]);
 }
 
+// bfloat16 rows that fit the block's registers (cols <= 16 * threads, a multiple of 8): every thread holds up
+// to two groups of 8 elements, all loads are issued before anything else, the row never goes through shared
+// memory.  The sum x + residual is formed and squared in 32-bit; the residual is rounded once.
+__global__ void __launch_bounds__(512)
+add_rmsnorm_bf16x8_reg_kernel(const __nv_bfloat16* x, __nv_bfloat16* residual, const float* __restrict__ w,
+                              __nv_bfloat16* out, int cols, float eps) {  // out may be x
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long base = (long long)blockIdx.x * cols;
+  const int groups = cols / 8;
+  const int g0 = threadIdx.x, g1 = threadIdx.x + blockDim.x;
+  const bool on0 = g0 < groups, on1 = g1 < groups;
+  uint4 xv[2], rv[2];
+  xv[0] = on0 ? *reinterpret_cast<const uint4*>(x + base + g0 * 8) : make_uint4(0, 0, 0, 0);
+  xv[1] = on1 ? *reinterpret_cast<const uint4*>(x + base + g1 * 8) : make_uint4(0, 0, 0, 0);
+  if (residual != nullptr) {
+    rv[0] = on0 ? *reinterpret_cast<const uint4*>(residual + base + g0 * 8) : make_uint4(0, 0, 0, 0);
+    rv[1] = on1 ? *reinterpret_cast<const uint4*>(residual + base + g1 * 8) : make_uint4(0, 0, 0, 0);
+  }
+  float s[2][8];
+  float acc = 0.f;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const __nv_bfloat16* xe = reinterpret_cast<const __nv_bfloat16*>(&xv[q]);
+    const __nv_bfloat16* re = reinterpret_cast<const __nv_bfloat16*>(&rv[q]);
+    uint4 ov;
+    __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      s[q][k] = __bfloat162float(xe[k]);
+      if (residual != nullptr) {
+        s[q][k] += __bfloat162float(re[k]);
+        oe[k] = __float2bfloat16_rn(s[q][k]);
+      }
+      acc += s[q][k] * s[q][k];
+    }
+    if (residual != nullptr && (q == 0 ? on0 : on1))
+      *reinterpret_cast<uint4*>(residual + base + (q == 0 ? g0 : g1) * 8) = ov;
+  }
+  const float total = block_sum(acc, scratch);
+  const float rstd = rsqrtf(total / (float)cols + eps);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int g = q == 0 ? g0 : g1;
+    if (g < groups) {
+      const float4 w0 = *reinterpret_cast<const float4*>(w + g * 8), w1 = *reinterpret_cast<const float4*>(w + g * 8 + 4);
+      const float wk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      uint4 ov;
+      __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16_rn(s[q][k] * rstd * wk[k]);
+      *reinterpret_cast<uint4*>(out + base + g * 8) = ov;
+    }
+  }
+}
+
 // bf16 rows of a multiple of 8 elements on 16-byte boundaries: 8 elements per thread and step.
 // Same arithmetic and the same order of additions inside a thread's 8-element groups.
 __global__ void add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* x, __nv_bfloat16* residual, const float* __restrict__ w,
@@ -197,6 +254,12 @@ static int add_rmsnorm_launch(int which, const void* x, void* residual, const fl
         return ULLM_ERR_LAUNCH;
       g_rmsnorm_smem_set[2] = 1;
     }
+    if (cols <= 16 * 512 && (uintptr_t)w % 16 == 0) {  // the row fits the registers of a block: two groups of 8 per thread
+      int threads = 32;
+      while (threads < 512 && threads * 16 < cols) threads <<= 1;
+      return ullm_launch_kernel(add_rmsnorm_bf16x8_reg_kernel, dim3(rows), dim3(threads), 0, st,
+                                (const __nv_bfloat16*)x, (__nv_bfloat16*)residual, w, (__nv_bfloat16*)out, cols, eps);
+    }
     int threads = 32;
     while (threads < 512 && threads * 8 < cols) threads <<= 1;
     return ullm_launch_kernel(add_rmsnorm_bf16x8_kernel, dim3(rows), dim3(threads), smem, st,
@@ -237,30 +300,38 @@ __global__ void act_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, lo
   }
 }
 
-// bf16 rows whose halves start on 16-byte boundaries: 8 elements per thread.
+// bfloat16 in 16-byte pieces: blockIdx.y is the row, a thread takes two pieces of 8 elements and loads gate and
+// up of both before anything else (no division per element, four loads in flight per thread).
 template <int ACT>
-__global__ void act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                                      long long rows, int inter) {
+__global__ void __launch_bounds__(256)
+act_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long rows,
+                      int inter) {
   pdl_launch_dependents();
   pdl_wait();
   const int per_row = inter / 8;
-  const long long n = rows * per_row;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / per_row;
-    const int c = (int)(i - t * per_row) * 8;
-    const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + c);
-    const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + c);
-    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv);
-    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv);
-    uint4 ov;
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+  for (long long t = blockIdx.y; t < rows; t += gridDim.y) {
+    const __nv_bfloat16* g_row = gu + t * 2 * inter;
+    const int c0 = (blockIdx.x * 2 * blockDim.x + threadIdx.x) * 8, c1 = c0 + blockDim.x * 8;
+    const bool on0 = c0 < per_row * 8, on1 = c1 < per_row * 8;
+    uint4 gv[2], uv[2];
+    gv[0] = on0 ? *reinterpret_cast<const uint4*>(g_row + c0) : make_uint4(0, 0, 0, 0);
+    uv[0] = on0 ? *reinterpret_cast<const uint4*>(g_row + inter + c0) : make_uint4(0, 0, 0, 0);
+    gv[1] = on1 ? *reinterpret_cast<const uint4*>(g_row + c1) : make_uint4(0, 0, 0, 0);
+    uv[1] = on1 ? *reinterpret_cast<const uint4*>(g_row + inter + c1) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float gf = to_f32(g[k]);
-      const float a = ACT == 0 ? act_silu(gf) : act_gelu_tanh(gf);
-      o[k] = __float2bfloat16_rn(a * to_f32(u[k]));
+    for (int q = 0; q < 2; ++q) {
+      const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&gv[q]);
+      const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&uv[q]);
+      uint4 ov;
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float gf = to_f32(g[k]);
+        const float a = ACT == 0 ? act_silu(gf) : act_gelu_tanh(gf);
+        o[k] = __float2bfloat16_rn(a * to_f32(u[k]));
+      }
+      if (q == 0 ? on0 : on1) *reinterpret_cast<uint4*>(out + t * inter + (q == 0 ? c0 : c1)) = ov;
     }
-    *reinterpret_cast<uint4*>(out + t * inter + c) = ov;
   }
 }
 
@@ -273,12 +344,11 @@ extern "C" int ullm_act_mul(int dtype, int act, const void* gate_up, void* out, 
   const int threads = 256;
   if (dtype == ULLM_DTYPE_BF16 && inter % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(out) % 16 == 0) {
-    long long blocks = (n / 8 + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    const dim3 grid((unsigned)((inter / 8 + 2 * threads - 1) / (2 * threads)), (unsigned)(rows < 65535 ? rows : 65535));
     if (act == 0)
-      return ullm_launch_kernel(act_mul_bf16x8_kernel<0>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
+      return ullm_launch_kernel(act_mul_bf16x8_kernel<0>, grid, dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
     else
-      return ullm_launch_kernel(act_mul_bf16x8_kernel<1>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
+      return ullm_launch_kernel(act_mul_bf16x8_kernel<1>, grid, dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
     return ullm_launch_status();
   }
   long long blocks = (n + threads - 1) / threads;

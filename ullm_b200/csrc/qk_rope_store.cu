@@ -90,80 +90,103 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
   }
 }
 
-// bfloat16, head sizes 64 and 128, full rotary: a lane owns D / 32 neighbouring elements (one 4- or 8-byte
-// load), the sum of squares is a warp reduction, and the rotation partner (D / 2 further) sits 16 lanes
-// away, so no shared memory is needed.  Same arithmetic as the general kernel.
-template <int D>
+// The same for bfloat16 with head size 64 or 128, moved in 16-byte pieces: D / 8 lanes hold one (token, head)
+// row (8 elements each), so a warp works on 32 / (D / 8) rows side by side.  A warp takes QKV_STEPS such sets
+// of one token's heads (6 for many tokens: fewer table reads and more bytes in flight per lane; 1 for the few
+// tokens of a decode step, where the shortest chain of work per warp counts): the token's position, its rows of the rotation tables and its cache slot are read once
+// for all of them, and all the rows are loaded before any arithmetic (96 bytes in flight per lane).  The
+// rotation partner of an element (D / 2 further) sits in the lane D / 16 away; sums and partners travel by
+// shuffles inside the row's lanes.  Nothing returns early: lanes without work stay in the shuffles.
+template <int D, int QKV_STEPS>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int num_kv, const float* __restrict__ q_w,
                                const float* __restrict__ k_w, float eps, const float* __restrict__ cos_t,
                                const float* __restrict__ sin_t, int max_positions, const int* __restrict__ positions,
                                const int* __restrict__ slot_mapping, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                long long num_slots, int* status) {
-  constexpr int VEC = D / 32;
+  constexpr int LW = D / 8;                  // lanes of a row
+  constexpr int ROWS = 32 / LW;              // rows of a warp, side by side
+  constexpr int CHUNK = ROWS * QKV_STEPS;    // heads of a token that one warp takes
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LW, sl = lane % LW;
   const int heads = num_q + 2 * num_kv;
+  const int chunks = (heads + CHUNK - 1) / CHUNK;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-  if (unit >= (long long)tokens * heads) return;
-  const int t = (int)(unit / heads);
-  const int h = (int)(unit - (long long)t * heads);
-  const bool is_q = h < num_q;
-  const bool is_k = !is_q && h < num_q + num_kv;
+  const bool on = unit < (long long)tokens * chunks;  // the same for the whole warp
+  const int t = on ? (int)(unit / chunks) : 0;
+  const int h0 = on ? (int)(unit - (long long)t * chunks) * CHUNK : heads;
+
+  // what the token's rows share
   long long slot = -1;
-  if (!is_q) {
-    if (slot_mapping == nullptr) return;
+  if (on && slot_mapping != nullptr) {
     slot = slot_mapping[t];
-    if (slot < 0) return;
     if (slot >= num_slots) {
       if (lane == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
-      return;
+      slot = -1;
     }
   }
-  __nv_bfloat16* src = qkv + (long long)t * heads * D + (long long)h * D + lane * VEC;
-  __nv_bfloat16 raw[VEC];
-  if (VEC == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
-  else *reinterpret_cast<unsigned*>(raw) = *reinterpret_cast<const unsigned*>(src);
-  if (!is_q && !is_k) {
-    __nv_bfloat16* dst = v_cache + (slot * num_kv + (h - num_q - num_kv)) * D + lane * VEC;
-    if (VEC == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(raw);
-    else *reinterpret_cast<unsigned*>(dst) = *reinterpret_cast<const unsigned*>(raw);
-    return;
-  }
-  float y[VEC];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    y[i] = __bfloat162float(raw[i]);
-    ss += y[i] * y[i];
-  }
-  const float* w = is_q ? q_w : k_w;
-  if (w != nullptr) {
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / (float)D + eps);
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) y[i] = y[i] * rstd * w[lane * VEC + i];
-  }
-  int pos = positions[t];
+  int pos = on ? positions[t] : 0;
   if (pos < 0 || pos >= max_positions) {
     if (lane == 0) ullm_report(status, ULLM_STATUS_POSITION, t, pos);
     pos = 0;
   }
-  const int j0 = (lane & 15) * VEC;  // index into the half-size tables
+  uint4 raw[QKV_STEPS];
+#pragma unroll
+  for (int u = 0; u < QKV_STEPS; ++u) {
+    const int h = h0 + u * ROWS + sub;
+    // key and value rows of a token without a slot (padding, or an execution that reads another one's cache) are skipped
+    const bool live = h < heads && (h < num_q || slot >= 0);
+    raw[u] = live ? *reinterpret_cast<const uint4*>(qkv + ((long long)t * heads + h) * D + sl * 8) : make_uint4(0, 0, 0, 0);
+  }
+  const int j0 = (sl % (LW / 2)) * 8;  // index into the half-size tables
   const float* cr = cos_t + (long long)pos * (D / 2) + j0;
   const float* sr = sin_t + (long long)pos * (D / 2) + j0;
-  __nv_bfloat16 o[VEC];
+  const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
+  const float c8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float s8[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
-    const float c = cr[i], sn = sr[i];
-    const float v = lane < 16 ? y[i] * c - partner * sn : y[i] * c + partner * sn;
-    o[i] = __float2bfloat16_rn(v);
+  for (int u = 0; u < QKV_STEPS; ++u) {
+    const int h = h0 + u * ROWS + sub;
+    const bool is_q = h < num_q, is_k = !is_q && h < num_q + num_kv;
+    const bool live = h < heads && (is_q || slot >= 0);
+    if (live && !is_q && !is_k) {  // value row: plain copy
+      *reinterpret_cast<uint4*>(v_cache + (slot * num_kv + (h - num_q - num_kv)) * D + sl * 8) = raw[u];
+    }
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
+    float y[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      y[i] = __bfloat162float(e[i]);
+      ss += y[i] * y[i];
+    }
+    const float* w = is_q ? q_w : k_w;
+#pragma unroll
+    for (int off = LW / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);  // every lane takes part
+    if (w != nullptr) {
+      const float rstd = rsqrtf(ss / (float)D + eps);
+      const float4 w0 = *reinterpret_cast<const float4*>(w + sl * 8), w1 = *reinterpret_cast<const float4*>(w + sl * 8 + 4);
+      y[0] *= rstd * w0.x; y[1] *= rstd * w0.y; y[2] *= rstd * w0.z; y[3] *= rstd * w0.w;
+      y[4] *= rstd * w1.x; y[5] *= rstd * w1.y; y[6] *= rstd * w1.z; y[7] *= rstd * w1.w;
+    }
+    uint4 ov;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, y[i], LW / 2);
+      const float v = sl < LW / 2 ? y[i] * c8[i] - partner * s8[i] : y[i] * c8[i] + partner * s8[i];
+      o[i] = __float2bfloat16_rn(v);
+    }
+    if (live && (is_q || is_k)) {
+      __nv_bfloat16* dst = is_q ? qkv + ((long long)t * heads + h) * D + sl * 8
+                                : k_cache + (slot * num_kv + (h - num_q)) * D + sl * 8;
+      *reinterpret_cast<uint4*>(dst) = ov;
+    }
   }
-  __nv_bfloat16* dst = is_q ? src : k_cache + (slot * num_kv + (h - num_q)) * D + lane * VEC;
-  if (VEC == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
-  else *reinterpret_cast<unsigned*>(dst) = *reinterpret_cast<const unsigned*>(o);
 }
 
 extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
@@ -183,16 +206,20 @@ extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num
   if (dtype == ULLM_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128) &&
       (uintptr_t)qkv % 8 == 0 && (slot_mapping == nullptr || ((uintptr_t)k_cache % 8 == 0 && (uintptr_t)v_cache % 8 == 0))) {
     const int warps = 8;
-    const long long vblocks = (units + warps - 1) / warps;
-    if (head_dim == 128)
-      return ullm_launch_kernel(qk_norm_rope_store_bf16_kernel<128>, dim3((int)vblocks), dim3(warps * 32), 0, st,
-                                (__nv_bfloat16*)qkv, tokens, num_q, num_kv, q_w, k_w, eps, cos_t, sin_t, max_positions,
-                                positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots,
-                                status);
-    return ullm_launch_kernel(qk_norm_rope_store_bf16_kernel<64>, dim3((int)vblocks), dim3(warps * 32), 0, st,
-                              (__nv_bfloat16*)qkv, tokens, num_q, num_kv, q_w, k_w, eps, cos_t, sin_t, max_positions,
-                              positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots,
-                              status);
+    const int steps = (long long)tokens * (num_q + 2 * num_kv) >= 8192 ? 6 : 1;
+    const int chunk = (32 / (head_dim / 8)) * steps;  // heads of a token that one warp takes
+    const long long vunits = (long long)tokens * ((num_q + 2 * num_kv + chunk - 1) / chunk);
+    const long long vblocks = (vunits + warps - 1) / warps;
+#define ULLM_ROPE_LAUNCH(DD, SS)                                                                                   \
+  return ullm_launch_kernel(qk_norm_rope_store_bf16_kernel<DD, SS>, dim3((int)vblocks), dim3(warps * 32), 0, st,   \
+                            (__nv_bfloat16*)qkv, tokens, num_q, num_kv, q_w, k_w, eps, cos_t, sin_t, max_positions, \
+                            positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots,   \
+                            status)
+    if (head_dim == 128 && steps == 6) ULLM_ROPE_LAUNCH(128, 6);
+    if (head_dim == 128) ULLM_ROPE_LAUNCH(128, 1);
+    if (steps == 6) ULLM_ROPE_LAUNCH(64, 6);
+    ULLM_ROPE_LAUNCH(64, 1);
+#undef ULLM_ROPE_LAUNCH
   }
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<float>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
