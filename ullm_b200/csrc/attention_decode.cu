@@ -287,14 +287,34 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
   if (d >= D) return;
+  // eight splits at a time, all their loads issued before they are used (the count is small, the latency of a
+  // chain of dependent loads is what this kernel would otherwise spend its time on)
+  const float* ml = part_ml + bh * num_splits * 2;
+  const float* po = part_o + bh * num_splits * D + d;
   float mm = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, part_ml[(bh * num_splits + s) * 2]);
+  for (int s0 = 0; s0 < num_splits; s0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = s0 + i < num_splits ? ml[(s0 + i) * 2] : -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mm = fmaxf(mm, v[i]);
+  }
   float ll = 0.f, acc = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float ms = part_ml[(bh * num_splits + s) * 2];
-    const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-    ll += part_ml[(bh * num_splits + s) * 2 + 1] * f;
-    acc += part_o[(bh * num_splits + s) * D + d] * f;
+  for (int s0 = 0; s0 < num_splits; s0 += 8) {
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool on = s0 + i < num_splits;
+      ms[i] = on ? ml[(s0 + i) * 2] : -INFINITY;
+      ls[i] = on ? ml[(s0 + i) * 2 + 1] : 0.f;
+      os[i] = on ? po[(long long)(s0 + i) * D] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // in split order: the same sum in every launch
+      const float f = ms[i] == -INFINITY ? 0.f : exp2f(ms[i] - mm);
+      ll += ls[i] * f;
+      acc += os[i] * f;
+    }
   }
   out[bh * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
 }
