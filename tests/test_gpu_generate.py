@@ -225,3 +225,43 @@ def test_generation_with_head_size_64_through_decode_graphs(tmp_path, dtype):
                 assert row.max().item() - row[tok].item() <= 2 * TOL[dtype] * scale, f"token {i}"
     if device() != "cpu":
         assert llm.engine.decode_graphs.replays > 0
+
+
+@pytest.mark.needs_cuda
+def test_command_line_writes_a_random_model_and_generates_from_it(tmp_path):
+    """`random-model` writes a folder from a config and a seed; `generate` loads it and prints one JSON line per
+    prompt.  The greedy tokens are those of the plain implementation on the same weights."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from tiny_configs import TINY_A
+    from ullm_b200.weights.safetensors_io import SafetensorsFile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY_A))
+    model = tmp_path / "model"
+    env = dict(os.environ, PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "ullm_b200.engine.cli", "random-model", "--out", str(model), "--config",
+                        str(cfg_path), "--seed", "3", "--std", "0.05", "--norm-std", "0.1"],
+                       capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert (model / "config.json").is_file() and (model / "model.safetensors").is_file()
+    prompts = [random_ids(256, 9, 1), random_ids(256, 21, 2)]
+    cmd = [sys.executable, "-m", "ullm_b200.engine.cli", "generate", "--model", str(model), "--max-bs", "2",
+           "--context-len", "64", "--page-size", "4", "--num-pages", "40", "--temperature", "0", "--ignore-eos",
+           "--max-new-tokens", "7"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 2
+    f = SafetensorsFile(str(model / "model.safetensors"))
+    w = {k: f.get(k).float().clone() for k in f.names()}
+    f.close()
+    for p, out in zip(prompts, lines):
+        assert out["prompt_tokens"] == len(p) and out["finish_reason"] == "LENGTH"
+        assert out["token_ids"] == pm.greedy_generate(p, w, TINY_A, 7)
