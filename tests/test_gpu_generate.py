@@ -265,3 +265,55 @@ def test_command_line_writes_a_random_model_and_generates_from_it(tmp_path):
     for p, out in zip(prompts, lines):
         assert out["prompt_tokens"] == len(p) and out["finish_reason"] == "LENGTH"
         assert out["token_ids"] == pm.greedy_generate(p, w, TINY_A, 7)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_workloads_through_the_engine_follow_the_plain_implementation(tmp_path, seed, monkeypatch):
+    """Random prompts (some share a prefix), random lengths to generate, random arrival (a few requests are added
+    while others decode), a small pool (preemption and page reuse), a small token budget (chunked prompts),
+    decode graphs of every size recorded in mid-stream: every request's greedy tokens are those of the plain
+    implementation, and every page comes back."""
+    import random
+
+    from ullm_b200 import SamplingParams
+
+    monkeypatch.setenv("ULLM_B200_MIN_GRAPH_BATCH", "1")
+    rng = random.Random(100 + seed)
+    llm, cfg, w = make_llm(tmp_path, "B", max_bs=4, max_num_batched_tokens=rng.choice([8, 24, 64]),
+                           num_pages=rng.choice([10, 14, 40]))
+    V = cfg["vocab_size"]
+    shared = random_ids(V, 33, 500 + seed)
+    reqs = []
+    for i in range(9):
+        n = rng.choice([1, 2, 5, 16, 17, 31, 40, 64])
+        p = random_ids(V, n, 600 + 10 * seed + i)
+        if rng.random() < 0.3:
+            p = shared + p[:8]
+        reqs.append((p, rng.choice([1, 2, 7, 15, 24])))
+    eng = llm.engine
+    got = {}
+    pending = list(enumerate(reqs))
+    rng.shuffle(pending)
+    live = 0
+    steps = 0
+    while pending or eng.has_unfinished_sequences():
+        # a new arrival now and then, otherwise step
+        if pending and (live == 0 or rng.random() < 0.25):
+            i, (p, n_new) = pending.pop()
+            eng.add_sequence(f"r{i}", p, SamplingParams(temperature=0.0, max_new_tokens=n_new, ignore_eos=True))
+            got[i] = []
+            live += 1
+            continue
+        for res in eng.step():
+            i = int(res.seq_id[1:])
+            if res.new_token_id >= 0:
+                got[i].append(res.new_token_id)
+            if res.is_finished:
+                live -= 1
+        steps += 1
+        assert steps < 5000, "the engine does not finish"
+    for i, (p, n_new) in enumerate(reqs):
+        assert got[i] == pm.greedy_generate(p, w, cfg, n_new), f"request {i}: prompt of {len(p)}, {n_new} new tokens"
+    cache = eng.runner.cache
+    cache.check_invariants()
+    assert not cache.requests
