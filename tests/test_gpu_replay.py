@@ -290,3 +290,45 @@ def test_real_widths_two_layers(tmp_path, dtype):
     ref = plain_logits(ids, w, cfg)
     got = run_cut(runner, "a", ids, [40] + [1] * 8)
     assert_close(got, ref, dtype, "0.6B widths")
+
+
+@pytest.mark.needs_cuda
+def test_long_context_at_real_widths_prompt_portions_against_decode_steps():
+    """Two layers at Qwen3-8B widths (hidden 4096, 32 heads, 8 kv heads, head size 128), bfloat16, random weights
+    made on the device, 8,192 tokens of context.  The same history is built twice: request a by prompt portions
+    of 2,048 tokens (the tcgen05 attention over pages), request b with its last tokens one by one (the split decode
+    attention).  No plain implementation runs at this size: the two paths are compared with each other, at the
+    tolerance they each have against the plain implementation."""
+    from helpers import TOL, TOL_RMS
+    from ullm_b200.engine import ModelRunner, StepEntry
+
+    cfg = {
+        "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936,
+        "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": False,
+        "max_position_embeddings": 16384, "torch_dtype": "bfloat16",
+    }
+    N = 8192
+    r = ModelRunner(config=cfg, dtype="bfloat16", page_size=16, num_pages=2 * (N // 16) + 8, max_requests=2,
+                    max_context=N + 16, max_step_tokens=2048, load_format="random", seed=4, poison_cache=True)
+    ids = random_ids(cfg["vocab_size"], N + 4, 77)
+    r.add_request("a")
+    for at in range(0, N, 2048):
+        by_portions = r.step([StepEntry("a", ids[at:at + 2048], [2047])]).float().cpu().clone()
+    r.add_request("b")
+    for at in range(0, N - 2048, 2048):
+        r.step([StepEntry("b", ids[at:at + 2048], [])])
+    r.step([StepEntry("b", ids[N - 2048:N - 3], [])])
+    for k in range(3):
+        one_by_one = r.step([StepEntry("b", [ids[N - 3 + k]], [0])]).float().cpu().clone()
+    r.check_device_status()
+    scale = by_portions.abs().max().item()
+    diff = (by_portions - one_by_one).abs()
+    assert torch.isfinite(one_by_one).all() and scale > 0
+    assert diff.max().item() <= TOL["bfloat16"] * scale, f"max {diff.max().item() / scale:.2e} of scale"
+    assert diff.pow(2).mean().sqrt().item() <= TOL_RMS["bfloat16"] * scale
+    assert int(by_portions.argmax()) == int(one_by_one.argmax())
+    # both requests decode on, side by side: same history, same next token
+    lg = r.step([StepEntry("a", [ids[N]], [0]), StepEntry("b", [ids[N]], [0])]).float().cpu()
+    assert (lg[0] - lg[1]).abs().max().item() <= TOL["bfloat16"] * scale
+    r.check_device_status()
