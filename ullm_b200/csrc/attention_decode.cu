@@ -17,56 +17,7 @@
 //
 // The grid depends on the batch size and the split count only, never on the
 // lengths, so a captured launch stays valid as the requests grow.
-#include "common.cuh"
-
-#define DEC_WARPS 4
-#define DEC_TILE 16   // keys per warp iteration
-#define DEC_STAGES 3
-
-__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool pred) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  const int n = pred ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3,
-                                                  const void* p) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
-
-// shared memory of one block: per warp a ring of K and V tiles; afterwards reused for the merge
-template <int D>
-struct DecodeSmem {
-  static constexpr int ROW_BYTES = D * 2;
-  static constexpr int TILE_BYTES = DEC_TILE * ROW_BYTES;
-  static constexpr int WARP_BYTES = DEC_STAGES * 2 * TILE_BYTES;
-  static constexpr int RING_BYTES = DEC_WARPS * WARP_BYTES;
-  static constexpr int MERGE_BYTES = DEC_WARPS * 16 * (D + 2) * 4;
-  static constexpr int BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
-};
+#include "decode_core.cuh"
 
 template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
