@@ -317,3 +317,17 @@ def test_random_workloads_through_the_engine_follow_the_plain_implementation(tmp
     cache = eng.runner.cache
     cache.check_invariants()
     assert not cache.requests
+
+
+@pytest.mark.needs_cuda
+def test_pool_sized_from_free_memory_when_no_page_count_is_given(tmp_path):
+    """Without `num_pages` the pool comes from the free device memory times `gpu_memory_utilization`, capped at
+    twice what `max_bs` requests of `context_len` tokens can hold; generation works on it."""
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "A", num_pages=None, max_bs=3, context_len=64, gpu_memory_utilization=0.5)
+    cache = llm.engine.runner.cache
+    assert cache.num_pages == 3 * (64 // 4) * 2
+    p = random_ids(256, 12, 3)
+    o = llm.generate_batch([p], SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True))[0]
+    assert o.token_ids == pm.greedy_generate(p, w, cfg, 6)
