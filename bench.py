@@ -370,6 +370,8 @@ def run_linear_probe(args) -> int:
         t = {"library": timeit(lambda i: torch.mm(x, ws[i].t(), out=out), copies)}
         if M <= 64:
             t["tcgen05"] = timeit(lambda i: K.small_m_linear(x, ws[i], out), copies)
+        else:
+            t["tcgen05"] = timeit(lambda i: K.large_linear(x, ws[i], out), copies)
         if M <= 32:
             t["skinny"] = timeit(lambda i: K.skinny_linear(x, ws[i], out), copies)
         line = "  ".join(f"{k} {v:7.1f} ({nbytes / v / 1e6:4.2f} TB/s)" for k, v in t.items())
@@ -379,6 +381,8 @@ def run_linear_probe(args) -> int:
             t = {"library+act_mul": timeit(lambda i: (torch.mm(x, ws[i].t(), out=out), K.act_mul(out, act, 0)), copies)}
             if M <= 64:
                 t["tcgen05 fused"] = timeit(lambda i: K.small_m_linear(x, ws[i], act, None, 0), copies)
+            else:
+                t["tcgen05 fused"] = timeit(lambda i: K.large_linear(x, ws[i], act, None, 0), copies)
             if M <= 32:
                 t["skinny fused"] = timeit(lambda i: K.skinny_linear(x, ws[i], act, None, 0), copies)
             print("         with the gate activation:  " + "  ".join(f"{k} {v:7.1f}" for k, v in t.items()))

@@ -533,6 +533,45 @@ def test_skinny_linear_is_deterministic_and_refuses_what_it_does_not_take():
                                  torch.empty(4, 128, dtype=torch.bfloat16, device="cuda"))
 
 
+@pytest.mark.parametrize("M,N,Kd", [
+    (128, 256, 64), (2048, 4096, 4096), (300, 1000, 520), (65, 331, 80), (1, 128, 64), (513, 777, 4104),
+    (2048, 6144, 1024), (129, 130, 72),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_large_linear_tcgen05(M, N, Kd, out_dtype):
+    """The persistent tcgen05 product for many rows against a float32 reference, with and without bias: sizes
+    that are no multiple of the 128 x 256 tile or of the 64-wide k block, more tiles than blocks (several tiles
+    per block through both accumulators), fewer tiles than blocks."""
+    x = rnd(M, Kd, seed=150, dtype=torch.bfloat16)
+    w = rnd(N, Kd, seed=151, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(N, seed=152, dtype=torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for b in (None, bias):
+        out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+        assert K().large_linear(x, w, out, b)
+        K().raise_on_status()
+        r = ref + (b.float() if b is not None else 0)
+        err = (out.float() - r).abs().max().item() / max(r.abs().max().item(), 1e-6)
+        assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+
+
+@pytest.mark.parametrize("M,I,Kd,act", [(128, 128, 64, 0), (2048, 3072, 1024, 0), (300, 200, 520, 1), (77, 331, 264, 0)])
+def test_large_linear_tcgen05_with_fused_gate_activation(M, I, Kd, act):
+    x = rnd(M, Kd, seed=160, dtype=torch.bfloat16)
+    w = rnd(2 * I, Kd, seed=161, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(2 * I, seed=162, dtype=torch.bfloat16)
+    for b in (None, bias):
+        y = x.float() @ w.float().t() + (b.float() if b is not None else 0)
+        g, u = y[:, :I], y[:, I:]
+        ref = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, I), 7.0, dtype=out_dtype, device="cuda")
+            assert K().large_linear(x, w, out, b, act)
+            K().raise_on_status()
+            err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+            assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+
+
 def test_small_m_linear_is_deterministic_and_independent_of_other_rows():
     """Partial sums of a tile are added in block order whoever arrives last: repeated launches give the same
     bits; a row's result does not depend on how many other rows the batch has."""
