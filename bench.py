@@ -371,7 +371,8 @@ def run_linear_probe(args) -> int:
         if M <= 64:
             t["tcgen05"] = timeit(lambda i: K.small_m_linear(x, ws[i], out), copies)
         else:
-            t["tcgen05"] = timeit(lambda i: K.large_linear(x, ws[i], out), copies)
+            t["tcgen05 128-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], out, None, None, 1), copies)
+            t["256-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], out, None, None, 2), copies)
         if M <= 32:
             t["skinny"] = timeit(lambda i: K.skinny_linear(x, ws[i], out), copies)
         line = "  ".join(f"{k} {v:7.1f} ({nbytes / v / 1e6:4.2f} TB/s)" for k, v in t.items())
@@ -382,7 +383,8 @@ def run_linear_probe(args) -> int:
             if M <= 64:
                 t["tcgen05 fused"] = timeit(lambda i: K.small_m_linear(x, ws[i], act, None, 0), copies)
             else:
-                t["tcgen05 fused"] = timeit(lambda i: K.large_linear(x, ws[i], act, None, 0), copies)
+                t["tcgen05 fused 128-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], act, None, 0, 1), copies)
+                t["256-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], act, None, 0, 2), copies)
             if M <= 32:
                 t["skinny fused"] = timeit(lambda i: K.skinny_linear(x, ws[i], act, None, 0), copies)
             print("         with the gate activation:  " + "  ".join(f"{k} {v:7.1f}" for k, v in t.items()))

@@ -538,25 +538,29 @@ def test_skinny_linear_is_deterministic_and_refuses_what_it_does_not_take():
     (2048, 6144, 1024), (129, 130, 72),
 ])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_large_linear_tcgen05(M, N, Kd, out_dtype):
-    """The persistent tcgen05 product for many rows against a float32 reference, with and without bias: sizes
-    that are no multiple of the 128 x 256 tile or of the 64-wide k block, more tiles than blocks (several tiles
-    per block through both accumulators), fewer tiles than blocks."""
+@pytest.mark.parametrize("variant", [1, 2])
+def test_large_linear_tcgen05(M, N, Kd, out_dtype, variant):
+    """The persistent tcgen05 product for many rows against a float32 reference, with and without bias, with
+    tiles of 128 rows (variant 1) and of 256 rows (variant 2): sizes that are no multiple of the tile or of the
+    64-wide k block, more tiles than blocks (several tiles per block through both accumulators), fewer tiles
+    than blocks."""
     x = rnd(M, Kd, seed=150, dtype=torch.bfloat16)
     w = rnd(N, Kd, seed=151, dtype=torch.bfloat16, scale=0.05)
     bias = rnd(N, seed=152, dtype=torch.bfloat16)
     ref = x.float() @ w.float().t()
     for b in (None, bias):
         out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
-        assert K().large_linear(x, w, out, b)
+        assert K().large_linear(x, w, out, b, None, variant)
         K().raise_on_status()
         r = ref + (b.float() if b is not None else 0)
         err = (out.float() - r).abs().max().item() / max(r.abs().max().item(), 1e-6)
         assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
 
 
-@pytest.mark.parametrize("M,I,Kd,act", [(128, 128, 64, 0), (2048, 3072, 1024, 0), (300, 200, 520, 1), (77, 331, 264, 0)])
-def test_large_linear_tcgen05_with_fused_gate_activation(M, I, Kd, act):
+@pytest.mark.parametrize("M,I,Kd,act", [(128, 128, 64, 0), (2048, 3072, 1024, 0), (300, 200, 520, 1), (77, 331, 264, 0),
+                                          (1100, 20000, 136, 0)])
+@pytest.mark.parametrize("variant", [1, 2])
+def test_large_linear_tcgen05_with_fused_gate_activation(M, I, Kd, act, variant):
     x = rnd(M, Kd, seed=160, dtype=torch.bfloat16)
     w = rnd(2 * I, Kd, seed=161, dtype=torch.bfloat16, scale=0.05)
     bias = rnd(2 * I, seed=162, dtype=torch.bfloat16)
@@ -566,7 +570,7 @@ def test_large_linear_tcgen05_with_fused_gate_activation(M, I, Kd, act):
         ref = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, I), 7.0, dtype=out_dtype, device="cuda")
-            assert K().large_linear(x, w, out, b, act)
+            assert K().large_linear(x, w, out, b, act, variant)
             K().raise_on_status()
             err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
             assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"

@@ -243,6 +243,196 @@ linear_tcgen05_large_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product with tiles of 256 rows of x: two 128-row halves share every tile of W in shared memory, so a
+// block loads 64 KB for 1,024 tensor-core clocks instead of 48 KB for 512 (two thirds of the traffic from L2,
+// which is what bounds the kernel above).  The two halves' accumulators fill all 512 columns of tensor memory:
+// there is no spare one, so the epilogue drains half 0, then half 1, while the next tile's products start on
+// half 0 as soon as it is drained.  Ring of three 64 KB stages.
+// ---------------------------------------------------------------------------------------------
+#define LG2_BM 256
+#define LG2_STAGES 3
+#define LG2_A_BYTES (LG2_BM * 128)
+#define LG2_STAGE_BYTES (LG2_A_BYTES + LG_B_BYTES)
+
+__global__ void __launch_bounds__(LG_THREADS, 1)
+linear_tcgen05_large2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                             const LgParams p) {
+  extern __shared__ unsigned char lg_smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[LG2_STAGES], empty_bar[LG2_STAGES], acc_full, acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int wait_flag[2];
+  pdl_launch_dependents();
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)lg_smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long num_tiles = (long long)p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < LG2_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_full, 1);
+    mbar_init(&acc_empty[0], 4);
+    mbar_init(&acc_empty[1], 4);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lin_smem(&tmem_base_slot)),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_base_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: TMA loads (256 rows of x in one box, 256 rows of W in one box) ------------------
+      int s = 0;
+      uint32_t parity = 1;  // a fresh barrier passes a wait on parity 1
+      for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int mt = (int)(tile % p.m_tiles), nt = (int)(tile / p.m_tiles);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], parity)) {
+            ullm_report(p.status, ULLM_STATUS_TIMEOUT, 41, kb);
+            tile = num_tiles;
+            break;
+          }
+          unsigned char* a = tiles + s * LG2_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], LG2_STAGE_BYTES);
+          tma_load_2d(a, &map_x, &full_bar[s], kb * LG_BK, mt * LG2_BM);
+          if (p.act == 0) tma_load_2d(a + LG2_A_BYTES, &map_w, &full_bar[s], kb * LG_BK, nt * LG_BN);
+          else tma_load_3d(a + LG2_A_BYTES, &map_w, &full_bar[s], kb * LG_BK, nt * (LG_BN / 2), 0);
+          if (++s == LG2_STAGES) s = 0, parity ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----------------------------------------------------------------------
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(LG_BN >> 3) << 17) |
+                             ((uint32_t)(LG_BM >> 4) << 24);
+      const uint64_t desc0 = umma_desc(tiles);
+      const uint32_t desc_hi = (uint32_t)(desc0 >> 32), lo0 = (uint32_t)desc0;
+      const uint32_t full0 = lin_smem(&full_bar[0]), empty0 = lin_smem(&empty_bar[0]);
+      uint32_t a_lo = lo0, full_s = full0, empty_s = empty0;
+      int s = 0, it = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const uint32_t drained = (uint32_t)(it & 1) ^ 1;  // parity of "the epilogue of the tile before has drained"
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_addr(full_s, phase)) {
+            ullm_report(p.status, ULLM_STATUS_TIMEOUT, 42, kb);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a1_lo = a_lo + (LG_A_BYTES >> 4), b_lo = a_lo + (LG2_A_BYTES >> 4);
+          if (kb == 0) {
+            if (!mbar_wait(&acc_empty[0], drained)) {
+              ullm_report(p.status, ULLM_STATUS_TIMEOUT, 44, it);
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          }
+          // half 0: 16 bf16 = 32 bytes further along the swizzled row is +2 in the 16-byte address field
+          umma_bf16_lo<-1>(tmem_d, a_lo, b_lo, desc_hi, idesc, kb > 0 ? 1u : 0u);
+          umma_bf16_lo<1>(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc);
+          umma_bf16_lo<1>(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc);
+          umma_bf16_lo<1>(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc);
+          if (kb == 0) {
+            if (!mbar_wait(&acc_empty[1], drained)) {
+              ullm_report(p.status, ULLM_STATUS_TIMEOUT, 45, it);
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          }
+          umma_bf16_lo<-1>(tmem_d + LG_BN, a1_lo, b_lo, desc_hi, idesc, kb > 0 ? 1u : 0u);
+          umma_bf16_lo<1>(tmem_d + LG_BN, a1_lo + 2, b_lo + 2, desc_hi, idesc);
+          umma_bf16_lo<1>(tmem_d + LG_BN, a1_lo + 4, b_lo + 4, desc_hi, idesc);
+          umma_bf16_lo<1>(tmem_d + LG_BN, a1_lo + 6, b_lo + 6, desc_hi, idesc);
+          umma_commit_addr(empty_s);  // the stage is free once these MMAs have read it
+          a_lo += (LG2_STAGE_BYTES >> 4), full_s += 8, empty_s += 8;
+          if (++s == LG2_STAGES) s = 0, phase ^= 1, a_lo = lo0, full_s = full0, empty_s = empty0;
+        }
+        if (ok) umma_commit(&acc_full);  // both accumulators are complete once every MMA above is
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5; a warp reads the accumulator lanes 32 (warp % 4) .. + 31, half 0 then half 1 ----
+    const int quarter = warp & 3;
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    const __nv_bfloat16* bias = (const __nv_bfloat16*)p.bias;
+    int it = 0;
+    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int mt = (int)(tile % p.m_tiles), nt = (int)(tile / p.m_tiles);
+      // One thread waits (bounded) and tells the others, so that all 128 take the same way out.
+      if (et == 0) {
+        const bool got = mbar_wait(&acc_full, it & 1);
+        if (!got) ullm_report(p.status, ULLM_STATUS_TIMEOUT, 43, it);
+        wait_flag[it & 1] = got ? 1 : 0;
+      }
+      lg_epi_bar_sync();
+      if (wait_flag[it & 1] == 0) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int half = 0; half < 2; ++half) {
+        const int row = mt * LG2_BM + half * LG_BM + quarter * 32 + lane;
+        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * LG_BN);
+        if (p.act == 0) {
+#pragma unroll 2
+          for (int c = 0; c < LG_BN / 16; ++c) {
+            float v[16];
+            tmem_ld16(taddr + c * 16, v);
+            const int col0 = nt * LG_BN + c * 16;
+            if (bias != nullptr) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (col0 + i < p.N) v[i] += __bfloat162float(bias[col0 + i]);
+            }
+            lg_store16(p, row, col0, v);
+          }
+        } else {
+#pragma unroll 2
+          for (int c = 0; c < LG_BN / 32; ++c) {
+            float g[16], u[16];
+            tmem_ld16(taddr + c * 16, g);
+            tmem_ld16(taddr + LG_BN / 2 + c * 16, u);
+            const int col0 = nt * (LG_BN / 2) + c * 16;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float gv = g[i], uv = u[i];
+              if (bias != nullptr && col0 + i < p.n_out) {
+                gv += __bfloat162float(bias[col0 + i]);
+                uv += __bfloat162float(bias[p.n_out + col0 + i]);
+              }
+              g[i] = (p.act == 1 ? act_silu(gv) : act_gelu_tanh(gv)) * uv;
+            }
+            lg_store16(p, row, col0, g);
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[half]);  // the MMA warp may fill this half again
+      }
+    }
+  }
+  __syncwarp();  // the lanes of the two single-thread roles wait here for their lane 0
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(512) : "memory");
+  }
+}
+
 // Shapes this kernel takes: K a multiple of 8 (16-byte rows for TMA), 16-byte aligned bases; with an activation N
 // is even.  Any M (made for many rows: a tile holds 128).
 extern "C" int ullm_linear_tcgen05_large_supported(int M, int N, int K) {
@@ -253,7 +443,7 @@ static int g_lg_attr_set = 0;
 static int g_lg_sms = 0;
 
 extern "C" int ullm_linear_tcgen05_large(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                                         int out_f32, int act, int* status, void* stream) {
+                                         int out_f32, int act, int variant, int* status, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (!ullm_linear_tcgen05_large_supported(M, N, K)) return ULLM_ERR_UNSUPPORTED;
   if (act < 0 || act > 2 || (act != 0 && N % 2 != 0)) return ULLM_ERR_UNSUPPORTED;
@@ -271,26 +461,40 @@ extern "C" int ullm_linear_tcgen05_large(const void* x, const void* w, const voi
   p.K = K;
   p.act = act;
   p.n_out = act != 0 ? N / 2 : N;
-  p.m_tiles = (M + LG_BM - 1) / LG_BM;
   p.n_tiles = act != 0 ? (p.n_out + LG_BN / 2 - 1) / (LG_BN / 2) : (N + LG_BN - 1) / LG_BN;
   p.k_blocks = (K + LG_BK - 1) / LG_BK;
   p.out_f32 = out_f32;
   p.out = out;
   p.bias = bias;
   p.status = status;
+  // Tiles of 128 or of 256 rows of x.  The second form moves two thirds of the bytes per product (measured: 0.885
+  // of the time per tile-row where one round of tiles covers the product) but has half as many tiles to spread
+  // over the SMs, and its epilogue is not hidden behind the next tile's products, which costs more than the
+  // saved traffic where the epilogue is long (the gate activation) or runs many times per block.  So: rounds of
+  // tiles x cost of a tile (4 against 7) decides for plain products; with an activation the 128-row form
+  // stays.  `variant` forces one (1, 2) or lets that estimate choose (0).
+  const long long t1 = (long long)((M + LG_BM - 1) / LG_BM) * p.n_tiles,
+                  t2 = (long long)((M + LG2_BM - 1) / LG2_BM) * p.n_tiles;
+  const long long c1 = ((t1 + g_lg_sms - 1) / g_lg_sms) * 4, c2 = ((t2 + g_lg_sms - 1) / g_lg_sms) * 7;
+  const bool two = variant == 2 || (variant == 0 && act == 0 && M > LG_BM && c2 < c1);
+  const int bm = two ? LG2_BM : LG_BM;
+  p.m_tiles = (M + bm - 1) / bm;
   const long long tiles = (long long)p.m_tiles * p.n_tiles;
   const int blocks = (int)(tiles < g_lg_sms ? tiles : g_lg_sms);
   CUtensorMap map_x, map_w;
-  if (!get_map(x, M, K, LG_BM, &map_x) || !get_map(w, N, K, act != 0 ? -(LG_BN / 2) : LG_BN, &map_w))
+  if (!get_map(x, M, K, bm, &map_x) || !get_map(w, N, K, act != 0 ? -(LG_BN / 2) : LG_BN, &map_w))
     return ULLM_ERR_LAUNCH;
-  const size_t smem = (size_t)LG_STAGES * LG_STAGE_BYTES + 1024;
+  const size_t smem = (two ? (size_t)LG2_STAGES * LG2_STAGE_BYTES : (size_t)LG_STAGES * LG_STAGE_BYTES) + 1024;
   if (!g_lg_attr_set) {
-    if (cudaFuncSetAttribute(linear_tcgen05_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(linear_tcgen05_large_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(LG_STAGES * LG_STAGE_BYTES + 1024)) != cudaSuccess ||
+        cudaFuncSetAttribute(linear_tcgen05_large2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(LG2_STAGES * LG2_STAGE_BYTES + 1024)) != cudaSuccess)
       return ULLM_ERR_LAUNCH;
     g_lg_attr_set = 1;
   }
-  int rc = ullm_launch_kernel(linear_tcgen05_large_kernel, dim3(blocks), dim3(LG_THREADS), smem, st, map_x, map_w, p);
+  int rc = two ? ullm_launch_kernel(linear_tcgen05_large2_kernel, dim3(blocks), dim3(LG_THREADS), smem, st, map_x, map_w, p)
+               : ullm_launch_kernel(linear_tcgen05_large_kernel, dim3(blocks), dim3(LG_THREADS), smem, st, map_x, map_w, p);
   if (rc != ULLM_OK) return rc;
   return ullm_launch_status();
 }

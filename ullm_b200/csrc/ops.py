@@ -120,7 +120,7 @@ class Kernels:
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
-            "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, P, P],
+            "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -224,7 +224,7 @@ class Kernels:
                     f"linear_skinny ({M}x{K} . {N}x{K})")
         return True
 
-    def large_linear(self, x, weight, out, bias=None, act: int | None = None) -> bool:
+    def large_linear(self, x, weight, out, bias=None, act: int | None = None, variant: int = 0) -> bool:
         """The persistent tcgen05/TMA product for many rows (prompt portions): tiles of 128 x 256, two accumulators
         in tensor memory, bias and the gate activation in the epilogue.  Same contract as `small_m_linear`."""
         M, K = x.shape
@@ -239,7 +239,8 @@ class Kernels:
             return False
         self._check(self.lib.ullm_linear_tcgen05_large(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), M, N, K,
                                                        1 if out.dtype == torch.float32 else 0,
-                                                       0 if act is None else act + 1, _ptr(self.status), _stream()),
+                                                       0 if act is None else act + 1, variant, _ptr(self.status),
+                                                       _stream()),
                     f"linear_tcgen05_large ({M}x{K} . {N}x{K})")
         return True
 
