@@ -15,7 +15,7 @@ def __getattr__(name):
         from .config import EngineConfig
 
         return EngineConfig
-    if name in ("SamplingParams", "FinishReason", "GenerateOutput"):
+    if name in ("SamplingParams", "FinishReason", "GenerateOutput", "EngineDeadError"):
         from .sampling import params
 
         return getattr(params, name)

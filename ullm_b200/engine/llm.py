@@ -24,7 +24,7 @@ import uuid
 from typing import AsyncGenerator
 
 from ..config.engine_config import EngineConfig
-from ..sampling.params import FinishReason, GenerateOutput, RequestOutput, SamplingParams
+from ..sampling.params import EngineDeadError, FinishReason, GenerateOutput, RequestOutput, SamplingParams
 from .engine import Engine
 
 
@@ -51,6 +51,18 @@ class LLM:
         self.tokenizer = init_tokenizer(config.model)
         self.request_states: dict[str, asyncio.Queue] = {}
         self._loop_task: asyncio.Task | None = None
+        self.is_dead = False  # set when a step raised: every later call raises EngineDeadError
+
+    def _check_alive(self) -> None:
+        if self.is_dead:
+            raise EngineDeadError()
+
+    def _step(self):
+        try:
+            return self.engine.step()
+        except Exception:
+            self.is_dead = True
+            raise
 
     # -- text <-> ids ----------------------------------------------------------------
     def tokenize(self, texts: list[str]) -> list[list[int]]:
@@ -78,7 +90,7 @@ class LLM:
     async def _engine_loop(self) -> None:
         try:
             while self.engine.has_unfinished_sequences():
-                results = await asyncio.to_thread(self.engine.step)
+                results = await asyncio.to_thread(self._step)
                 for r in results:
                     q = self.request_states.get(r.seq_id)
                     if q is None:
@@ -100,6 +112,7 @@ class LLM:
         params: SamplingParams | None = None,
         sequence_id: str | None = None,
     ) -> AsyncGenerator[GenerateOutput, None]:
+        self._check_alive()
         if sequence_id is None:
             sequence_id = uuid.uuid4().hex
         try:
@@ -122,6 +135,9 @@ class LLM:
             raise
 
     def abort(self, sequence_id: str) -> None:
+        if self.is_dead:  # nothing to take back from an engine that is not stepped again
+            self.request_states.pop(sequence_id, None)
+            return
         if sequence_id in self.request_states:
             self.engine.abort_sequence(sequence_id)
             del self.request_states[sequence_id]
@@ -134,6 +150,7 @@ class LLM:
     async def profile(self, action: str) -> None:
         """"start" / "stop" per-step timing (the reference starts and stops a
         torch profiler, ullm/core/engine.py:210-238)."""
+        self._check_alive()
         self.engine.profile_steps = action == "start"
 
     # -- synchronous batch --------------------------------------------------------------
@@ -145,6 +162,7 @@ class LLM:
     ) -> list[RequestOutput]:
         """Runs all prompts to completion under continuous batching and returns
         them in the order given."""
+        self._check_alive()
         plist = params if isinstance(params, list) else [params] * len(prompts)
         ids_list, order = [], []
         for i, (pr, pa) in enumerate(zip(prompts, plist)):
@@ -156,7 +174,7 @@ class LLM:
         got: dict[str, list[int]] = {sid: [] for sid in order}
         reason: dict[str, FinishReason | None] = {}
         while len(reason) < len(order) and self.engine.has_unfinished_sequences():
-            for r in self.engine.step():
+            for r in self._step():
                 if r.seq_id not in got:
                     continue
                 if r.new_token_id >= 0:

@@ -47,6 +47,17 @@ class GenerateOutput:
     token_id: int = -1
 
 
+class EngineDeadError(Exception):
+    """Raised by the entry point's calls once a step of the engine has failed (ullm/core/common.py:46-54: there
+    the engine is a process that has exited; here it lives in this process and is not stepped again after a
+    step raised, since the cache and the requests in flight are in an unknown state)."""
+
+    MESSAGE = "The engine has failed and takes no more requests."
+
+    def __init__(self, message: str = MESSAGE, *args):
+        super().__init__(message, *args)
+
+
 @dataclass
 class EngineStepResult:
     """ullm/core/common.py:36-43."""
