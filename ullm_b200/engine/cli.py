@@ -3,8 +3,8 @@
 and meanings here, and offline use, which the reference leaves to scripts
 (bench.py), gets sub-commands:
 
-    python -m ullm_b200.engine.cli generate --model DIR --prompt-ids 1,2,3 --max-new-tokens 16
-    python -m ullm_b200.engine.cli random-model --out DIR --config config.json --seed 0
+    python -m ullm_b200 generate --model DIR --prompt-ids 1,2,3 --max-new-tokens 16
+    python -m ullm_b200 random-model --out DIR --config config.json --seed 0
 """
 
 from __future__ import annotations
