@@ -406,7 +406,7 @@ def run_decode_attention_probe(args) -> int:
 
     K = kernels()
     Hq, Hkv, D, page = (QWEN3_8B["num_attention_heads"], QWEN3_8B["num_key_value_heads"], QWEN3_8B["head_dim"],
-                        PAGE_SIZE)
+                        args.page_size)
     pk = peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
@@ -433,8 +433,8 @@ def run_decode_attention_probe(args) -> int:
         cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
         kvl = torch.tensor(lens, dtype=torch.int32, device="cuda")
         res, outs = {}, []
-        for balanced in (False, True):
-            K.use_balanced_decode = balanced
+        for mode in ("split", "balanced", "tcgen05"):
+            K.use_balanced_decode, K.use_tcgen05_decode = mode == "balanced", mode == "tcgen05"
             out = torch.empty(B, Hq * D, device="cuda", dtype=torch.bfloat16)
             ts = []
             for _ in range(7):
@@ -445,12 +445,13 @@ def run_decode_attention_probe(args) -> int:
                 e1.record()
                 torch.cuda.synchronize()
                 ts.append(e0.elapsed_time(e1) * 1000)
-            res[balanced] = statistics.median(ts[2:])
+            res[mode] = statistics.median(ts[2:])
             outs.append(out.float())
         mb = sum(lens) * Hkv * D * 2 * 2 / 1e6
         print(f"{name:28s} K+V {mb:7.1f} MB  at the copy peak {mb / pk['hbm_gbs'] * 1e3:6.1f} us   "
-              f"per-request splits {res[False]:7.1f} us   batch-balanced {res[True]:7.1f} us   "
-              f"(largest difference of the outputs {(outs[0] - outs[1]).abs().max().item():.1e})")
+              f"per-request splits {res['split']:7.1f} us   batch-balanced {res['balanced']:7.1f} us   "
+              f"tcgen05 {res['tcgen05']:7.1f} us   (largest differences of the outputs "
+              f"{(outs[0] - outs[1]).abs().max().item():.1e}, {(outs[0] - outs[2]).abs().max().item():.1e})")
 
     random.seed(1)
     case("8 x 2048", [2048] * 8)
@@ -598,6 +599,7 @@ def main() -> int:
     ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

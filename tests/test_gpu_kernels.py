@@ -304,14 +304,18 @@ class _DecodeCtx:
 
 @pytest.mark.parametrize("Hq,Hkv,D,page,window", [
     (32, 8, 128, 16, 0), (8, 8, 128, 16, 0), (16, 1, 64, 16, 0), (12, 3, 64, 8, 0), (6, 2, 128, 32, 0),
-    (32, 8, 128, 16, 100), (4, 2, 64, 4, 37), (9, 3, 128, 1, 0),
+    (32, 8, 128, 16, 100), (4, 2, 64, 4, 37), (9, 3, 128, 1, 0), (24, 2, 128, 8, 0), (16, 1, 128, 128, 300),
 ])
 @pytest.mark.parametrize("batch", [1, 3, 40])
-@pytest.mark.parametrize("balanced", [False, True])
-def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, balanced):
-    """The two split tensor-core decode kernels (every request split alike; the whole batch's keys cut evenly
-    over the blocks) against the plain reference: contexts of 1 token, around page and tile edges, and long
-    ones, ragged within a batch; padding rows (length 0) give zeros."""
+@pytest.mark.parametrize("mode", ["split", "balanced", "tcgen05"])
+def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, mode):
+    """The three tensor-core decode kernels (every request split alike; the whole batch's keys cut evenly over
+    the warps; the same over the blocks with the products on tcgen05) against the plain reference: contexts of
+    1 token, around page and tile edges, and long ones, ragged within a batch; padding rows (length 0) give
+    zeros."""
+    balanced = mode == "balanced"
+    if mode == "tcgen05" and not K().lib.ullm_decode_attention_tcgen05_supported(D, Hq, Hkv, batch, page):
+        pytest.skip("the tcgen05 decode kernel takes head size 128 and pages of 8 to 128 tokens")
     dtype = torch.bfloat16
     lens = [1, 15, 16, 17, 63, 64, 65, 300, 1000, 2049, 0, 33, 129, 511, 77, 5]
     kv_lens = [lens[(i * 7 + batch) % len(lens)] for i in range(batch)]
@@ -344,16 +348,16 @@ def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, balanced):
     out = torch.full((batch, Hq * D), 9.0, dtype=dtype, device="cuda")
     scale = D ** -0.5
     ctx = _DecodeCtx(batch)
-    old = K().use_balanced_decode
-    K().use_balanced_decode = balanced
+    old = K().use_balanced_decode, K().use_tcgen05_decode
+    K().use_balanced_decode, K().use_tcgen05_decode = balanced, mode == "tcgen05"
     try:
         K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
                             torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window,
                             scale, ctx)
     finally:
-        K().use_balanced_decode = old
+        K().use_balanced_decode, K().use_tcgen05_decode = old
     K().raise_on_status()
-    assert K().attention_path == ("decode_balanced" if balanced else "decode")
+    assert K().attention_path == {"split": "decode", "balanced": "decode_balanced", "tcgen05": "decode_tcgen05"}[mode]
     live = [r for r, kl in enumerate(kv_lens) if kl > 0]
     ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(batch, Hq, D)[live],
                               torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),

@@ -231,7 +231,8 @@ def test_bf16_engine_uses_the_tensor_core_attention_kernels(tmp_path):
         runner.step([StepEntry("a", ids[:39], [38])])
         assert kernels().attention_path == ("prefill_tcgen05" if tag == "E" else "prefill")
         runner.step([StepEntry("a", ids[39:], [0])])
-        assert kernels().attention_path == "decode"
+        # (ULLM_B200_DECODE_TC=1 sends head size 128 to the tcgen05 decode kernel instead)
+        assert kernels().attention_path == ("decode_tcgen05" if kernels().use_tcgen05_decode and tag == "E" else "decode")
         runner, cfg, w, page = make_runner(tmp_path, tag, "float32", num_pages=8)
         runner.add_request("a")
         runner.step([StepEntry("a", ids[:39], [38])])
@@ -259,7 +260,8 @@ def test_decode_batches_of_very_unequal_lengths_take_the_balanced_attention_kern
     for k in range(8):
         ctx_entries = [StepEntry(r, [ids[r][n + k]], [0]) for r, n in lens.items()]
         lg = runner.step(ctx_entries)
-        assert kernels().attention_path == "decode_balanced"
+        assert kernels().attention_path == ("decode_tcgen05" if kernels().use_tcgen05_decode and tag == "E"
+                                            else "decode_balanced")
         for row, (r, n) in enumerate(lens.items()):
             assert_close(lg[row:row + 1].float().cpu(), refs[r][[n + k]], "bfloat16", f"{r}, decode step {k}")
     runner.check_device_status()

@@ -85,6 +85,8 @@ class Kernels:
             self.lib.ullm_set_max_smem_carveout(1)
         self.decode_split_target = int(os.environ.get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
+        # decode attention on the tcgen05 tensor cores (head size 128), the batch's keys cut evenly over the blocks
+        self.use_tcgen05_decode = os.environ.get("ULLM_B200_DECODE_TC", "0") == "1"
         # decode attention: the batch's keys cut evenly over the warps (True), every request split alike (False),
         # or "auto": the first for batches of very unequal lengths (the step context says so), else the second
         mode = os.environ.get("ULLM_B200_DECODE_BALANCED", "auto")
@@ -121,6 +123,7 @@ class Kernels:
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
+            "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -134,6 +137,10 @@ class Kernels:
         L.ullm_decode_attention_balanced_supported.restype = c_int
         L.ullm_decode_attention_balanced_scratch_floats.argtypes = [I, I]
         L.ullm_decode_attention_balanced_scratch_floats.restype = c_longlong
+        L.ullm_decode_attention_tcgen05_supported.argtypes = [I, I, I, I, I]
+        L.ullm_decode_attention_tcgen05_supported.restype = c_int
+        L.ullm_decode_attention_tcgen05_scratch_floats.argtypes = [I]
+        L.ullm_decode_attention_tcgen05_scratch_floats.restype = c_longlong
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
         L.ullm_prefill_attention_tcgen05_supported.argtypes = [I, I, I, I]
@@ -406,24 +413,31 @@ class Kernels:
                 and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
             # one token per request: stream the pages once
             balanced = getattr(ctx, "ragged", False) if self.use_balanced_decode == "auto" else self.use_balanced_decode
-            if balanced and self.lib.ullm_decode_attention_balanced_supported(
-                    head_dim, num_q, num_kv, T, page_size):
+            tc = self.use_tcgen05_decode and self.lib.ullm_decode_attention_tcgen05_supported(
+                head_dim, num_q, num_kv, T, page_size) and qkv.stride(0) % head_dim == 0
+            if tc or (balanced and self.lib.ullm_decode_attention_balanced_supported(
+                    head_dim, num_q, num_kv, T, page_size)):
+                # both kernels cut the batch's keys evenly (over blocks, over warps) and share the scratch arrays
+                # and the merge kernel for the pairs that a cut went through
                 key = (head_dim, num_q, num_kv)
                 if key not in self._decb:
                     n = self.lib.ullm_decode_attention_balanced_scratch_floats(head_dim, num_q // num_kv)
+                    if head_dim == 128:
+                        n = max(n, self.lib.ullm_decode_attention_tcgen05_scratch_floats(num_q // num_kv))
                     if n <= 0:
-                        raise KernelError("decode_attention_balanced: cannot size its grid on this device")
+                        raise KernelError("decode attention: cannot size its grid on this device")
                     self._decb[key] = (torch.empty(n, dtype=torch.float32, device="cuda"),
                                        torch.zeros(513, dtype=torch.int32, device="cuda"),
                                        torch.zeros(512 * num_q, dtype=torch.int32, device="cuda"))
                 part, prefix, flags = self._decb[key]
-                self._check(self.lib.ullm_decode_attention_balanced(
+                fn = self.lib.ullm_decode_attention_tcgen05 if tc else self.lib.ullm_decode_attention_balanced
+                self._check(fn(
                     _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                     _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(part), _ptr(prefix), _ptr(flags), T, num_q, num_kv, head_dim,
                     page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
-                    f"decode_attention_balanced (head_dim {head_dim})")
+                    f"decode_attention_{'tcgen05' if tc else 'balanced'} (head_dim {head_dim})")
                 self.launches += 1  # the merge of the shared pairs
-                self.attention_path = "decode_balanced"
+                self.attention_path = "decode_tcgen05" if tc else "decode_balanced"
                 return
             splits = max(1, min(32, -(-self.decode_split_target // (T * num_kv))))
             scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32)
