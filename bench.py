@@ -368,6 +368,10 @@ def run_linear_probe(args) -> int:
         x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         t = {"library": timeit(lambda i: torch.mm(x, ws[i].t(), out=out), copies)}
+        if K.lt_linear(x, ws[0], out):  # times the library's candidates for this shape once
+            ch = K.lt_last_choice()
+            t[f"library, timed choice (#{ch['chosen']} of {ch['candidates']})"] = timeit(
+                lambda i: K.lt_linear(x, ws[i], out, tune=False), copies)
         if M <= 64:
             t["tcgen05"] = timeit(lambda i: K.small_m_linear(x, ws[i], out), copies)
         else:

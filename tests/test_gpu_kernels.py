@@ -661,3 +661,54 @@ def test_prefill_attention_tcgen05_mixed_batch(Hq, Hkv, page, window):
     got = out.view(T, Hq, D).float().cpu()
     assert torch.isfinite(got).all()
     close(got, ref, dtype)
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 64, 64), (16, 6144, 4096), (16, 200, 520), (64, 1000, 136), (256, 777 * 8, 264),
+                                     (5, 96, 8192)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_library_product_with_timed_choice(M, N, Kd, out_dtype):
+    """`lt_linear`: the vendor library's product through cuBLASLt, the algorithm chosen by timing the library's
+    candidates once per shape.  Whatever it chooses computes x W^T; the second call (no timing) gives the same
+    bits as the first (the choice is kept)."""
+    x = rnd(M, Kd, seed=170, dtype=torch.bfloat16)
+    w = rnd(N, Kd, seed=171, dtype=torch.bfloat16, scale=0.05)
+    ref = x.float() @ w.float().t()
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+    assert K().lt_linear(x, w, out)
+    err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+    assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+    again = torch.full((M, N), 3.0, dtype=out_dtype, device="cuda")
+    assert K().lt_linear(x, w, again)
+    assert torch.equal(out, again)
+    ch = K().lt_last_choice()
+    assert 0 <= ch["chosen"] < max(ch["candidates"], 1)
+
+
+def test_library_product_with_timed_choice_refuses_what_it_cannot_take():
+    x = rnd(4, 60, seed=1, dtype=torch.bfloat16)  # rows of 120 bytes: no 16-byte pieces
+    assert not K().lt_linear(x, rnd(16, 60, seed=2, dtype=torch.bfloat16), torch.empty(4, 16, dtype=torch.bfloat16, device="cuda"))
+    xf = rnd(4, 64, seed=1)  # float32 operands stay with the 32-bit path
+    assert not K().lt_linear(xf, rnd(16, 64, seed=2), torch.empty(4, 16, device="cuda"))
+
+
+def test_library_product_inside_a_stream_capture_takes_an_untimed_shape_without_timing():
+    """A shape first seen while a CUDA graph is being recorded cannot be timed (timing synchronises): it takes the
+    library's first candidate, the recording holds that launch, and the shape is timed at its next eager call."""
+    x = rnd(24, 320, seed=180, dtype=torch.bfloat16)
+    w = rnd(264, 320, seed=181, dtype=torch.bfloat16, scale=0.05)
+    out = torch.zeros(24, 264, dtype=torch.bfloat16, device="cuda")
+    ref = x.float() @ w.float().t()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g):
+            assert K().lt_linear(x, w, out)
+    assert (24, 264, 320, 0) not in K()._lt_tuned
+    g.replay()
+    torch.cuda.synchronize()
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+    out.zero_()
+    assert K().lt_linear(x, w, out)
+    assert (24, 264, 320, 0) in K()._lt_tuned
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()

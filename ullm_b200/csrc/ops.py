@@ -100,7 +100,12 @@ class Kernels:
             raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: 0, skinny or tcgen05")
         # rows from which the gated feed-forward's first product runs on the own tcgen05 kernel with the activation
         # fused (0 rows would mean always; a huge number never)
-        self.fused_mlp_rows = int(os.environ.get("ULLM_B200_FUSED_MLP_ROWS", "2048"))
+        self.fused_mlp_rows = int(os.environ.get("ULLM_B200_FUSED_MLP_ROWS", "4096"))
+        # rows up to which the library's product is called through cuBLASLt with a timed choice of algorithm
+        self.lt_rows = int(os.environ.get("ULLM_B200_LT_ROWS", str(1 << 30)))
+        self._lt_ok = None
+        self._lt_ws = None
+        self._lt_tuned = set()
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
@@ -124,6 +129,7 @@ class Kernels:
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_lt_linear": [P, P, P, I, I, I, I, P, LL, I, P, LL, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -141,6 +147,10 @@ class Kernels:
         L.ullm_decode_attention_tcgen05_supported.restype = c_int
         L.ullm_decode_attention_tcgen05_scratch_floats.argtypes = [I]
         L.ullm_decode_attention_tcgen05_scratch_floats.restype = c_longlong
+        L.ullm_lt_available.argtypes = []
+        L.ullm_lt_available.restype = c_int
+        L.ullm_lt_last_choice.argtypes = [P, P, P, P]
+        L.ullm_lt_last_choice.restype = None
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
         L.ullm_prefill_attention_tcgen05_supported.argtypes = [I, I, I, I]
@@ -251,6 +261,51 @@ class Kernels:
                     f"linear_tcgen05_large ({M}x{K} . {N}x{K})")
         return True
 
+    def lt_linear(self, x, weight, out, tune: bool = True) -> bool:
+        """out = x @ weight.T through cuBLASLt with a measured choice among the library's candidate algorithms
+        (timed once per shape, outside stream captures, with L2 flushed; kept for the life of the process).
+        bfloat16 operands, bfloat16 or float32 out, no bias.  False: not taken (the caller uses torch)."""
+        M, K = x.shape
+        N = weight.shape[0]
+        if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous()
+                or not weight.is_contiguous() or not out.is_contiguous() or weight.shape[1] != K
+                or out.shape != (M, N) or out.dtype not in (torch.bfloat16, torch.float32) or K % 8
+                or (out.dtype == torch.bfloat16 and N % 8)
+                or x.data_ptr() % 16 or weight.data_ptr() % 16 or out.data_ptr() % 16):
+            return False
+        if self._lt_ok is None:
+            self._lt_ok = bool(self.lib.ullm_lt_available())
+            if self._lt_ok:
+                self._lt_ws = torch.empty(32 << 20, dtype=torch.uint8, device="cuda")
+        if not self._lt_ok:
+            return False
+        out_f32 = 1 if out.dtype == torch.float32 else 0
+        key = (M, N, K, out_f32)
+        flush = None
+        if tune and key not in self._lt_tuned and not torch.cuda.is_current_stream_capturing():
+            flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")  # larger than L2; gone after this call
+            self._lt_tuned.add(key)
+        rc = self.lib.ullm_lt_linear(_ptr(x), _ptr(weight), _ptr(out), M, N, K, out_f32, _ptr(self._lt_ws),
+                                     self._lt_ws.numel(), 1 if flush is not None else 0, _ptr(flush),
+                                     0 if flush is None else flush.numel(), _stream())
+        if rc == 4:  # a shape the library has no candidate for
+            return False
+        self._check(rc, f"lt_linear ({M}x{K} . {N}x{K})")
+        return True
+
+    def _lt_takes(self, rows: int) -> bool:
+        """Row counts whose products go through the timed choice: the padded sizes of decode steps and whole
+        multiples of 256 (full prompt portions).  Other counts would each cost a timing pass for a shape that may
+        never come again; they take the library's own first choice."""
+        return rows <= self.lt_rows and (rows <= 64 or rows % 256 == 0)
+
+    def lt_last_choice(self) -> dict:
+        """The last timed choice: index in the library's list, candidates, microseconds (chosen, list's first)."""
+        c, n = c_int(0), c_int(0)
+        b, f = c_float(0), c_float(0)
+        self.lib.ullm_lt_last_choice(ctypes.byref(c), ctypes.byref(n), ctypes.byref(b), ctypes.byref(f))
+        return {"chosen": c.value, "candidates": n.value, "best_us": b.value, "first_us": f.value}
+
     def _own_linear(self, x, weight, out, bias=None, act=None) -> bool:
         """Tries the hand-written few-row product that the mode names; False: the caller uses the library."""
         if self.small_m_mode == "skinny":
@@ -268,6 +323,8 @@ class Kernels:
         _need(out, "out")
         if self._own_linear(x, weight, out, bias):
             return out
+        if bias is None and self._lt_takes(x.shape[0]) and self.lt_linear(x, weight, out):
+            return out
         if bias is not None:
             torch.addmm(bias, x, weight.t(), out=out)
         else:
@@ -282,9 +339,10 @@ class Kernels:
         _need(out, "out")
         if self._own_linear(x, weight, out, None, act):
             return out
-        # many rows: the persistent tcgen05 product with the activation in its epilogue beats the library's
-        # product followed by the activation kernel (measured at Qwen3-8B sizes: 320 against 339 us at 2,048 rows,
-        # 558 against 670 us at 4,096; it loses below about 1,500 rows)
+        # many rows: the persistent tcgen05 product with the activation in its epilogue against the library's
+        # product followed by the activation kernel (measured at Qwen3-8B sizes): 300 against 310 us at 2,048 rows
+        # with the library's own first algorithm, but 300 against 251 + 31 us with the library's timed choice
+        # (`lt_linear`); 576 against 500 - 535 + 62 us at 4,096 rows, from where it is taken
         if x.shape[0] >= self.fused_mlp_rows and self.large_linear(x, weight, out, None, act):
             return out
         self.linear(x, weight, gate_up)
@@ -298,6 +356,8 @@ class Kernels:
             torch.mm(x, weight.t(), out=out)
             return out
         if self._own_linear(x, weight, out):
+            return out
+        if self._lt_takes(x.shape[0]) and self.lt_linear(x, weight, out):
             return out
         if self._f32_out_mm is None:
             try:
