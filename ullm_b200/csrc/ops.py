@@ -293,11 +293,12 @@ class Kernels:
         self._check(rc, f"lt_linear ({M}x{K} . {N}x{K})")
         return True
 
-    def _lt_takes(self, rows: int) -> bool:
-        """Row counts whose products go through the timed choice: the padded sizes of decode steps and whole
-        multiples of 256 (full prompt portions).  Other counts would each cost a timing pass for a shape that may
+    def _lt_takes(self, rows: int, weight) -> bool:
+        """Products that go through the timed choice: weights of at least 8 MB (below that there is nothing to
+        gain and a timing pass per shape to lose) at the padded row counts of decode steps and at whole multiples
+        of 256 rows (full prompt portions).  Other row counts would each cost a timing pass for a shape that may
         never come again; they take the library's own first choice."""
-        return rows <= self.lt_rows and (rows <= 64 or rows % 256 == 0)
+        return rows <= self.lt_rows and (rows <= 64 or rows % 256 == 0) and weight.numel() >= (1 << 22)
 
     def lt_last_choice(self) -> dict:
         """The last timed choice: index in the library's list, candidates, microseconds (chosen, list's first)."""
@@ -323,7 +324,7 @@ class Kernels:
         _need(out, "out")
         if self._own_linear(x, weight, out, bias):
             return out
-        if bias is None and self._lt_takes(x.shape[0]) and self.lt_linear(x, weight, out):
+        if bias is None and self._lt_takes(x.shape[0], weight) and self.lt_linear(x, weight, out):
             return out
         if bias is not None:
             torch.addmm(bias, x, weight.t(), out=out)
@@ -357,7 +358,7 @@ class Kernels:
             return out
         if self._own_linear(x, weight, out):
             return out
-        if self._lt_takes(x.shape[0]) and self.lt_linear(x, weight, out):
+        if self._lt_takes(x.shape[0], weight) and self.lt_linear(x, weight, out):
             return out
         if self._f32_out_mm is None:
             try:
