@@ -334,3 +334,9 @@ def test_long_context_at_real_widths_prompt_portions_against_decode_steps():
     lg = r.step([StepEntry("a", [ids[N]], [0]), StepEntry("b", [ids[N]], [0])]).float().cpu()
     assert (lg[0] - lg[1]).abs().max().item() <= TOL["bfloat16"] * scale
     r.check_device_status()
+    # at these widths the library's products went through the timed choice of algorithm (portions and decode steps)
+    from ullm_b200.csrc import kernels
+
+    if kernels().lt_rows > 0:
+        tuned = kernels()._lt_tuned
+        assert any(k[0] == 2048 for k in tuned) and any(k[0] <= 2 for k in tuned), sorted(tuned)
