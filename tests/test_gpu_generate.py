@@ -78,6 +78,23 @@ def test_preemption_under_a_tiny_pool_keeps_the_tokens(tmp_path):
     llm.engine.runner.cache.check_invariants()
 
 
+def test_requests_that_reach_a_page_end_in_the_same_step_with_too_few_pages_left(tmp_path):
+    """Six requests of equal length decode side by side, steps launched ahead, and all need a new page in the
+    same step while three are left: some are preempted (after the step in flight has been read: their tokens must
+    be known to be recomputed), all finish with the tokens of the plain implementation."""
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "B", num_pages=15, max_bs=6, max_num_batched_tokens=64)
+    page = llm.engine.runner.cache.page_size
+    n = 2 * page - 2
+    prompts = [random_ids(331, n, 300 + i) for i in range(6)]
+    outs = llm.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=24, ignore_eos=True))
+    assert llm.engine.stats()["preemptions"] >= 1
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == pm.greedy_generate(p, w, cfg, 24)
+    llm.engine.runner.cache.check_invariants()
+
+
 def test_finish_rules(tmp_path):
     from ullm_b200 import SamplingParams
 

@@ -340,6 +340,9 @@ class CacheManager:
             tree_pages = set(self.tree.pages()) if (self.tree is not None and g == 0) else set()
             if len(tree_pages) != (self.tree.num_pages if (self.tree is not None and g == 0) else 0):
                 raise AssertionError("prefix tree holds a page twice")
+            if self.tree is not None and g == 0 and self.tree.num_evictable() != self.tree.count_evictable_by_walk():
+                raise AssertionError(f"prefix tree counts {self.tree.num_evictable()} evictable pages, a walk finds "
+                                     f"{self.tree.count_evictable_by_walk()}")
             for p in tree_pages:
                 owners[p] = "tree"
             for rc in self.requests.values():

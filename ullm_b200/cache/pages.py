@@ -108,6 +108,7 @@ class PrefixTree:
         self._clock = itertools.count(1)
         self._heap: list[tuple[int, int, _Node]] = []
         self.num_pages = 0
+        self._num_unreferenced = 0  # nodes with ref == 0, kept as references come and go
 
     def _touch(self, node: _Node) -> None:
         node.stamp = next(self._clock)
@@ -129,6 +130,8 @@ class PrefixTree:
 
     def acquire(self, nodes: list[_Node]) -> None:
         for n in nodes:
+            if n.ref == 0:
+                self._num_unreferenced -= 1
             n.ref += 1
             n.stamp = next(self._clock)
 
@@ -137,6 +140,8 @@ class PrefixTree:
             if n.ref <= 0:
                 raise ValueError("prefix node released more often than acquired")
             n.ref -= 1
+            if n.ref == 0:
+                self._num_unreferenced += 1
             self._touch(n)
 
     def insert(self, tokens, pages: list[int], have: list[_Node]) -> list[int]:
@@ -154,6 +159,7 @@ class PrefixTree:
                 child = _Node(key, pages[i], node, next(self._uid))
                 node.children[key] = child
                 self.num_pages += 1
+                self._num_unreferenced += 1
             else:
                 dup.append(pages[i])
             self._touch(child)
@@ -188,13 +194,21 @@ class PrefixTree:
             parent = node.parent
             node.parent = None
             self.num_pages -= 1
+            self._num_unreferenced -= 1
             out.append(node.page)
             if parent is not self.root and parent.ref == 0 and not parent.children:
                 heapq.heappush(self._heap, (parent.stamp, parent.uid, parent))
         return out
 
     def num_evictable(self) -> int:
-        """Pages that eviction could return now (unreferenced subtrees)."""
+        """Pages that eviction could return now: the nodes of unreferenced subtrees.  A request holds the whole
+        chain from the root to its last node, so a node that nobody holds has no held descendant either, and the
+        count is simply the number of unreferenced nodes, which is kept as references come and go (this is asked
+        for every running request in every step)."""
+        return self._num_unreferenced
+
+    def count_evictable_by_walk(self) -> int:
+        """The same number from a walk over the whole tree (tests compare the two)."""
 
         def walk(node) -> tuple[int, bool]:
             total, all_free = 0, True

@@ -159,9 +159,19 @@ class Engine:
 
     def _must_read_first(self) -> bool:
         """The step in flight has to be read before the next is scheduled when scheduling may preempt (a
-        preempted sequence is recomputed from its tokens, which must all be known)."""
+        preempted sequence is recomputed from its tokens, which must all be known).  It may when the running
+        sequences TOGETHER want more pages for their next tokens than can be had: several of them can reach the
+        end of a page in the same step."""
         cache = self.runner.cache
-        return any(s.cache is not None and not cache.can_reserve(s.cache, 2) for s in self.scheduler.running)
+        need = [0] * len(cache.groups)
+        for s in self.scheduler.running:
+            if s.cache is None:
+                continue
+            if not cache.can_reserve(s.cache, 2):  # (also: a request at the most pages a request may hold)
+                return True
+            for g, k in enumerate(cache.pages_needed(s.cache, 2)):
+                need[g] += max(int(k), 0)
+        return any(need[g] > cache.num_available_pages(g) for g in range(len(need)))
 
     def _collect(self, step) -> list[EngineStepResult]:
         handle, pending, n_seqs, n_tokens, t0 = step
