@@ -276,6 +276,43 @@ def test_sampling_filters_and_draws(V):
         assert lo - 1e-5 <= us[r] * float(c[-1]) <= float(c[i]) + 1e-5, f"case {r}: drew {i}, inverse CDF gives {ref_draw}"
 
 
+@pytest.mark.parametrize("V", [5, 331, 4099, 50257, 151936])
+def test_sampling_over_a_cluster_gives_the_tokens_and_probabilities_of_the_one_block_kernel(V):
+    """A row spread over a cluster of eight blocks (slices in shared memory, histograms and sums exchanged
+    through distributed shared memory) against one block per row: all sums are integer sums, so tokens and
+    probabilities agree bit for bit, for every filter combination, with rows that start on no 16-byte boundary."""
+    cases = [(0.7, 20, 0.95, 0.0), (1.0, -1, 0.5, 0.0), (1.3, 5, 1.0, 0.1), (0.5, -1, 1.0, 0.3), (1.0, -1, 1.0, 0.0),
+             (0.0, -1, 1.0, 0.0), (2.0, 1, 1.0, 0.0), (0.9, 50, 0.3, 0.05), (0.6, 20, 0.95, 0.0), (1.0, 3, 0.01, 0.0),
+             (1.5, -1, 0.999, 0.0), (0.8, 100000, 0.9, 0.5)]
+    R = len(cases)
+    wide = rnd(R, V + 3, seed=23, scale=2.5)
+    wide[2, 10 % V] = wide[2, 3 % V]  # equal values
+    wide[4, :] = wide[4, 0]           # a flat row
+    dev = lambda xs, dt: torch.tensor(xs, dtype=dt, device="cuda")
+    args = (dev([c[0] for c in cases], torch.float32), dev([c[1] for c in cases], torch.int32),
+            dev([c[2] for c in cases], torch.float32), dev([c[3] for c in cases], torch.float32))
+    for shift in (0, 1):  # rows at 16-byte boundaries (if V allows) and off them
+        lg = wide[:, shift:shift + V]
+        for seed in range(3):
+            us = dev([((r * 37 + seed * 101) % 1000) / 1000.0 for r in range(R)], torch.float32)
+            got, ref = [], []
+            for one_block, res in ((False, got), (True, ref)):
+                out = torch.full((R,), -7, dtype=torch.int32, device="cuda")
+                probs = torch.full((R, V), -1.0, device="cuda")
+                slots = torch.arange(R, dtype=torch.int32, device="cuda")
+                last = torch.full((R,), -9, dtype=torch.int32, device="cuda")
+                K().sample_force_one_block(one_block)
+                try:
+                    K().sample(lg, *args, us, out, probs, row_slots=slots, last_tokens=last)
+                    assert K().sample_used_cluster() == (not one_block)
+                finally:
+                    K().sample_force_one_block(False)
+                res += [out.cpu(), probs.cpu(), last.cpu()]
+            assert torch.equal(got[0], ref[0]), (got[0].tolist(), ref[0].tolist())
+            assert torch.equal(got[1], ref[1])
+            assert torch.equal(got[2], ref[2]) and torch.equal(got[2], got[0])
+
+
 def test_sampling_is_independent_of_batch():
     V = 4099
     lg = rnd(6, V, seed=22, scale=2.0)

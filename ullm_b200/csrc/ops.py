@@ -147,6 +147,10 @@ class Kernels:
         L.ullm_decode_attention_tcgen05_supported.restype = c_int
         L.ullm_decode_attention_tcgen05_scratch_floats.argtypes = [I]
         L.ullm_decode_attention_tcgen05_scratch_floats.restype = c_longlong
+        L.ullm_sample_force_one_block.argtypes = [I]
+        L.ullm_sample_force_one_block.restype = None
+        L.ullm_sample_last_used_cluster.argtypes = []
+        L.ullm_sample_last_used_cluster.restype = c_int
         L.ullm_lt_available.argtypes = []
         L.ullm_lt_available.restype = c_int
         L.ullm_lt_last_choice.argtypes = [P, P, P, P]
@@ -545,6 +549,13 @@ class Kernels:
         if logits.stride(1) != 1 or out.numel() < R:
             raise KernelError("argmax: logits rows must be contiguous and out must hold one id per row")
         self._check(self.lib.ullm_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+
+    def sample_force_one_block(self, on: bool) -> None:
+        """Rows go to the one-block sampling kernel instead of the cluster kernel (tests compare the two)."""
+        self.lib.ullm_sample_force_one_block(1 if on else 0)
+
+    def sample_used_cluster(self) -> bool:
+        return bool(self.lib.ullm_sample_last_used_cluster())
 
     def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None, row_slots=None,
                last_tokens=None):
