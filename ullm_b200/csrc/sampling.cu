@@ -561,11 +561,30 @@ sample_cluster_kernel(const float* __restrict__ logits, long long row_stride, in
       const unsigned int mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
       for (int b = tid; b < SC_HISTS * 256; b += SC_THREADS) mass_w[b] = 0ull;
       __syncthreads();
-      for (int i = tid; i < n; i += SC_THREADS) {
-        const float x = vals[i];
-        const unsigned int key = order_key(x);
-        if (key >= key_floor && (key & mask) == prefix)
-          atomicAdd(&mass_w[hist * 256 + ((key >> shift) & 255u)], mass_of(x, mx));
+      if (pass == 0 && key_floor == 0u) {  // (after a top-k only its k survivors take part: plain atomics do)
+        // every kept element takes part and most fall into a few digits: lanes of a warp with the same digit add
+        // once (64-bit atomics on one address are what costs here; for the 32-bit counts above it does not pay).
+        // A mass is at most 2^40, so the sums of its low and of its high 20 bits over 32 lanes fit 32 bits.
+        for (int i0 = warp * 32; i0 < n; i0 += SC_THREADS) {
+          const int i = i0 + lane;
+          const float x = i < n ? vals[i] : 0.f;
+          const unsigned int key = order_key(x);
+          const bool in = i < n && key >= key_floor;
+          const unsigned int digit = in ? (key >> 24) : 0xffffffffu;
+          const unsigned long long m = in ? mass_of(x, mx) : 0ull;
+          const unsigned int same = __match_any_sync(0xffffffffu, digit);
+          const unsigned int lo = __reduce_add_sync(same, (unsigned int)(m & 0xfffffull));
+          const unsigned int hi = __reduce_add_sync(same, (unsigned int)(m >> 20));
+          if (in && lane == __ffs(same) - 1)
+            atomicAdd(&mass_w[hist * 256 + digit], ((unsigned long long)hi << 20) + lo);
+        }
+      } else {
+        for (int i = tid; i < n; i += SC_THREADS) {
+          const float x = vals[i];
+          const unsigned int key = order_key(x);
+          if (key >= key_floor && (key & mask) == prefix)
+            atomicAdd(&mass_w[hist * 256 + ((key >> shift) & 255u)], mass_of(x, mx));
+        }
       }
       __syncthreads();
       if (tid < 256) {
