@@ -471,6 +471,53 @@ def run_decode_attention_probe(args) -> int:
     return 0
 
 
+def run_sampling_probe(args) -> int:
+    """`--probe sampling`: the two sampling kernels alone on `--batch` rows of the benchmark's vocabulary, one
+    parameter set for all rows; microseconds per call, 20 calls recorded in a CUDA graph (the logits stay in L2,
+    as they do behind the output head's product)."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.sampling.params import SamplingParams
+    from ullm_b200.sampling.sampler import Sampler
+
+    K = kernels()
+    V, R = QWEN3_8B["vocab_size"], args.batch
+    logits = torch.randn(R, V, device="cuda") * 3
+    s = Sampler("cuda", R, V)
+    cases = [("greedy", SamplingParams(temperature=0.0)), ("temperature", SamplingParams(temperature=0.8)),
+             ("top_k 50", SamplingParams(temperature=0.8, top_k=50)), ("top_p 0.9", SamplingParams(temperature=0.8, top_p=0.9)),
+             ("top_k 50 + top_p 0.9", SamplingParams(temperature=0.8, top_k=50, top_p=0.9)),
+             ("min_p 0.05", SamplingParams(temperature=0.8, min_p=0.05))]
+    print(f"rows {R}, vocabulary {V}; microseconds per call")
+    for name, p in cases:
+        s.stage([p] * R, list(range(R)), [3] * R)
+        t = {}
+        for label, one_block in (("one block per row", True), ("cluster of 8 blocks per row", False)):
+            K.sample_force_one_block(one_block)
+            try:
+                s.run(logits, R)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for _ in range(20):
+                        s.run(logits, R)
+                ts = []
+                for _ in range(6):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    g.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1) * 1000 / 20)
+                t[label] = statistics.median(ts[2:])
+            finally:
+                K.sample_force_one_block(False)
+        print(f"{name:24s} " + "   ".join(f"{k} {v:8.1f}" for k, v in t.items()))
+    K.raise_on_status()
+    return 0
+
+
 def _write_reference_model(path: str, cfg: dict) -> None:
     """A model folder the reference can open: random weights (this repo's seeded writer), and a synthetic
     byte-level tokenizer (its LLM loads a tokenizer unconditionally; ids go in and out as integers here, the
@@ -600,7 +647,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention"],
+    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "sampling"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
@@ -614,6 +661,8 @@ def main() -> int:
         return run_linear_probe(args)
     if args.probe == "decode-attention":
         return run_decode_attention_probe(args)
+    if args.probe == "sampling":
+        return run_sampling_probe(args)
     if args.probe:
         return run_probe(args)
     if args.impl == "reference":
