@@ -146,6 +146,28 @@ def test_available_pages_do_not_walk_the_prefix_tree():
     m.check_invariants()
 
 
+def test_eviction_queue_does_not_grow_without_evictions():
+    """A pool with room to spare never evicts; the queue of eviction candidates must not grow with every request
+    that finishes (it is rebuilt from the tree when stale entries pile up), and eviction still takes the least
+    recently used pages first afterwards."""
+    m = manager([(FULL, None, None)], num_pages=64, page=4, per_request=16)
+    toks = {r: [r * 100 + i for i in range(16)] for r in range(3)}
+    for _ in range(2000):
+        for r in (0, 1, 2):
+            a = m.admit(f"r{r}", toks[r])
+            need = 16 - a.num_tokens
+            m.reserve(a, need)
+            m.commit(a, need)
+            m.release(a, toks[r])
+    assert m.tree.num_pages == 12
+    assert len(m.tree._heap) <= 4 * m.tree.num_pages + 1024 + 8
+    m.check_invariants()
+    # request 0 was released first in every round: its last page is the least recently used leaf
+    chain0 = m.tree.match(toks[0], 4)
+    assert len(chain0) == 4
+    assert m.tree.evict(1) == [chain0[-1].page]
+
+
 def test_two_fresh_requests_with_one_prefix_leak_nothing():
     """The reference loses the second request's duplicate slots here
     (ullm/core/kv_cache.py:379: freed only when old_prefix_len != 0)."""

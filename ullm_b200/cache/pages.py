@@ -114,6 +114,22 @@ class PrefixTree:
         node.stamp = next(self._clock)
         if node.ref == 0 and not node.children:
             heapq.heappush(self._heap, (node.stamp, node.uid, node))
+            # Entries are only taken out by evictions; a server with room to spare never evicts, and every
+            # release adds one.  When stale entries outnumber the tree's pages several times over, the heap is
+            # rebuilt from the unreferenced leaves that exist now.
+            if len(self._heap) > 4 * self.num_pages + 1024:
+                self._rebuild_heap()
+
+    def _rebuild_heap(self) -> None:
+        live, stack = [], [self.root]
+        while stack:
+            n = stack.pop()
+            for c in n.children.values():
+                if c.ref == 0 and not c.children:
+                    live.append((c.stamp, c.uid, c))
+                stack.append(c)
+        heapq.heapify(live)
+        self._heap = live
 
     def match(self, tokens, max_pages: int) -> list[_Node]:
         """Nodes of the longest chain of full pages that prefixes `tokens`,
