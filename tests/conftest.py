@@ -17,6 +17,9 @@ CPU_DOUBLE = os.environ.get("ULLM_B200_CPU_DOUBLE") == "1"
 
 
 def pytest_configure(config):
+    # no test may hang a run: with the pytest-timeout plugin present, every test gets five minutes at most
+    if config.pluginmanager.hasplugin("timeout") and not getattr(config.option, "timeout", None):
+        config.option.timeout = 300
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
     config.addinivalue_line("markers", "needs_cuda: cannot run against the CPU stand-in")
 

@@ -1,6 +1,9 @@
 """The Python entry point's behaviour that needs no GPU: what happens after a step of the engine has failed."""
 
 import asyncio
+import threading
+import time
+from collections import deque
 from types import SimpleNamespace
 
 import pytest
@@ -22,6 +25,11 @@ class _FailingEngine:
         self.live: list[str] = []
         self.steps = 0
         self.profile_steps = False
+
+    def check_prompt(self, ids):
+        if not ids:
+            raise ValueError("empty prompt")
+        return list(ids)
 
     def add_sequence(self, sid, ids, params):
         self.live.append(sid)
@@ -50,6 +58,7 @@ def _llm() -> LLM:
     llm.request_states = {}
     llm._loop_task = None
     llm.is_dead = False
+    llm._commands = deque()
     return llm
 
 
@@ -87,3 +96,89 @@ def test_streaming_generators_get_the_failure_and_later_calls_raise_engine_dead(
         await llm.shutdown()
 
     asyncio.run(run())
+
+
+class _SlowEngine:
+    """Steps take a while and record whether a request was added or cancelled while one was running."""
+
+    context_len = 64
+
+    def __init__(self):
+        self.runner = SimpleNamespace(spec=SimpleNamespace(eos_token_id=None))
+        self.live: dict[str, int] = {}
+        self.in_step = False
+        self.touched_during_step = 0
+        self.threads = set()
+        self.aborted: list[str] = []
+        self.profile_steps = False
+
+    def check_prompt(self, ids):
+        return list(ids)
+
+    def _touch(self):
+        self.threads.add(threading.get_ident())
+        if self.in_step:
+            self.touched_during_step += 1
+
+    def add_sequence(self, sid, ids, params):
+        self._touch()
+        if sid in self.live:
+            raise ValueError(f"sequence {sid!r} already exists")
+        self.live[sid] = params.max_new_tokens
+
+    def abort_sequence(self, sid):
+        self._touch()
+        self.aborted.append(sid)
+        self.live.pop(sid, None)
+
+    def has_unfinished_sequences(self):
+        return bool(self.live)
+
+    def step(self):
+        self.in_step = True
+        time.sleep(0.02)
+        out = []
+        for sid in list(self.live):
+            self.live[sid] -= 1
+            done = self.live[sid] == 0
+            out.append(EngineStepResult(sid, 5, done, None, 0, 0))
+            if done:
+                del self.live[sid]
+        self.in_step = False
+        return out
+
+    def shutdown(self):
+        pass
+
+
+def test_requests_and_cancellations_reach_the_engine_only_between_steps():
+    """Steps run in a worker thread; `generate` and `abort` are called from the event loop while one runs.  They
+    are queued and applied by the worker between two steps, never while the scheduler's lists are in use."""
+    llm = _llm()
+    eng = llm.engine = _SlowEngine()
+
+    async def consume(sid, n, cancel_after=None):
+        got = 0
+        agen = llm.generate([1, 2, 3], SamplingParams(max_new_tokens=n), sid)
+        async for _ in agen:
+            got += 1
+            if cancel_after is not None and got == cancel_after:
+                await agen.aclose()  # the caller goes away: the generator cancels its request
+                break
+        return got
+
+    async def run():
+        first = asyncio.create_task(consume("a", 12))
+        await asyncio.sleep(0.03)  # a step is running now
+        second = asyncio.create_task(consume("b", 6))
+        third = asyncio.create_task(consume("c", 30, cancel_after=2))
+        await asyncio.sleep(0.01)
+        with pytest.raises(ValueError, match="already exists"):
+            await consume("a", 3)  # a duplicate id: the error comes back to its caller only
+        assert await first == 12 and await second == 6 and await third == 2
+        await llm.shutdown()
+
+    asyncio.run(run())
+    assert eng.touched_during_step == 0
+    assert "c" in eng.aborted and not eng.live
+    assert len(eng.threads) >= 1

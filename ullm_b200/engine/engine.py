@@ -64,13 +64,7 @@ class Engine:
     def add_sequence(self, sequence_id: str, prompt_token_ids: list[int], sampling_params: SamplingParams) -> None:
         """ullm/core/engine.py:72-90: a prompt longer than the context keeps its
         last `context_len` ids."""
-        ids = [int(t) for t in prompt_token_ids]
-        if not ids:
-            raise ValueError("empty prompt")
-        V = self.runner.spec.vocab_size
-        bad = [t for t in ids if not 0 <= t < V]
-        if bad:
-            raise ValueError(f"token id {bad[0]} is outside the vocabulary of {V}")
+        ids = self.check_prompt(prompt_token_ids)
         if len(ids) > self.context_len:
             ids = ids[-self.context_len:]
         seed = sampling_params.seed
@@ -80,6 +74,17 @@ class Engine:
         seq = Sequence(sequence_id, ids, len(ids), sampling_params, seed=seed)
         self.scheduler.add_sequence(seq)
         logger.debug("Added sequence %s.", sequence_id)
+
+    def check_prompt(self, prompt_token_ids) -> list[int]:
+        """The prompt as a list of ints; ValueError if it is empty or holds an id outside the vocabulary."""
+        ids = [int(t) for t in prompt_token_ids]
+        if not ids:
+            raise ValueError("empty prompt")
+        V = self.runner.spec.vocab_size
+        bad = [t for t in ids if not 0 <= t < V]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside the vocabulary of {V}")
+        return ids
 
     def abort_sequence(self, sequence_id: str) -> None:
         seq = self.scheduler.get_sequence(sequence_id)

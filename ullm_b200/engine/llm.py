@@ -21,6 +21,7 @@ from __future__ import annotations
 import asyncio
 import os
 import uuid
+from collections import deque
 from typing import AsyncGenerator
 
 from ..config.engine_config import EngineConfig
@@ -52,17 +53,41 @@ class LLM:
         self.request_states: dict[str, asyncio.Queue] = {}
         self._loop_task: asyncio.Task | None = None
         self.is_dead = False  # set when a step raised: every later call raises EngineDeadError
+        # Steps run in a worker thread while the event loop goes on taking requests and cancellations.  Those do
+        # not touch the engine themselves: they are queued here and applied by the worker between two steps (the
+        # reference sends them to its engine process over a socket, ullm/core/engine_client.py:299-326).
+        self._commands: deque = deque()
 
     def _check_alive(self) -> None:
         if self.is_dead:
             raise EngineDeadError()
 
+    def _apply_commands(self) -> list[tuple[str, Exception]]:
+        """Queued additions and cancellations, in order; returns (sequence id, error) for those that failed."""
+        errors = []
+        while self._commands:
+            cmd = self._commands.popleft()
+            try:
+                if cmd[0] == "add":
+                    self.engine.add_sequence(*cmd[1:])
+                else:
+                    self.engine.abort_sequence(cmd[1])
+            except Exception as e:
+                errors.append((cmd[1], e))
+        return errors
+
     def _step(self):
+        """One step of the engine, after what was queued since the last (runs in the worker thread)."""
+        errors = self._apply_commands()
         try:
-            return self.engine.step()
+            return self.engine.step(), errors
         except Exception:
             self.is_dead = True
             raise
+
+    def _ensure_loop(self) -> None:
+        if self._loop_task is None or self._loop_task.done():
+            self._loop_task = asyncio.create_task(self._engine_loop())
 
     # -- text <-> ids ----------------------------------------------------------------
     def tokenize(self, texts: list[str]) -> list[list[int]]:
@@ -89,8 +114,12 @@ class LLM:
     # -- streaming, as the reference ----------------------------------------------------
     async def _engine_loop(self) -> None:
         try:
-            while self.engine.has_unfinished_sequences():
-                results = await asyncio.to_thread(self._step)
+            while self._commands or self.engine.has_unfinished_sequences():
+                results, errors = await asyncio.to_thread(self._step)
+                for sid, e in errors:
+                    q = self.request_states.get(sid)
+                    if q is not None:
+                        q.put_nowait(e)
                 for r in results:
                     q = self.request_states.get(r.seq_id)
                     if q is None:
@@ -115,13 +144,16 @@ class LLM:
         self._check_alive()
         if sequence_id is None:
             sequence_id = uuid.uuid4().hex
+        if sequence_id in self.request_states:  # (its queue would replace the live request's)
+            raise ValueError(f"sequence {sequence_id!r} already exists")
         try:
             token_ids = prompts if isinstance(prompts, list) else self.tokenize([prompts])[0]
             q: asyncio.Queue = asyncio.Queue()
+            sp = self._params(params)
+            self.engine.check_prompt(token_ids)  # an empty prompt or an id outside the vocabulary raises here
             self.request_states[sequence_id] = q
-            self.engine.add_sequence(sequence_id, token_ids, self._params(params))
-            if self._loop_task is None or self._loop_task.done():
-                self._loop_task = asyncio.create_task(self._engine_loop())
+            self._commands.append(("add", sequence_id, token_ids, sp))
+            self._ensure_loop()
             while True:
                 out = await q.get()
                 if isinstance(out, Exception):
@@ -129,7 +161,7 @@ class LLM:
                 if out is None:
                     break
                 yield out
-            del self.request_states[sequence_id]
+            self.request_states.pop(sequence_id, None)
         except (asyncio.CancelledError, GeneratorExit):
             self.abort(sequence_id)
             raise
@@ -139,8 +171,13 @@ class LLM:
             self.request_states.pop(sequence_id, None)
             return
         if sequence_id in self.request_states:
-            self.engine.abort_sequence(sequence_id)
             del self.request_states[sequence_id]
+            self._commands.append(("abort", sequence_id))
+            try:
+                asyncio.get_running_loop()
+                self._ensure_loop()  # (applies it even if nothing else is left to run)
+            except RuntimeError:
+                pass  # no event loop here: it is applied before the next step
 
     async def shutdown(self) -> None:
         if self._loop_task is not None:
@@ -174,7 +211,7 @@ class LLM:
         got: dict[str, list[int]] = {sid: [] for sid in order}
         reason: dict[str, FinishReason | None] = {}
         while len(reason) < len(order) and self.engine.has_unfinished_sequences():
-            for r in self._step():
+            for r in self._step()[0]:
                 if r.seq_id not in got:
                     continue
                 if r.new_token_id >= 0:
