@@ -95,6 +95,28 @@ def test_requests_that_reach_a_page_end_in_the_same_step_with_too_few_pages_left
     llm.engine.runner.cache.check_invariants()
 
 
+@pytest.mark.needs_cuda
+def test_graphs_recorded_at_start_up_are_the_ones_generation_replays(tmp_path):
+    """`warmup_graphs`: every padded batch size is recorded (even and ragged form) before the first request, the
+    throw-away requests leave nothing behind, and generation then only replays: same tokens as the plain
+    implementation, no new graph."""
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "D", dtype="bfloat16", max_bs=4, num_pages=64, warmup_graphs=True)
+    dg = llm.engine.decode_graphs
+    assert set(dg.graphs) == {(s, r) for s in dg.sizes for r in ((False, True) if s > 1 else (False,))}
+    cache = llm.engine.runner.cache
+    assert not cache.requests and cache.num_free_pages(0) == 64
+    cache.check_invariants()
+    held = {k: v[0] for k, v in dg.graphs.items()}
+    prompts = [random_ids(cfg["vocab_size"], n, 500 + n) for n in (9, 40, 3)]
+    outs = llm.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True))
+    llm32, _, w32 = make_llm(tmp_path, "D", dtype="bfloat16", max_bs=4, num_pages=64, enforce_eager=True)
+    ref = llm32.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True))
+    assert [o.token_ids for o in outs] == [o.token_ids for o in ref]
+    assert dg.replays > 0 and all(dg.graphs[k][0] is g for k, g in held.items())
+
+
 def test_finish_rules(tmp_path):
     from ullm_b200 import SamplingParams
 

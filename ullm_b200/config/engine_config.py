@@ -43,6 +43,7 @@ class EngineConfig:
     seed: int = 0
     num_pages: int | None = None  # None: sized from free memory x gpu_memory_utilization
     enable_prefix_caching: bool = True
+    warmup_graphs: bool = False  # record every decode graph while the engine starts instead of at first use
     random_init_std: float = 0.02
     random_init_norm_std: float = 0.0
 
@@ -115,6 +116,8 @@ class EngineConfig:
         parser.add_argument("--seed", type=int, default=0, help="Seed of random weights and of sampling")
         parser.add_argument("--num-pages", type=int, default=None, help="KV pages (default: from free memory)")
         parser.add_argument("--no-prefix-caching", action="store_true", help="Disable prefix reuse over pages")
+        parser.add_argument("--warmup-graphs", action="store_true",
+                            help="Record the CUDA graphs of all decode batch sizes at start-up (default: at first use)")
 
     @staticmethod
     def from_args(args: argparse.Namespace) -> "EngineConfig":
@@ -140,4 +143,5 @@ class EngineConfig:
             seed=getattr(args, "seed", 0),
             num_pages=getattr(args, "num_pages", None),
             enable_prefix_caching=not getattr(args, "no_prefix_caching", False),
+            warmup_graphs=getattr(args, "warmup_graphs", False),
         )

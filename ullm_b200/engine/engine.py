@@ -59,6 +59,9 @@ class Engine:
         self._seed_counter = 0
         self.profile_steps = config.profile
         self.step_times: list[tuple[int, int, float]] = []
+        if config.warmup_graphs:
+            n = self.warm_up_graphs()
+            logger.info("recorded %d decode graphs", n)
 
     # -- requests -------------------------------------------------------------------
     def add_sequence(self, sequence_id: str, prompt_token_ids: list[int], sampling_params: SamplingParams) -> None:
@@ -214,6 +217,61 @@ class Engine:
         if self._length_reached(seq, length):
             return True, FinishReason.LENGTH
         return False, None
+
+    def warm_up_graphs(self) -> int:
+        """Records the decode graphs of every padded batch size now, for even and for ragged batches, instead of
+        at the first step of that size (the reference records its graphs while the engine starts,
+        ullm/core/model_runner.py:428-500).  Each size runs one decode step of throw-away requests (one token of
+        context each; for the ragged form one of them holds 33), which also times the library's products of
+        that size; their pages and slots are given back.  Sizes the pool or the slots cannot hold are left for
+        later.  Returns the number of graphs held afterwards."""
+        from ..cache import OutOfPages
+
+        dg = self.decode_graphs
+        if dg is None or self.scheduler.running or self.scheduler.waiting or self._inflight is not None:
+            return 0 if dg is None else len(dg.graphs)
+        runner, greedy = self.runner, SamplingParams(temperature=0.0)
+        # First the largest step there can be (a full token budget of prompt portions): the buffers that steps
+        # work in grow to their final size, and a recorded graph is only good for the buffers it was recorded with.
+        budget = self.scheduler.max_num_batched_tokens
+        per = max(1, min(budget, self.context_len - 1))
+        counts = [per] * (budget // per) + ([budget % per] if budget % per else [])
+        admitted = []
+        try:
+            entries = []
+            for i, n in enumerate(counts[: self.scheduler.max_bs]):
+                rid = f"__warm_up_p{i}"
+                if runner.add_request(rid) is None:
+                    break
+                admitted.append(rid)
+                entries.append(StepEntry(rid, [0] * n, [n - 1]))
+            if entries:
+                runner.step(entries)
+        except OutOfPages:
+            pass
+        finally:
+            for rid in admitted:
+                runner.end_request(rid)
+        for size in dg.sizes:
+            for ragged in ((False, True) if size > 1 else (False,)):
+                ids = [f"__warm_up_{i}" for i in range(size)]
+                admitted = []
+                try:
+                    for i, rid in enumerate(ids):
+                        if runner.add_request(rid) is None:
+                            raise OutOfPages("no request slot")
+                        admitted.append(rid)
+                        n = 33 if (ragged and i == 0) else 1
+                        runner.step([StepEntry(rid, [0] * n, [])])
+                    entries = [StepEntry(rid, [0], [0]) for rid in ids]
+                    dg.run(entries, [greedy] * size, [0] * size, [0] * size)
+                except OutOfPages:
+                    pass
+                finally:
+                    for rid in admitted:
+                        runner.end_request(rid)
+        self.runner.check_device_status()
+        return len(dg.graphs)
 
     def stats(self) -> dict:
         c = self.runner.cache
