@@ -299,10 +299,12 @@ class Kernels:
 
     def _lt_takes(self, rows: int, weight) -> bool:
         """Products that go through the timed choice: weights of at least 8 MB (below that there is nothing to
-        gain and a timing pass per shape to lose) at the padded row counts of decode steps and at whole multiples
-        of 256 rows (full prompt portions).  Other row counts would each cost a timing pass for a shape that may
+        gain and a timing pass per shape to lose) at the padded row counts of decode steps (1, 2, 4, 8, 16, 32, 48,
+        64) and at whole multiples of 256 rows (full prompt portions).  Other row counts would each cost a timing pass for a shape that may
         never come again; they take the library's own first choice."""
-        return rows <= self.lt_rows and (rows <= 64 or rows % 256 == 0) and weight.numel() >= (1 << 22)
+        if rows > self.lt_rows or weight.numel() < (1 << 22):
+            return False
+        return rows in (1, 2, 4, 8) or rows % 16 == 0 and (rows <= 64 or rows % 256 == 0)
 
     def lt_last_choice(self) -> dict:
         """The last timed choice: index in the library's list, candidates, microseconds (chosen, list's first)."""
