@@ -168,7 +168,8 @@ extern "C" int ullm_lt_linear(const void* x, const void* w, void* out, int M, in
         // flush, so that the clocks are those of sustained work.
         const bool cold = M < 512 && flush != nullptr;
         const int reps = cold ? 1 : 3;
-        for (int r = 0; r < 6; ++r) {
+        const int rounds = cold ? 12 : 6;  // cold runs are short and noisier: more of them
+        for (int r = 0; r < rounds; ++r) {
           for (int i = 0; i < n; ++i) {
             if (failed[i]) continue;
             if (cold) lt_flush_read_kernel<<<1024, 256, 0, st>>>((const uint4*)flush, flush_bytes / 16, (uint4*)flush);

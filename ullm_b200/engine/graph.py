@@ -18,12 +18,13 @@ import torch
 from .batch import StepEntry
 
 
-def graph_batch_sizes(max_bs: int, smallest: int = 1) -> list[int]:
-    """ullm/core/model_runner.py:431-433: 1, 2, 4, 8, then steps of 16 up to max_bs.  `smallest` drops the
-    sizes below it (a batch of 3 is then padded to `smallest` rows).  The engine's default is 16: the vendor
-    library's matrix products for 16 rows stream the weights faster than its choices for 1 to 8 rows
-    (measured: 78 us against 89 us per layer at Qwen3-8B sizes), and the padding rows cost nothing else."""
-    sizes = [b for b in (1, 2, 4, 8) if b <= max_bs] + list(range(16, max_bs + 1, 16))
+def graph_batch_sizes(max_bs: int, smallest: int = 1, skip: tuple = (8,)) -> list[int]:
+    """ullm/core/model_runner.py:431-433: 1, 2, 4, 8, then steps of 16 up to max_bs.  Here 8 is left out by
+    default (a batch of 5 to 8 is padded to 16 rows): with the library's products at their timed choice of
+    algorithm, a step of 8 requests takes 4.19 ms recorded at 8 rows and 4.05 ms at 16 (Qwen3-8B sizes), while 1
+    and 2 requests are faster at their own size (3.74 against 3.92 ms, 3.84 against 3.94 ms) and 4 is a tie; the
+    padding rows cost nothing else.  `smallest` drops the sizes below it."""
+    sizes = [b for b in (1, 2, 4, 8) if b <= max_bs and b not in skip] + list(range(16, max_bs + 1, 16))
     if max_bs not in sizes:
         sizes.append(max_bs)
     sizes = sorted(set(sizes))
@@ -37,7 +38,7 @@ class DecodeGraphs:
         self.sampler = sampler
         import os
 
-        self.sizes = graph_batch_sizes(max_bs, int(os.environ.get("ULLM_B200_MIN_GRAPH_BATCH", "16")))
+        self.sizes = graph_batch_sizes(max_bs, int(os.environ.get("ULLM_B200_MIN_GRAPH_BATCH", "1")))
         # (size, ragged) -> (graph, signature, kernels recorded): batches of very unequal lengths replay a
         # graph that was recorded with the batch-balanced attention kernel
         self.graphs: dict[tuple, tuple] = {}
