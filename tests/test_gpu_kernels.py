@@ -344,7 +344,7 @@ class _DecodeCtx:
     (32, 8, 128, 16, 100), (4, 2, 64, 4, 37), (9, 3, 128, 1, 0), (24, 2, 128, 8, 0), (16, 1, 128, 128, 300),
 ])
 @pytest.mark.parametrize("batch", [1, 3, 40])
-@pytest.mark.parametrize("mode", ["split", "balanced", "tcgen05"])
+@pytest.mark.parametrize("mode", ["split", "split-merge-kernel", "balanced", "tcgen05"])
 def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, mode):
     """The three tensor-core decode kernels (every request split alike; the whole batch's keys cut evenly over
     the warps; the same over the blocks with the products on tcgen05) against the plain reference: contexts of
@@ -386,15 +386,23 @@ def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, mode):
     scale = D ** -0.5
     ctx = _DecodeCtx(batch)
     old = K().use_balanced_decode, K().use_tcgen05_decode
+    old_cluster = K().decode_cluster_merge
     K().use_balanced_decode, K().use_tcgen05_decode = balanced, mode == "tcgen05"
+    K().set_decode_cluster_merge(mode == "split")
     try:
         K().paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
                             torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window,
                             scale, ctx)
     finally:
         K().use_balanced_decode, K().use_tcgen05_decode = old
+        K().set_decode_cluster_merge(old_cluster)
     K().raise_on_status()
-    assert K().attention_path == {"split": "decode", "balanced": "decode_balanced", "tcgen05": "decode_tcgen05"}[mode]
+    assert K().attention_path == {"split": "decode", "split-merge-kernel": "decode", "balanced": "decode_balanced",
+                                  "tcgen05": "decode_tcgen05"}[mode]
+    if mode == "split" and batch * Hkv < 400:  # several splits: they met inside a cluster
+        assert K().lib.ullm_decode_attention_last_used_cluster() == 1
+    if mode == "split-merge-kernel":
+        assert K().lib.ullm_decode_attention_last_used_cluster() == 0
     live = [r for r, kl in enumerate(kv_lens) if kl > 0]
     ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(batch, Hq, D)[live],
                               torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),

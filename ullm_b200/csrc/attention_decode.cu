@@ -17,9 +17,15 @@
 //
 // The grid depends on the batch size and the split count only, never on the
 // lengths, so a captured launch stays valid as the requests grow.
+#include <cooperative_groups.h>
+
 #include "decode_core.cuh"
 
-template <int D>
+namespace cg = cooperative_groups;
+
+// CL: the splits of a (request, kv head) pair are the blocks of one thread-block cluster (at most 8) and merge
+// their partials through distributed shared memory; no scratch arrays, no second kernel.
+template <int D, bool CL>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -28,6 +34,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
                         float* __restrict__ part_ml, int num_q, int num_kv, int page_size, int window,
                         float scale_log2, long long num_pages, int* status) {
   extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ float cm[CL ? 16 * (D + 2) : 1];  // this block's merged partial (cluster form): [head][D outputs, max, sum]
   pdl_launch_dependents();
   pdl_wait();
   constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
@@ -218,6 +225,12 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     const int h = kh * group + r;
     if (num_splits == 1) {
       out[((long long)b * num_q + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    } else if (CL) {
+      cm[r * (D + 2) + d] = acc;
+      if (d == 0) {
+        cm[r * (D + 2) + D] = mm;
+        cm[r * (D + 2) + D + 1] = ll;
+      }
     } else {
       const long long p = ((long long)b * num_q + h) * num_splits + split;
       part_o[p * D + d] = acc;
@@ -226,6 +239,28 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
         part_ml[p * 2 + 1] = ll;
       }
     }
+  }
+  if (CL && num_splits > 1) {
+    // The splits' partials meet: block `split` of the cluster finishes every num_splits-th output element, reading
+    // all partials (its peers' through distributed shared memory) and adding them in split order, as the merge
+    // kernel does: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    for (int idx = split * blockDim.x + threadIdx.x; idx < group * D; idx += num_splits * blockDim.x) {
+      const int r = idx / D, d = idx - r * D;
+      float mm = -INFINITY;
+      for (int s2 = 0; s2 < num_splits; ++s2) mm = fmaxf(mm, cluster.map_shared_rank(cm, s2)[r * (D + 2) + D]);
+      float ll = 0.f, acc = 0.f;
+      for (int s2 = 0; s2 < num_splits; ++s2) {
+        const float* peer = cluster.map_shared_rank(cm, s2) + r * (D + 2);
+        const float ms = peer[D];
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+        ll += peer[D + 1] * f;
+        acc += peer[d] * f;
+      }
+      out[((long long)b * num_q + kh * group + r) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    }
+    cluster.sync();  // no block leaves while a peer may still read its partial
   }
 }
 
@@ -271,6 +306,13 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
 }
 
 static int g_decode_attr_set[2] = {0, 0};
+static int g_decode_cluster = 1;  // 1: splits of 2 to 8 merge inside a cluster; 0: always scratch arrays + merge kernel
+
+// 0 switches the cluster form off (tests and measurements compare the two).
+extern "C" void ullm_decode_attention_cluster_merge(int on) { g_decode_cluster = on ? 1 : 0; }
+// What the last launch used: 1 the cluster form, 0 the merge kernel (or a single split).
+static int g_decode_last_cluster = 0;
+extern "C" int ullm_decode_attention_last_used_cluster(void) { return g_decode_last_cluster; }
 
 template <int D>
 static int launch_decode(int which, const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
@@ -279,15 +321,45 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
                          float scale, int num_splits, long long num_pages, int* status, cudaStream_t st) {
   using S = DecodeSmem<D>;
   if (!g_decode_attr_set[which]) {
-    if (cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(decode_attention_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(decode_attention_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
+            cudaSuccess)
       return ULLM_ERR_LAUNCH;
-    cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(decode_attention_kernel<D, false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(decode_attention_kernel<D, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     g_decode_attr_set[which] = 1;
   }
   dim3 grid(num_splits, num_kv, batch);
-  int rc = ullm_launch_kernel(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), (size_t)S::BYTES, st,
+  g_decode_last_cluster = 0;
+  if (g_decode_cluster == 1 && num_splits > 1 && num_splits <= 8) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.dynamicSmemBytes = (size_t)S::BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)num_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_ullm_pdl ? 2 : 1;
+    if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, true>, (const __nv_bfloat16*)q, q_row_stride,
+                           (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table, max_pages, req_slots,
+                           kv_len, (__nv_bfloat16*)out, part_o, part_ml, num_q, num_kv, page_size, window,
+                           scale * 1.4426950408889634f, num_pages, status) == cudaSuccess) {
+      g_decode_last_cluster = 1;
+      return ULLM_OK;
+    }
+    cudaGetLastError();
+    g_decode_cluster = -1;  // this device does not take the cluster launch: scratch arrays and merge kernel from now on
+  }
+  int rc = ullm_launch_kernel(decode_attention_kernel<D, false>, grid, dim3(DEC_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
       max_pages, req_slots, kv_len, (__nv_bfloat16*)out, part_o, part_ml, num_q, num_kv, page_size, window,
       scale * 1.4426950408889634f, num_pages, status);

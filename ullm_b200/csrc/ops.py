@@ -85,6 +85,12 @@ class Kernels:
             self.lib.ullm_set_max_smem_carveout(1)
         self.decode_split_target = int(os.environ.get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
+        # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
+        # scratch arrays and a second kernel
+        # ("auto": for one or two requests, where it measured 1.5 % faster per step; at eight requests it is 1.5 %
+        # slower than the merge kernel)
+        mode = os.environ.get("ULLM_B200_DECODE_CLUSTER", "auto")
+        self.decode_cluster_merge = {"1": True, "0": False}.get(mode, "auto")
         # decode attention on the tcgen05 tensor cores (head size 128), the batch's keys cut evenly over the blocks
         self.use_tcgen05_decode = os.environ.get("ULLM_B200_DECODE_TC", "0") == "1"
         # decode attention: the batch's keys cut evenly over the warps (True), every request split alike (False),
@@ -147,6 +153,10 @@ class Kernels:
         L.ullm_decode_attention_tcgen05_supported.restype = c_int
         L.ullm_decode_attention_tcgen05_scratch_floats.argtypes = [I]
         L.ullm_decode_attention_tcgen05_scratch_floats.restype = c_longlong
+        L.ullm_decode_attention_cluster_merge.argtypes = [I]
+        L.ullm_decode_attention_cluster_merge.restype = None
+        L.ullm_decode_attention_last_used_cluster.argtypes = []
+        L.ullm_decode_attention_last_used_cluster.restype = c_int
         L.ullm_sample_force_one_block.argtypes = [I]
         L.ullm_sample_force_one_block.restype = None
         L.ullm_sample_last_used_cluster.argtypes = []
@@ -506,14 +516,16 @@ class Kernels:
                 self.launches += 1  # the merge of the shared pairs
                 self.attention_path = "decode_tcgen05" if tc else "decode_balanced"
                 return
-            splits = max(1, min(32, -(-self.decode_split_target // (T * num_kv))))
+            cluster = T <= 2 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
+            self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
+            splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
             scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32)
             self._check(self.lib.ullm_decode_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
                 int(window), float(scale), splits, num_pages, _ptr(self.status), _stream()),
                 f"decode_attention (head_dim {head_dim})")
-            if splits > 1:
+            if splits > 1 and not self.lib.ullm_decode_attention_last_used_cluster():
                 self.launches += 1  # the merge of the splits
             self.attention_path = "decode"
             return
@@ -551,6 +563,11 @@ class Kernels:
         if logits.stride(1) != 1 or out.numel() < R:
             raise KernelError("argmax: logits rows must be contiguous and out must hold one id per row")
         self._check(self.lib.ullm_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+
+    def set_decode_cluster_merge(self, on: bool) -> None:
+        """The splits of the per-request decode attention merge inside a cluster (True) or through scratch arrays
+        and the merge kernel (False; tests compare the two), or "auto": the first for one or two requests."""
+        self.decode_cluster_merge = on if on == "auto" else bool(on)
 
     def sample_force_one_block(self, on: bool) -> None:
         """Rows go to the one-block sampling kernel instead of the cluster kernel (tests compare the two)."""
