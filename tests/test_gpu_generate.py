@@ -117,6 +117,25 @@ def test_graphs_recorded_at_start_up_are_the_ones_generation_replays(tmp_path):
     assert dg.replays > 0 and all(dg.graphs[k][0] is g for k, g in held.items())
 
 
+@pytest.mark.needs_cuda
+def test_a_recorded_graph_survives_larger_steps_that_come_later(tmp_path):
+    """Step buffers are made at their final size at first use (a row per token of the largest step, a row per
+    request slot), so a decode graph recorded after a short prompt is still good after a prompt that fills the
+    token budget and after a larger batch: it is the same graph object, and the workspace's generation stands."""
+    from ullm_b200 import SamplingParams
+
+    llm, cfg, w = make_llm(tmp_path, "D", dtype="bfloat16", max_bs=4, num_pages=64, max_num_batched_tokens=64)
+    sp = SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    llm.generate_batch([random_ids(cfg["vocab_size"], 5, 600)], sp)
+    dg, ws = llm.engine.decode_graphs, llm.engine.runner.workspace
+    held, gen = {k: v[0] for k, v in dg.graphs.items()}, ws.generation
+    assert held
+    prompts = [random_ids(cfg["vocab_size"], n, 601 + n) for n in (150, 64, 9, 31)]
+    llm.generate_batch(prompts, sp)
+    assert ws.generation == gen
+    assert all(dg.graphs[k][0] is g for k, g in held.items())
+
+
 def test_finish_rules(tmp_path):
     from ullm_b200 import SamplingParams
 

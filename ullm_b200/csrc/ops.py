@@ -519,7 +519,10 @@ class Kernels:
             cluster = T <= 2 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
             self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
             splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
-            scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32)
+            # (splits x rows stays below the blocks aimed for, per kv head, plus one split per row)
+            most = num_q * (self.decode_split_target // num_kv + max(T, getattr(ctx.workspace, "max_requests", 0)))
+            scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32,
+                                        reserve=most)
             self._check(self.lib.ullm_decode_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,

@@ -40,22 +40,34 @@ class Workspace:
     """Named activation buffers that persist across steps (so a captured CUDA
     graph finds them at the same address).  `get` returns the first `rows` rows;
     a buffer grows when more rows are asked for than it has, which bumps
-    `generation` (anything that recorded addresses must be re-recorded)."""
+    `generation` (anything that recorded addresses must be re-recorded).  To
+    keep that rare, a buffer is made at once for what its caller says it may
+    ever need (`reserve` rows): per-token buffers for the largest step
+    (`max_tokens`), per-request buffers for all request slots (`max_requests`)."""
 
-    def __init__(self, device, min_rows: int = 0):
+    def __init__(self, device, max_tokens: int = 0, max_requests: int = 0):
         self.device = device
-        self.min_rows = min_rows
+        self.max_tokens = max_tokens
+        self.max_requests = max_requests
         self.buffers: dict[str, torch.Tensor] = {}
         self.generation = 0
 
-    def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, rows: int, cols: int, dtype: torch.dtype, reserve: int = 0) -> torch.Tensor:
         buf = self.buffers.get(name)
         if buf is None or buf.shape[0] < rows or buf.shape[1] != cols or buf.dtype != dtype:
-            cap = max(rows, self.min_rows if buf is None else buf.shape[0], 1)
+            cap = max(rows, reserve, 0 if buf is None else buf.shape[0], 1)
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self.buffers[name] = buf
             self.generation += 1
         return buf[:rows]
+
+    def tokens(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer with a row per token of the step."""
+        return self.get(name, rows, cols, dtype, reserve=self.max_tokens)
+
+    def requests(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer with a row per request of the step (more rows when a caller wants logits at many places)."""
+        return self.get(name, rows, cols, dtype, reserve=self.max_requests)
 
 
 @dataclass

@@ -105,7 +105,7 @@ class ModelRunner:
         self.staging = StepStaging(self.device, max_step_tokens, max_requests, len(self.cache.groups))
         # decode steps have few integers: a small buffer of their own keeps their copy small
         self.decode_staging = StepStaging(self.device, max_requests, max_requests, len(self.cache.groups))
-        self.workspace = Workspace(self.device)
+        self.workspace = Workspace(self.device, max_tokens=max_step_tokens, max_requests=max_requests)
         # per-request state of fixed size: the token each request sampled last, by request slot
         self.last_tokens = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
         self.steps_run = 0

@@ -95,7 +95,7 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx, cache):
         K = kernels()
         T = x.shape[0]
-        qkv = ctx.workspace.get("attn.qkv", T, self.q_size + 2 * self.kv_size, x.dtype)
+        qkv = ctx.workspace.tokens("attn.qkv", T, self.q_size + 2 * self.kv_size, x.dtype)
         linear(x, self.w_qkv, qkv, self.b_qkv)
         g = cache.group
         tables = self.position.tables() if self.position is not None else {}
@@ -109,13 +109,13 @@ class PagedAttention(Mixer):
             ctx.positions, g.slot_mapping if cache.writes else None,
             cache.k_pages, cache.v_pages,
         )
-        attn = ctx.workspace.get("attn.out", T, self.q_size, x.dtype)
+        attn = ctx.workspace.tokens("attn.out", T, self.q_size, x.dtype)
         K.paged_attention(
             qkv, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len,
             ctx.token_req,
             self.num_heads, self.num_kv_heads, self.head_dim, g.page_size,
             self.window or 0, self.scale, ctx,
         )
-        out = ctx.workspace.get("mixer.out", T, self.hidden_size, x.dtype)
+        out = ctx.workspace.tokens("mixer.out", T, self.hidden_size, x.dtype)
         linear(attn, self.tensors["o_proj.weight"], out)
         return out

@@ -40,7 +40,7 @@ class PreNormResidualBlock(Block):
         block, with residual None).  Returns (feed-forward output, residual);
         the caller's final norm adds them."""
         T = x.shape[0]
-        h = ctx.workspace.get("block.normed", T, x.shape[1], x.dtype)
+        h = ctx.workspace.tokens("block.normed", T, x.shape[1], x.dtype)
         if residual is None:
             residual = x
             self.mixer_norm.forward(x, None, out=h)

@@ -40,9 +40,9 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         I = self.intermediate_size
-        gu = ctx.workspace.get("mlp.gate_up", T, 2 * I, x.dtype)
-        act = ctx.workspace.get("mlp.act", T, I, x.dtype)
+        gu = ctx.workspace.tokens("mlp.gate_up", T, 2 * I, x.dtype)
+        act = ctx.workspace.tokens("mlp.act", T, I, x.dtype)
         kernels().linear_act_mul(x, self.w_gate_up, act, gu, _ACTIVATIONS[self.activation])
-        out = ctx.workspace.get("ffn.out", T, self.hidden_size, x.dtype)
+        out = ctx.workspace.tokens("ffn.out", T, self.hidden_size, x.dtype)
         linear(act, self.tensors["down_proj.weight"], out)
         return out

@@ -66,7 +66,7 @@ class DecoderModel(Part):
         """Runs the blocks over the step's tokens.  Returns (y, residual): the
         last feed-forward output and the residual stream, before the final norm."""
         T = ctx.num_tokens
-        x = ctx.workspace.get("model.hidden", T, self.spec.hidden_size, self.dtype)
+        x = ctx.workspace.tokens("model.hidden", T, self.spec.hidden_size, self.dtype)
         self.embedding.forward(ctx.token_ids, x, ctx)
         residual = None
         for i, e in enumerate(self.schedule):
@@ -81,11 +81,11 @@ class DecoderModel(Part):
             return None
         K = kernels()
         H = self.spec.hidden_size
-        ys = ctx.workspace.get("head.y", R, H, self.dtype)
-        rs = ctx.workspace.get("head.res", R, H, self.dtype)
+        ys = ctx.workspace.requests("head.y", R, H, self.dtype)
+        rs = ctx.workspace.requests("head.res", R, H, self.dtype)
         K.gather_rows(y, ctx.logits_rows, ys)
         K.gather_rows(residual, ctx.logits_rows, rs)
         self.final_norm.forward(ys, rs, out=ys)
-        logits = ctx.workspace.get("head.logits", R, self.spec.vocab_size, torch.float32)
+        logits = ctx.workspace.requests("head.logits", R, self.spec.vocab_size, torch.float32)
         self.head.forward(ys, logits)
         return logits
