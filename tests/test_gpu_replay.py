@@ -340,3 +340,51 @@ def test_long_context_at_real_widths_prompt_portions_against_decode_steps():
     if kernels().lt_rows > 0:
         tuned = kernels()._lt_tuned
         assert any(k[0] == 2048 for k in tuned) and any(k[0] <= 2 for k in tuned), sorted(tuned)
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_random_configurations_follow_the_plain_implementation(tmp_path, seed):
+    """Configurations drawn at random from what config.json allows (head sizes in steps of 16 up to 256, any
+    number of heads and groups, widths and vocabularies that are no power of two, bias, tied head, windows, eps,
+    rotation base, page size): a sequence whole, with its last tokens one by one, and in portions of changing
+    size, in both dtypes, against the plain implementation."""
+    import random
+
+    import plain_model as pm
+    from conftest import device
+    from helpers import errors, TOL, TOL_RMS
+    from ullm_b200.engine import ModelRunner, StepEntry
+
+    rng = random.Random(1000 + seed)
+    D = rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 144, 256])
+    Hkv, G = rng.choice([1, 1, 2, 3, 5]), rng.choice([1, 2, 3, 4, 7, 8])
+    window = rng.choice([None, None, 24, 50])
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": rng.choice([1, 2, 3]),
+           "hidden_size": rng.choice([24, 40, 72, 100, 136, 200]), "num_attention_heads": Hkv * G,
+           "num_key_value_heads": Hkv, "head_dim": D, "intermediate_size": rng.choice([24, 56, 136, 200, 328]),
+           "vocab_size": rng.choice([97, 331, 517, 1000, 1031]), "rope_theta": rng.choice([10000.0, 1e6, 5e5]),
+           "rms_norm_eps": rng.choice([1e-6, 1e-5, 3e-6]), "attention_bias": rng.random() < 0.4,
+           "tie_word_embeddings": rng.random() < 0.5, "max_position_embeddings": 512, "torch_dtype": "float32"}
+    if window is not None:
+        cfg.update(use_sliding_window=True, sliding_window=window, max_window_layers=rng.choice([0, 1]))
+    page, n = rng.choice([4, 8, 16, 32]), rng.choice([70, 130, 201])
+    ids = random_ids(cfg["vocab_size"], n, seed)
+    chunks, left = [], n
+    while left:
+        c = min(rng.choice([2, 3, 7, 16, 33, 5]), left)
+        chunks.append(c)
+        left -= c
+    for dtype in ("float32", "bfloat16"):
+        w = pm.random_weights(cfg, seed=seed, std=0.05, norm_std=0.1)
+        if dtype == "bfloat16":
+            w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+        d = write_model_dir(str(tmp_path / f"m{dtype}"), cfg, w)
+        r = ModelRunner(d, dtype=dtype, device=device(), page_size=page, num_pages=2 * (-(-n // page)) + 2,
+                        max_requests=3, max_context=512, max_step_tokens=64, poison_cache=True)
+        ref = plain_logits(ids, w, cfg)
+        for name, cuts in (("whole", [n]), ("decode", [n - 9] + [1] * 9), ("portions", chunks)):
+            got = run_cut(r, name, ids, cuts)
+            mx, rms = errors(got, ref)
+            assert mx <= TOL[dtype] and rms <= TOL_RMS[dtype], (
+                f"{dtype}, {name}: max {mx:.2e}, rms {rms:.2e} of scale; {cfg}, page {page}")
+        r.cache.check_invariants()
