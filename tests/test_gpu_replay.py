@@ -388,3 +388,46 @@ def test_random_configurations_follow_the_plain_implementation(tmp_path, seed):
             assert mx <= TOL[dtype] and rms <= TOL_RMS[dtype], (
                 f"{dtype}, {name}: max {mx:.2e}, rms {rms:.2e} of scale; {cfg}, page {page}")
         r.cache.check_invariants()
+
+
+@pytest.mark.needs_cuda
+@pytest.mark.parametrize("tag", ["D", "E"])
+def test_mixed_steps_send_their_decode_rows_to_the_decode_kernel(tmp_path, tag):
+    """A step with one-token entries at its head and prompt portions behind them: the first go through the
+    decode attention kernel, the rest through the prompt kernel, each with its slice of the per-request arrays;
+    every row's logits follow the plain implementation (E has a sliding window on its last layer)."""
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine import StepEntry
+
+    runner, cfg, w, page = make_runner(tmp_path, tag, "bfloat16", num_pages=60, max_requests=6)
+    V = cfg["vocab_size"]
+    lens = {"d0": 70, "d1": 9, "d2": 33, "p0": 50, "p1": 21}
+    ids = {r: random_ids(V, n + 6, 700 + n) for r, n in lens.items()}
+    refs = {r: plain_logits(ids[r], w, cfg) for r in lens}
+    for r in ("d0", "d1", "d2"):
+        runner.add_request(r)
+        runner.step([StepEntry(r, ids[r][:lens[r]], [])])
+    runner.add_request("p0")
+    runner.add_request("p1")
+    old = kernels().mixed_decode_rows
+    kernels().mixed_decode_rows = 2
+    try:
+        done = {"p0": 0, "p1": 0}
+        for k, (n0, n1) in enumerate([(17, 5), (2, 16), (31, 0), (6, 6)]):
+            entries = [StepEntry(r, [ids[r][lens[r] + k]], [0]) for r in ("d0", "d1", "d2")]
+            for r, n in (("p0", n0), ("p1", n1)):
+                if n:
+                    entries.append(StepEntry(r, ids[r][done[r]:done[r] + n], list(range(n))))
+            lg = runner.step(entries).float().cpu()
+            assert kernels().attention_path in ("prefill_tcgen05", "prefill")  # the last kernel of the step
+            row = 0
+            for e in entries:
+                r, n = e.request_id, len(e.tokens)
+                at = lens[r] + k if r.startswith("d") else done[r]
+                assert_close(lg[row:row + n], refs[r][at:at + n], "bfloat16", f"{r}, step {k}")
+                row += n
+                if r.startswith("p"):
+                    done[r] += n
+    finally:
+        kernels().mixed_decode_rows = old
+    runner.check_device_status()

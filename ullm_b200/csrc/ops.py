@@ -91,6 +91,8 @@ class Kernels:
         # slower than the merge kernel)
         mode = os.environ.get("ULLM_B200_DECODE_CLUSTER", "auto")
         self.decode_cluster_merge = {"1": True, "0": False}.get(mode, "auto")
+        # a mixed step's leading one-token entries go to the decode attention kernel from this many on (0: never)
+        self.mixed_decode_rows = int(os.environ.get("ULLM_B200_MIXED_DECODE_ROWS", "4"))
         # decode attention on the tcgen05 tensor cores (head size 128), the batch's keys cut evenly over the blocks
         self.use_tcgen05_decode = os.environ.get("ULLM_B200_DECODE_TC", "0") == "1"
         # decode attention: the batch's keys cut evenly over the warps (True), every request split alike (False),
@@ -470,6 +472,55 @@ class Kernels:
             _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
             num_slots, _ptr(self.status), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
 
+    def _decode_rows(self, qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
+                     page_size, window, scale, num_pages, ragged, ctx) -> None:
+        """Decode attention of T one-token rows (row i belongs to request row i): streams the pages once."""
+        T = out.shape[0]
+        cu_q = None
+        balanced = ragged if self.use_balanced_decode == "auto" else self.use_balanced_decode
+        tc = self.use_tcgen05_decode and self.lib.ullm_decode_attention_tcgen05_supported(
+            head_dim, num_q, num_kv, T, page_size) and qkv.stride(0) % head_dim == 0
+        if tc or (balanced and self.lib.ullm_decode_attention_balanced_supported(
+                head_dim, num_q, num_kv, T, page_size)):
+            # both kernels cut the batch's keys evenly (over blocks, over warps) and share the scratch arrays
+            # and the merge kernel for the pairs that a cut went through
+            key = (head_dim, num_q, num_kv)
+            if key not in self._decb:
+                n = self.lib.ullm_decode_attention_balanced_scratch_floats(head_dim, num_q // num_kv)
+                if head_dim == 128:
+                    n = max(n, self.lib.ullm_decode_attention_tcgen05_scratch_floats(num_q // num_kv))
+                if n <= 0:
+                    raise KernelError("decode attention: cannot size its grid on this device")
+                self._decb[key] = (torch.empty(n, dtype=torch.float32, device="cuda"),
+                                   torch.zeros(513, dtype=torch.int32, device="cuda"),
+                                   torch.zeros(512 * num_q, dtype=torch.int32, device="cuda"))
+            part, prefix, flags = self._decb[key]
+            fn = self.lib.ullm_decode_attention_tcgen05 if tc else self.lib.ullm_decode_attention_balanced
+            self._check(fn(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(part), _ptr(prefix), _ptr(flags), T, num_q, num_kv, head_dim,
+                page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
+                f"decode_attention_{'tcgen05' if tc else 'balanced'} (head_dim {head_dim})")
+            self.launches += 1  # the merge of the shared pairs
+            self.attention_path = "decode_tcgen05" if tc else "decode_balanced"
+            return
+        cluster = T <= 2 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
+        self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
+        splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
+        # (splits x rows stays below the blocks aimed for, per kv head, plus one split per row)
+        most = num_q * (self.decode_split_target // num_kv + max(T, getattr(ctx.workspace, "max_requests", 0)))
+        scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32,
+                                    reserve=most)
+        self._check(self.lib.ullm_decode_attention(
+            _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+            _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+            int(window), float(scale), splits, num_pages, _ptr(self.status), _stream()),
+            f"decode_attention (head_dim {head_dim})")
+        if splits > 1 and not self.lib.ullm_decode_attention_last_used_cluster():
+            self.launches += 1  # the merge of the splits
+        self.attention_path = "decode"
+        return
+
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
                         head_dim, page_size, window, scale, ctx=None):
         """Attention of every row of the flat batch over its request's pages.
@@ -486,58 +537,36 @@ class Kernels:
         if k_pages.shape[-3:] != (page_size, num_kv, head_dim):
             raise KernelError(f"paged_attention: pages {tuple(k_pages.shape)} != [*, {page_size}, {num_kv}, {head_dim}]")
         num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
-        if (ctx is not None and ctx.decode_only and T == ctx.num_requests and qkv.dtype == torch.bfloat16
-                and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
-            # one token per request: stream the pages once
-            balanced = getattr(ctx, "ragged", False) if self.use_balanced_decode == "auto" else self.use_balanced_decode
-            tc = self.use_tcgen05_decode and self.lib.ullm_decode_attention_tcgen05_supported(
-                head_dim, num_q, num_kv, T, page_size) and qkv.stride(0) % head_dim == 0
-            if tc or (balanced and self.lib.ullm_decode_attention_balanced_supported(
-                    head_dim, num_q, num_kv, T, page_size)):
-                # both kernels cut the batch's keys evenly (over blocks, over warps) and share the scratch arrays
-                # and the merge kernel for the pairs that a cut went through
-                key = (head_dim, num_q, num_kv)
-                if key not in self._decb:
-                    n = self.lib.ullm_decode_attention_balanced_scratch_floats(head_dim, num_q // num_kv)
-                    if head_dim == 128:
-                        n = max(n, self.lib.ullm_decode_attention_tcgen05_scratch_floats(num_q // num_kv))
-                    if n <= 0:
-                        raise KernelError("decode attention: cannot size its grid on this device")
-                    self._decb[key] = (torch.empty(n, dtype=torch.float32, device="cuda"),
-                                       torch.zeros(513, dtype=torch.int32, device="cuda"),
-                                       torch.zeros(512 * num_q, dtype=torch.int32, device="cuda"))
-                part, prefix, flags = self._decb[key]
-                fn = self.lib.ullm_decode_attention_tcgen05 if tc else self.lib.ullm_decode_attention_balanced
-                self._check(fn(
-                    _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-                    _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(part), _ptr(prefix), _ptr(flags), T, num_q, num_kv, head_dim,
-                    page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
-                    f"decode_attention_{'tcgen05' if tc else 'balanced'} (head_dim {head_dim})")
-                self.launches += 1  # the merge of the shared pairs
-                self.attention_path = "decode_tcgen05" if tc else "decode_balanced"
-                return
-            cluster = T <= 2 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
-            self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
-            splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
-            # (splits x rows stays below the blocks aimed for, per kv head, plus one split per row)
-            most = num_q * (self.decode_split_target // num_kv + max(T, getattr(ctx.workspace, "max_requests", 0)))
-            scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32,
-                                        reserve=most)
-            self._check(self.lib.ullm_decode_attention(
-                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
-                int(window), float(scale), splits, num_pages, _ptr(self.status), _stream()),
-                f"decode_attention (head_dim {head_dim})")
-            if splits > 1 and not self.lib.ullm_decode_attention_last_used_cluster():
-                self.launches += 1  # the merge of the splits
-            self.attention_path = "decode"
+        decode_ok = (ctx is not None and qkv.dtype == torch.bfloat16
+                     and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv))
+        if decode_ok and ctx.decode_only and T == ctx.num_requests:
+            self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
+                              page_size, window, scale, num_pages, getattr(ctx, "ragged", False), ctx)
             return
+        # A step that mixes decoded tokens with prompt portions: the one-token entries at its head (the scheduler
+        # puts them first) go to the decode kernel, which streams their pages once; the prompt kernels would give
+        # each of them a 128-row tile of its own.  The rest of the step follows with its own slices of the
+        # per-request arrays (cu_q holds absolute rows, so q and out stay whole).
+        n_dec = 0
+        if decode_ok and self.mixed_decode_rows > 0 and getattr(ctx, "cu_q_host", None) is not None:
+            cq = ctx.cu_q_host
+            while n_dec < ctx.num_requests and cq[n_dec] == n_dec and cq[n_dec + 1] == n_dec + 1:
+                n_dec += 1
+            if n_dec < self.mixed_decode_rows or n_dec == ctx.num_requests:
+                n_dec = 0
+        if n_dec:
+            lens = [ctx.start_positions_host[i] + 1 for i in range(n_dec)]
+            ragged = n_dec > 1 and 2 * n_dec * max(lens) > 3 * sum(lens)
+            self._decode_rows(qkv[:n_dec], out[:n_dec], k_pages, v_pages, block_table, req_slots[:n_dec], kv_len[:n_dec],
+                              num_q, num_kv, head_dim, page_size, window, scale, num_pages, ragged, ctx)
+            req_slots, cu_q, kv_len = req_slots[n_dec:], cu_q[n_dec:], kv_len[n_dec:]
+        num_requests = (ctx.num_requests - n_dec) if ctx is not None else 0
         if (ctx is not None and qkv.dtype == torch.bfloat16 and self.use_tcgen05_attention
                 and self.lib.ullm_prefill_attention_tcgen05_supported(head_dim, num_q, num_kv, page_size)
                 and qkv.stride(0) % head_dim == 0):
             self._check(self.lib.ullm_prefill_attention_tcgen05(
                 _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
-                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q, num_kv,
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, num_requests, num_q, num_kv,
                 head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
                 f"prefill_attention_tcgen05 (head_dim {head_dim})")
             self.attention_path = "prefill_tcgen05"
@@ -547,11 +576,13 @@ class Kernels:
                 and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv)):
             self._check(self.lib.ullm_prefill_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
-                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q, num_kv,
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, num_requests, num_q, num_kv,
                 head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
                 f"prefill_attention (head_dim {head_dim})")
             self.attention_path = "prefill"
             return
+        if n_dec:
+            raise KernelError("paged_attention: a step's decode rows were split off but no prompt kernel takes the rest")
         self.attention_path = "generic"
         self._check(self.lib.ullm_paged_attention_generic(
             _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
