@@ -299,7 +299,10 @@ class Kernels:
         key = (M, N, K, out_f32)
         flush = None
         if tune and key not in self._lt_tuned and not torch.cuda.is_current_stream_capturing():
-            flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")  # larger than L2; gone after this call
+            try:
+                flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")  # larger than L2; gone after this call
+            except torch.cuda.OutOfMemoryError:
+                flush = None  # no room to time anything: the library's first candidate it is
             self._lt_tuned.add(key)
         rc = self.lib.ullm_lt_linear(_ptr(x), _ptr(weight), _ptr(out), M, N, K, out_f32, _ptr(self._lt_ws),
                                      self._lt_ws.numel(), 1 if flush is not None else 0, _ptr(flush),
