@@ -9,6 +9,7 @@ and a missing or unbuildable library is an error at first use.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -76,8 +77,6 @@ class Kernels:
         self._f32_out_mm = None
         self._lin_ws = None  # partial sums and tile counters of the tcgen05 product, made at its first use
         self._lin_counters = None
-        import os
-
         self.pdl = False
         if os.environ.get("ULLM_B200_PDL", "0") == "1":
             self.set_pdl(True)
