@@ -168,14 +168,14 @@ def test_requests_and_cancellations_reach_the_engine_only_between_steps():
         return got
 
     async def run():
-        first = asyncio.create_task(consume("a", 12))
+        first = asyncio.create_task(consume("a", 40))
         await asyncio.sleep(0.03)  # a step is running now
         second = asyncio.create_task(consume("b", 6))
         third = asyncio.create_task(consume("c", 30, cancel_after=2))
         await asyncio.sleep(0.01)
         with pytest.raises(ValueError, match="already exists"):
             await consume("a", 3)  # a duplicate id: the error comes back to its caller only
-        assert await first == 12 and await second == 6 and await third == 2
+        assert await first == 40 and await second == 6 and await third == 2
         await llm.shutdown()
 
     asyncio.run(run())
