@@ -69,6 +69,9 @@ class CpuKernels:
         a = g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")
         out.copy_((a * u).to(out.dtype))
 
+    def decode_fusion_applies(self, *args, **kwargs):
+        return False  # the stand-in always prepares q and k in a step of their own
+
     def qk_norm_rope_store(self, qkv, num_q, num_kv, D, q_w, k_w, eps, cos, sin, rotary_dim, positions,
                            slot_mapping, k_pages, v_pages):
         self._count("qk_norm_rope_store")

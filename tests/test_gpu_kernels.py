@@ -757,3 +757,76 @@ def test_library_product_inside_a_stream_capture_takes_an_untimed_shape_without_
     assert K().lt_linear(x, w, out)
     assert (24, 264, 320, 0) in K()._lt_tuned
     assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page,window,with_norm", [
+    (32, 8, 128, 16, 0, True), (8, 8, 128, 16, 0, True), (12, 3, 64, 8, 0, True), (6, 2, 128, 32, 40, False),
+    (16, 1, 64, 16, 0, True),
+])
+@pytest.mark.parametrize("batch", [1, 3, 40])
+def test_decode_attention_that_prepares_q_k_and_v_itself(Hq, Hkv, D, page, window, with_norm, batch):
+    """The per-request decode kernel with the q/k norm, the rotation and the cache write inside it, against the
+    two-kernel way (`qk_norm_rope_store`, then the attention): the same attention output, the same new key and
+    value in the cache (to a rounding of bfloat16: the sums of squares are added in another order); rows of
+    length 0 write nothing; every split count, with the cluster merge and with the merge kernel."""
+    dtype = torch.bfloat16
+    lens = [1, 15, 16, 17, 63, 64, 65, 300, 1000, 2049, 0, 33, 129, 511, 77, 5]
+    kv_lens = [lens[(i * 5 + batch) % len(lens)] for i in range(batch)]
+    max_pages = -(-max(kv_lens + [1]) // page) + 1
+    pages = sum(-(-k // page) for k in kv_lens) + 2
+    g = torch.Generator().manual_seed(90 + batch)
+    perm = torch.randperm(pages, generator=g)
+    bt = torch.full((batch, max_pages), -1, dtype=torch.int32)
+    used = 0
+    for r, kl in enumerate(kv_lens):
+        n = -(-kl // page)
+        bt[r, :n] = perm[used:used + n].int()
+        used += n
+    slot_mapping = torch.tensor([int(bt[r, (kl - 1) // page]) * page + (kl - 1) % page if kl > 0 else -1
+                                 for r, kl in enumerate(kv_lens)], dtype=torch.int32, device="cuda")
+    positions = torch.tensor([max(kl - 1, 0) for kl in kv_lens], dtype=torch.int32, device="cuda")
+    kp0 = rnd(pages, page, Hkv, D, seed=91, dtype=dtype)
+    vp0 = rnd(pages, page, Hkv, D, seed=92, dtype=dtype)
+    qkv0 = rnd(batch, (Hq + 2 * Hkv) * D, seed=93, dtype=dtype)
+    q_w = (1 + 0.1 * rnd(D, seed=94)) if with_norm else None
+    k_w = (1 + 0.1 * rnd(D, seed=95)) if with_norm else None
+    pos = torch.arange(2100, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    cos, sin = torch.cos(pos[:, None] * inv).cuda().contiguous(), torch.sin(pos[:, None] * inv).cuda().contiguous()
+    slots = torch.arange(batch, dtype=torch.int32, device="cuda")
+    cu = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
+    kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    scale = D ** -0.5
+    old = K().use_balanced_decode, K().use_tcgen05_decode, K().decode_cluster_merge, K().decode_split_target
+    K().use_balanced_decode, K().use_tcgen05_decode = False, False
+    try:
+        for cluster, target in ((True, 400), (False, 400), (False, 4000), (True, 1)):
+            K().set_decode_cluster_merge(cluster)
+            K().decode_split_target = target
+            res = []
+            for fused in (False, True):
+                qkv, kp, vp = qkv0.clone(), kp0.clone(), vp0.clone()
+                out = torch.full((batch, Hq * D), 9.0, dtype=dtype, device="cuda")
+                ctx = _DecodeCtx(batch)
+                fuse = None
+                if fused:
+                    assert K().decode_fusion_applies(ctx, qkv, Hq, Hkv, D, page, D, cos)
+                    fuse = dict(q_w=q_w, k_w=k_w, eps=1e-6, cos=cos, sin=sin, positions=positions, slot_mapping=slot_mapping)
+                else:
+                    K().qk_norm_rope_store(qkv, Hq, Hkv, D, q_w, k_w, 1e-6, cos, sin, D, positions, slot_mapping, kp, vp)
+                K().paged_attention(qkv, out, kp, vp, bt.cuda(), slots, cu, kvl, slots, Hq, Hkv, D, page, window, scale,
+                                    ctx, **({"fuse": fuse} if fused else {}))
+                K().raise_on_status()
+                res.append((out.float(), kp.float(), vp.float()))
+            (o0, k0, v0), (o1, k1, v1) = res
+            assert torch.equal(v0, v1)
+            assert (k0 - k1).abs().max().item() <= 2 ** -7 * max(k0.abs().max().item(), 1.0)
+            assert (k0 != kp0.float()).any() or all(kl == 0 for kl in kv_lens)  # the new keys were written
+            live = [r for r, kl in enumerate(kv_lens) if kl > 0]
+            scale_o = max(o0[live].abs().max().item(), 1e-6)
+            assert (o0[live] - o1[live]).abs().max().item() <= 2e-2 * scale_o, (cluster, target)
+            assert (o1[[r for r in range(batch) if r not in live]] == 0).all()
+    finally:
+        K().use_balanced_decode, K().use_tcgen05_decode = old[0], old[1]
+        K().set_decode_cluster_merge(old[2])
+        K().decode_split_target = old[3]

@@ -23,6 +23,24 @@
 
 namespace cg = cooperative_groups;
 
+// What the kernel needs to prepare q and the new key and value itself (cos == nullptr: they come prepared, as
+// qk_rope_store.cu leaves them): per-head RMSNorm weights (or null), the rotation tables [positions, D / 2], the
+// row's position and cache slot.  The arithmetic is that of qk_norm_rope_store_bf16_kernel: 32-bit sums and
+// rotation, one rounding to bfloat16.
+struct DecFuse {
+  const float* q_w;
+  const float* k_w;
+  const float* cos_t;
+  const float* sin_t;
+  const int* positions;
+  const int* slot_mapping;  // null: this execution does not write the cache
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  long long num_slots;
+  int max_positions;
+  float eps;
+};
+
 // CL: the splits of a (request, kv head) pair are the blocks of one thread-block cluster (at most 8) and merge
 // their partials through distributed shared memory; no scratch arrays, no second kernel.
 template <int D, bool CL>
@@ -32,7 +50,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
                         const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_slots,
                         const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int num_q, int num_kv, int page_size, int window,
-                        float scale_log2, long long num_pages, int* status) {
+                        float scale_log2, long long num_pages, int* status, const DecFuse fu) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float cm[CL ? 16 * (D + 2) : 1];  // this block's merged partial (cluster form): [head][D outputs, max, sum]
   pdl_launch_dependents();
@@ -70,6 +88,111 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
       qa[kk][1] = r1 < group ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + c) : 0u;
       qa[kk][2] = r0 < group ? *reinterpret_cast<const unsigned*>(q0 + kk * 16 + 8 + c) : 0u;
       qa[kk][3] = r1 < group ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + 8 + c) : 0u;
+    }
+  }
+  uint4 new_kv = make_uint4(0, 0, 0, 0);  // this lane's 16 bytes of the new key (lanes < D / 8) or value (the next D / 8)
+  bool have_new = false;
+  if (fu.cos_t != nullptr) {
+    int qpos = kvl > 0 ? fu.positions[b] : 0;
+    if (qpos < 0 || qpos >= fu.max_positions) {
+      if (threadIdx.x == 0 && kvl > 0) ullm_report(status, ULLM_STATUS_POSITION, b, qpos);
+      qpos = 0;
+    }
+    // ---- q: RMSNorm over the head, then the rotation; a thread holds, of rows r0 and r1, the columns
+    // 16 kk + c, + 1, + 8, + 9 for every kk: the rotation partner (D / 2 further) is its own kk + KSTEPS / 2 ----
+    const int c = (lane & 3) * 2;
+    const float* cr = fu.cos_t + (long long)qpos * (D / 2);
+    const float* sr = fu.sin_t + (long long)qpos * (D / 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {  // row r0 (fragment words 0, 2), then row r1 (words 1, 3)
+      float y[KSTEPS][4];
+      float ss = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&qa[kk][half]);
+        const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&qa[kk][half + 2]);
+        y[kk][0] = __bfloat162float(a.x), y[kk][1] = __bfloat162float(a.y);
+        y[kk][2] = __bfloat162float(bb.x), y[kk][3] = __bfloat162float(bb.y);
+        ss += y[kk][0] * y[kk][0] + y[kk][1] * y[kk][1] + y[kk][2] * y[kk][2] + y[kk][3] * y[kk][3];
+      }
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      if (fu.q_w != nullptr) {
+        const float rstd = rsqrtf(ss / (float)D + fu.eps);
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          const float2 w0 = *reinterpret_cast<const float2*>(fu.q_w + kk * 16 + c);
+          const float2 w1 = *reinterpret_cast<const float2*>(fu.q_w + kk * 16 + 8 + c);
+          y[kk][0] *= rstd * w0.x, y[kk][1] *= rstd * w0.y, y[kk][2] *= rstd * w1.x, y[kk][3] *= rstd * w1.y;
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS / 2; ++kk) {
+        const float2 c0 = *reinterpret_cast<const float2*>(cr + kk * 16 + c), c1 = *reinterpret_cast<const float2*>(cr + kk * 16 + 8 + c);
+        const float2 s0 = *reinterpret_cast<const float2*>(sr + kk * 16 + c), s1 = *reinterpret_cast<const float2*>(sr + kk * 16 + 8 + c);
+        const float cs[4] = {c0.x, c0.y, c1.x, c1.y}, sn[4] = {s0.x, s0.y, s1.x, s1.y};
+        float lo4[4], hi4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = y[kk][i], p2 = y[kk + KSTEPS / 2][i];
+          lo4[i] = a * cs[i] - p2 * sn[i];
+          hi4[i] = p2 * cs[i] + a * sn[i];
+        }
+        qa[kk][half] = pack_bf16(lo4[0], lo4[1]);
+        qa[kk][half + 2] = pack_bf16(lo4[2], lo4[3]);
+        qa[kk + KSTEPS / 2][half] = pack_bf16(hi4[0], hi4[1]);
+        qa[kk + KSTEPS / 2][half + 2] = pack_bf16(hi4[2], hi4[3]);
+      }
+      // (rows >= group were loaded as zeros and stay zeros: 0 * rstd * w, rotated, is 0)
+    }
+    // ---- the new key and value: the warp whose keys end with the newest one prepares them, writes them to the
+    // cache for the steps to come, and keeps them to put them into its own last tile once that has landed (what
+    // the tile's load finds in the slot meanwhile does not matter) ----------------------------------------------
+    if (fu.slot_mapping != nullptr && n_keys > 0 && w_end == lo + n_keys && w_end > w_begin) {
+      constexpr int LW = D / 8;  // lanes of a row
+      long long slot = fu.slot_mapping[b];
+      if (slot >= fu.num_slots) {
+        if (lane == 0) ullm_report(status, ULLM_STATUS_SLOT, b, (int)slot);
+        slot = -1;
+      }
+      if (slot >= 0) {
+        const int sl = lane % LW, which = lane / LW;  // 0: the key row, 1: the value row (further lanes idle)
+        const __nv_bfloat16* src = q + (long long)b * q_row_stride + (long long)(num_q + (which == 1 ? num_kv : 0) + kh) * D + sl * 8;
+        const uint4 raw = which < 2 ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+        float y[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          y[i] = __bfloat162float(e[i]);
+          ss += y[i] * y[i];
+        }
+#pragma unroll
+        for (int off = LW / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);  // every lane takes part
+        if (fu.k_w != nullptr) {
+          const float rstd = rsqrtf(ss / (float)D + fu.eps);
+          const float4 w0 = *reinterpret_cast<const float4*>(fu.k_w + sl * 8), w1 = *reinterpret_cast<const float4*>(fu.k_w + sl * 8 + 4);
+          y[0] *= rstd * w0.x, y[1] *= rstd * w0.y, y[2] *= rstd * w0.z, y[3] *= rstd * w0.w;
+          y[4] *= rstd * w1.x, y[5] *= rstd * w1.y, y[6] *= rstd * w1.z, y[7] *= rstd * w1.w;
+        }
+        const int j0 = (sl % (LW / 2)) * 8;
+        const float4 c0 = *reinterpret_cast<const float4*>(cr + j0), c1 = *reinterpret_cast<const float4*>(cr + j0 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sr + j0), s1 = *reinterpret_cast<const float4*>(sr + j0 + 4);
+        const float c8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float s8[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        uint4 ov;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float partner = __shfl_xor_sync(0xffffffffu, y[i], LW / 2);
+          const float v = sl < LW / 2 ? y[i] * c8[i] - partner * s8[i] : y[i] * c8[i] + partner * s8[i];
+          ob[i] = __float2bfloat16_rn(v);
+        }
+        new_kv = which == 0 ? ov : raw;
+        have_new = which < 2;
+        if (which == 0) *reinterpret_cast<uint4*>(fu.k_cache + (slot * num_kv + kh) * D + sl * 8) = ov;
+        if (which == 1) *reinterpret_cast<uint4*>(fu.v_cache + (slot * num_kv + kh) * D + sl * 8) = raw;
+      }
     }
   }
 
@@ -116,8 +239,17 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     cp_async_commit();
     cp_async_wait<DEC_STAGES - 1>();
     __syncwarp();
-    const unsigned char* kbuf = ring + (it % DEC_STAGES) * 2 * S::TILE_BYTES;
-    const unsigned char* vbuf = kbuf + S::TILE_BYTES;
+    unsigned char* kbuf = ring + (it % DEC_STAGES) * 2 * S::TILE_BYTES;
+    unsigned char* vbuf = kbuf + S::TILE_BYTES;
+    if (it == tiles - 1 && __any_sync(0xffffffffu, have_new)) {
+      // the newest key and value, prepared above, go into their row of this tile
+      if (have_new) {
+        constexpr int LW = D / 8;
+        const int row = w_end - 1 - (w_begin + it * DEC_TILE), ch = lane % LW;
+        *reinterpret_cast<uint4*>((lane < LW ? kbuf : vbuf) + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16)) = new_kv;
+      }
+      __syncwarp();
+    }
     // ---- scores: 2 n-tiles of 8 keys ------------------------------------------------
     float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -318,7 +450,8 @@ template <int D>
 static int launch_decode(int which, const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
                          const int* block_table, int max_pages, const int* req_slots, const int* kv_len, void* out,
                          float* part_o, float* part_ml, int batch, int num_q, int num_kv, int page_size, int window,
-                         float scale, int num_splits, long long num_pages, int* status, cudaStream_t st) {
+                         float scale, int num_splits, long long num_pages, int* status, cudaStream_t st,
+                         const DecFuse& fu) {
   using S = DecodeSmem<D>;
   if (!g_decode_attr_set[which]) {
     if (cudaFuncSetAttribute(decode_attention_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
@@ -352,7 +485,7 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
     if (cudaLaunchKernelEx(&cfg, decode_attention_kernel<D, true>, (const __nv_bfloat16*)q, q_row_stride,
                            (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table, max_pages, req_slots,
                            kv_len, (__nv_bfloat16*)out, part_o, part_ml, num_q, num_kv, page_size, window,
-                           scale * 1.4426950408889634f, num_pages, status) == cudaSuccess) {
+                           scale * 1.4426950408889634f, num_pages, status, fu) == cudaSuccess) {
       g_decode_last_cluster = 1;
       return ULLM_OK;
     }
@@ -362,7 +495,7 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
   int rc = ullm_launch_kernel(decode_attention_kernel<D, false>, grid, dim3(DEC_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
       max_pages, req_slots, kv_len, (__nv_bfloat16*)out, part_o, part_ml, num_q, num_kv, page_size, window,
-      scale * 1.4426950408889634f, num_pages, status);
+      scale * 1.4426950408889634f, num_pages, status, fu);
   if (rc != ULLM_OK) return rc;
   if (num_splits > 1)
     rc = ullm_launch_kernel(decode_merge_kernel<D>, dim3(batch * num_q), dim3(D), 0, st, (const float*)part_o,
@@ -381,11 +514,11 @@ extern "C" long long ullm_decode_attention_scratch_floats(int batch, int num_q, 
   return (long long)batch * num_q * num_splits * (head_dim + 2);
 }
 
-extern "C" int ullm_decode_attention(const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
-                                     const int* block_table, int max_pages, const int* req_slots, const int* kv_len,
-                                     void* out, float* scratch, int batch, int num_q, int num_kv, int head_dim,
-                                     int page_size, int window, float scale, int num_splits, long long num_pages,
-                                     int* status, void* stream) {
+static int decode_attention_impl(const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
+                                 const int* block_table, int max_pages, const int* req_slots, const int* kv_len,
+                                 void* out, float* scratch, int batch, int num_q, int num_kv, int head_dim,
+                                 int page_size, int window, float scale, int num_splits, long long num_pages,
+                                 int* status, void* stream, const DecFuse& fu) {
   cudaStream_t st = (cudaStream_t)stream;
   if (batch < 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || num_splits <= 0 || window < 0)
     return ULLM_ERR_BAD_SIZE;
@@ -397,9 +530,48 @@ extern "C" int ullm_decode_attention(const void* q, long long q_row_stride, cons
   if (head_dim == 64)
     return launch_decode<64>(0, q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out,
                              part_o, part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages,
-                             status, st);
+                             status, st, fu);
   return launch_decode<128>(1, q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, part_o,
-                            part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages, status, st);
+                            part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages, status, st, fu);
+}
+
+extern "C" int ullm_decode_attention(const void* q, long long q_row_stride, const void* k_cache, const void* v_cache,
+                                     const int* block_table, int max_pages, const int* req_slots, const int* kv_len,
+                                     void* out, float* scratch, int batch, int num_q, int num_kv, int head_dim,
+                                     int page_size, int window, float scale, int num_splits, long long num_pages,
+                                     int* status, void* stream) {
+  DecFuse fu = {};
+  return decode_attention_impl(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, scratch,
+                               batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages, status,
+                               stream, fu);
+}
+
+// The same with q, the new key and the new value taken as the projection left them: the kernel applies the
+// per-head RMSNorm (weights may be null) and the rotation itself and writes key and value to their cache slot
+// (`slot_mapping` null: nothing is written).  qkv rows: [q heads | k heads | v heads], one row per request.
+extern "C" int ullm_decode_attention_fused(const void* qkv, long long q_row_stride, void* k_cache, void* v_cache,
+                                           const int* block_table, int max_pages, const int* req_slots,
+                                           const int* kv_len, void* out, float* scratch, int batch, int num_q,
+                                           int num_kv, int head_dim, int page_size, int window, float scale,
+                                           int num_splits, long long num_pages, const float* q_w, const float* k_w,
+                                           float eps, const float* cos_t, const float* sin_t, int max_positions,
+                                           const int* positions, const int* slot_mapping, int* status, void* stream) {
+  if (cos_t == nullptr || sin_t == nullptr || positions == nullptr || max_positions <= 0) return ULLM_ERR_BAD_SIZE;
+  DecFuse fu;
+  fu.q_w = q_w;
+  fu.k_w = k_w;
+  fu.cos_t = cos_t;
+  fu.sin_t = sin_t;
+  fu.positions = positions;
+  fu.slot_mapping = slot_mapping;
+  fu.k_cache = (__nv_bfloat16*)k_cache;
+  fu.v_cache = (__nv_bfloat16*)v_cache;
+  fu.num_slots = num_pages * page_size;
+  fu.max_positions = max_positions;
+  fu.eps = eps;
+  return decode_attention_impl(qkv, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out,
+                               scratch, batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages,
+                               status, stream, fu);
 }
 
 // ---------------------------------------------------------------------------

@@ -90,6 +90,9 @@ class Kernels:
         # slower than the merge kernel)
         mode = os.environ.get("ULLM_B200_DECODE_CLUSTER", "auto")
         self.decode_cluster_merge = {"1": True, "0": False}.get(mode, "auto")
+        # decode steps: the per-request decode attention kernel applies the q/k norm and the rotation and writes the
+        # new key and value itself (one launch less per layer)
+        self.fuse_decode_rope = os.environ.get("ULLM_B200_FUSE_DECODE_ROPE", "1") == "1"
         # a mixed step's leading one-token entries go to the decode attention kernel from this many on (0: never)
         self.mixed_decode_rows = int(os.environ.get("ULLM_B200_MIXED_DECODE_ROWS", "4"))
         # decode attention on the tcgen05 tensor cores (head size 128), the batch's keys cut evenly over the blocks
@@ -130,6 +133,8 @@ class Kernels:
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
             "ullm_decode_attention_balanced": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_decode_attention_fused": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, F, P, P, I,
+                                            P, P, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
@@ -474,16 +479,36 @@ class Kernels:
             _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
             num_slots, _ptr(self.status), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
 
+    def _decode_choice(self, T, ragged, num_q, num_kv, head_dim, page_size, row_stride) -> str:
+        """Which decode attention kernel takes T one-token rows: "tcgen05", "balanced" or "split"."""
+        balanced = ragged if self.use_balanced_decode == "auto" else self.use_balanced_decode
+        if (self.use_tcgen05_decode and self.lib.ullm_decode_attention_tcgen05_supported(
+                head_dim, num_q, num_kv, T, page_size) and row_stride % head_dim == 0):
+            return "tcgen05"
+        if balanced and self.lib.ullm_decode_attention_balanced_supported(head_dim, num_q, num_kv, T, page_size):
+            return "balanced"
+        return "split"
+
+    def decode_fusion_applies(self, ctx, qkv, num_q, num_kv, head_dim, page_size, rotary_dim, cos) -> bool:
+        """True when the step's attention is the per-request decode kernel and that kernel can prepare q, k and v
+        itself (norm, rotation, cache write): the caller then skips `qk_norm_rope_store` and hands the pieces to
+        `paged_attention(..., fuse=...)`."""
+        T = qkv.shape[0]
+        return bool(self.fuse_decode_rope and ctx is not None and ctx.decode_only and T == ctx.num_requests
+                    and qkv.dtype == torch.bfloat16 and cos is not None and rotary_dim == head_dim
+                    and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)
+                    and self._decode_choice(T, getattr(ctx, "ragged", False), num_q, num_kv, head_dim, page_size,
+                                            qkv.stride(0)) == "split")
+
     def _decode_rows(self, qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
-                     page_size, window, scale, num_pages, ragged, ctx) -> None:
+                     page_size, window, scale, num_pages, ragged, ctx, fuse=None) -> None:
         """Decode attention of T one-token rows (row i belongs to request row i): streams the pages once."""
         T = out.shape[0]
-        cu_q = None
-        balanced = ragged if self.use_balanced_decode == "auto" else self.use_balanced_decode
-        tc = self.use_tcgen05_decode and self.lib.ullm_decode_attention_tcgen05_supported(
-            head_dim, num_q, num_kv, T, page_size) and qkv.stride(0) % head_dim == 0
-        if tc or (balanced and self.lib.ullm_decode_attention_balanced_supported(
-                head_dim, num_q, num_kv, T, page_size)):
+        choice = self._decode_choice(T, ragged, num_q, num_kv, head_dim, page_size, qkv.stride(0))
+        if fuse is not None and choice != "split":
+            raise KernelError("decode attention: q and k were left unprepared for a kernel that does not prepare them")
+        tc = choice == "tcgen05"
+        if choice != "split":
             # both kernels cut the batch's keys evenly (over blocks, over warps) and share the scratch arrays
             # and the merge kernel for the pairs that a cut went through
             key = (head_dim, num_q, num_kv)
@@ -513,20 +538,34 @@ class Kernels:
         most = num_q * (self.decode_split_target // num_kv + max(T, getattr(ctx.workspace, "max_requests", 0)))
         scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32,
                                     reserve=most)
-        self._check(self.lib.ullm_decode_attention(
-            _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
-            _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
-            int(window), float(scale), splits, num_pages, _ptr(self.status), _stream()),
-            f"decode_attention (head_dim {head_dim})")
+        if fuse is not None:
+            for t, n in ((fuse["cos"], "cos table"), (fuse["sin"], "sin table")):
+                _need(t, n, torch.float32)
+            _need(fuse["positions"], "positions", torch.int32)
+            self._check(self.lib.ullm_decode_attention_fused(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+                int(window), float(scale), splits, num_pages, _ptr(fuse["q_w"]), _ptr(fuse["k_w"]), float(fuse["eps"]),
+                _ptr(fuse["cos"]), _ptr(fuse["sin"]), fuse["cos"].shape[0], _ptr(fuse["positions"]),
+                _ptr(fuse["slot_mapping"]), _ptr(self.status), _stream()),
+                f"decode_attention_fused (head_dim {head_dim})")
+        else:
+            self._check(self.lib.ullm_decode_attention(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+                int(window), float(scale), splits, num_pages, _ptr(self.status), _stream()),
+                f"decode_attention (head_dim {head_dim})")
         if splits > 1 and not self.lib.ullm_decode_attention_last_used_cluster():
             self.launches += 1  # the merge of the splits
         self.attention_path = "decode"
         return
 
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
-                        head_dim, page_size, window, scale, ctx=None):
+                        head_dim, page_size, window, scale, ctx=None, fuse=None):
         """Attention of every row of the flat batch over its request's pages.
-        `qkv` holds q in its first num_q * head_dim columns."""
+        `qkv` holds q in its first num_q * head_dim columns.  `fuse` (only after `decode_fusion_applies` said
+        yes): q, k and v are as the projection left them, and the kernel norms, rotates and stores them itself;
+        a dict with q_w, k_w (or None), eps, cos, sin, positions, slot_mapping (or None)."""
         _need(qkv, "qkv")
         _need(out, "out", qkv.dtype)
         _need(k_pages, "k_pages", qkv.dtype)
@@ -543,8 +582,10 @@ class Kernels:
                      and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv))
         if decode_ok and ctx.decode_only and T == ctx.num_requests:
             self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
-                              page_size, window, scale, num_pages, getattr(ctx, "ragged", False), ctx)
+                              page_size, window, scale, num_pages, getattr(ctx, "ragged", False), ctx, fuse)
             return
+        if fuse is not None:
+            raise KernelError("paged_attention: q and k were left unprepared, but this step is no decode step")
         # A step that mixes decoded tokens with prompt portions: the one-token entries at its head (the scheduler
         # puts them first) go to the decode kernel, which streams their pages once; the prompt kernels would give
         # each of them a 128-row tile of its own.  The rest of the step follows with its own slices of the

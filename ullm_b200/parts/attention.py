@@ -99,22 +99,28 @@ class PagedAttention(Mixer):
         linear(x, self.w_qkv, qkv, self.b_qkv)
         g = cache.group
         tables = self.position.tables() if self.position is not None else {}
-        K.qk_norm_rope_store(
-            qkv, self.num_heads, self.num_kv_heads, self.head_dim,
-            self.q_norm.tensors["weight"] if self.q_norm is not None else None,
-            self.k_norm.tensors["weight"] if self.k_norm is not None else None,
-            self.q_norm.eps if self.q_norm is not None else 0.0,
-            tables.get("cos"), tables.get("sin"),
-            self.position.rotary_dim if self.position is not None else 0,
-            ctx.positions, g.slot_mapping if cache.writes else None,
-            cache.k_pages, cache.v_pages,
-        )
+        q_w = self.q_norm.tensors["weight"] if self.q_norm is not None else None
+        k_w = self.k_norm.tensors["weight"] if self.k_norm is not None else None
+        eps = self.q_norm.eps if self.q_norm is not None else 0.0
+        rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        slot_mapping = g.slot_mapping if cache.writes else None
+        fuse = None
+        if K.decode_fusion_applies(ctx, qkv, self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, rotary_dim,
+                                   tables.get("cos")):
+            # a decode step: the attention kernel norms and rotates q and k and writes k and v to their pages itself
+            fuse = dict(q_w=q_w, k_w=k_w, eps=eps, cos=tables["cos"], sin=tables["sin"], positions=ctx.positions,
+                        slot_mapping=slot_mapping)
+        else:
+            K.qk_norm_rope_store(
+                qkv, self.num_heads, self.num_kv_heads, self.head_dim, q_w, k_w, eps, tables.get("cos"),
+                tables.get("sin"), rotary_dim, ctx.positions, slot_mapping, cache.k_pages, cache.v_pages,
+            )
         attn = ctx.workspace.tokens("attn.out", T, self.q_size, x.dtype)
         K.paged_attention(
             qkv, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len,
             ctx.token_req,
             self.num_heads, self.num_kv_heads, self.head_dim, g.page_size,
-            self.window or 0, self.scale, ctx,
+            self.window or 0, self.scale, ctx, **({"fuse": fuse} if fuse is not None else {}),
         )
         out = ctx.workspace.tokens("mixer.out", T, self.hidden_size, x.dtype)
         linear(attn, self.tensors["o_proj.weight"], out)
