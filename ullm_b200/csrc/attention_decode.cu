@@ -17,6 +17,12 @@
 //
 // The grid depends on the batch size and the split count only, never on the
 // lengths, so a captured launch stays valid as the requests grow.
+//
+// Given the rotation tables (DecFuse), the kernel also prepares its inputs from the
+// raw projection: every block norms and rotates the q rows it holds as fragments,
+// and the one warp whose keys end with the newest one norms and rotates the new
+// key, copies the new value, writes both to the cache and, once its last tile has
+// landed, into that tile's rows in shared memory.
 #include <cooperative_groups.h>
 
 #include "decode_core.cuh"
