@@ -196,7 +196,18 @@ class CacheManager:
         want = -(-total // self.page_size)
         return [max(0, want - len(p)) for p in rc.pages]
 
+    def _fits_held_pages(self, rc: RequestCache, n_new: int) -> bool:
+        """The common case of a decode step: the next tokens still fit the pages the request holds."""
+        room = rc.num_tokens + n_new
+        ps = self.page_size
+        for p in rc.pages:
+            if room > len(p) * ps:
+                return False
+        return True
+
     def can_reserve(self, rc: RequestCache, n_new: int) -> bool:
+        if self._fits_held_pages(rc, n_new):
+            return True
         if -(-(rc.num_tokens + n_new) // self.page_size) > self.max_pages_per_request:
             return False
         return all(n <= self.num_available_pages(g) for g, n in enumerate(self.pages_needed(rc, n_new)))
@@ -204,6 +215,8 @@ class CacheManager:
     def reserve(self, rc: RequestCache, n_new: int) -> None:
         """Makes room for tokens [num_tokens, num_tokens + n_new); evicts
         unreferenced prefix pages if the free list is short.  All or nothing."""
+        if self._fits_held_pages(rc, n_new):
+            return
         need = self.pages_needed(rc, n_new)
         if -(-(rc.num_tokens + n_new) // self.page_size) > self.max_pages_per_request:
             raise OutOfPages(f"request {rc.request_id!r} would exceed {self.max_pages_per_request} pages")
