@@ -232,3 +232,41 @@ def test_random_workloads_always_finish(seed):
     assert cache.slots.num_free == s.max_bs
     free = cache.num_free_pages() + (cache.tree.num_evictable() if cache.tree is not None else 0)
     assert free == num_pages
+
+
+def test_decode_graph_sizes_and_padding():
+    """ullm/core/model_runner.py:431-433 records 1, 2, 4, 8 and then steps of 16; here 8 is left out (a batch of 5
+    to 15 is padded to 16, which measured faster) and the largest batch always has a graph of its own size."""
+    from ullm_b200.engine.graph import graph_batch_sizes
+
+    assert graph_batch_sizes(64) == [1, 2, 4, 16, 32, 48, 64]
+    assert graph_batch_sizes(50) == [1, 2, 4, 16, 32, 48, 50]
+    assert graph_batch_sizes(8) == [1, 2, 4, 8]
+    assert graph_batch_sizes(3) == [1, 2, 3]
+    assert graph_batch_sizes(1) == [1]
+    assert graph_batch_sizes(64, smallest=16) == [16, 32, 48, 64]
+    assert graph_batch_sizes(4, smallest=16) == [4]
+    assert graph_batch_sizes(64, skip=()) == [1, 2, 4, 8, 16, 32, 48, 64]
+
+
+def test_workspace_buffers_are_made_at_their_final_size():
+    """A buffer with a row per token is made for the largest step at its first use, one with a row per request
+    for all request slots; `generation` (which invalidates recorded graphs) only moves when a buffer is made or
+    has to grow beyond that."""
+    import torch
+
+    from ullm_b200.engine.batch import Workspace
+
+    ws = Workspace(torch.device("cpu"), max_tokens=64, max_requests=8)
+    a = ws.tokens("x", 5, 16, torch.float32)
+    assert a.shape == (5, 16) and ws.buffers["x"].shape == (64, 16) and ws.generation == 1
+    b = ws.tokens("x", 64, 16, torch.float32)
+    assert b.data_ptr() == a.data_ptr() and ws.generation == 1
+    r = ws.requests("head", 2, 10, torch.float32)
+    assert ws.buffers["head"].shape == (8, 10) and ws.generation == 2 and r.shape == (2, 10)
+    ws.requests("head", 30, 10, torch.float32)  # a caller that wants logits at many places
+    assert ws.buffers["head"].shape == (30, 10) and ws.generation == 3
+    ws.get("scratch", 3, 4, torch.float32, reserve=100)
+    assert ws.buffers["scratch"].shape == (100, 4)
+    ws.tokens("x", 5, 32, torch.float32)  # another width: a new buffer
+    assert ws.buffers["x"].shape == (64, 32) and ws.generation == 5
