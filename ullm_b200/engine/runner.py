@@ -229,7 +229,26 @@ class ModelRunner:
         starts = []
         max_q = max_kv = 1
         sum_kv = 0
-        for b, (e, rc) in enumerate(zip(entries, rcs)):
+        one_token_each = T == B
+        if one_token_each:
+            # a decode step: every segment is filled by one assignment instead of one per entry
+            ps = cache.page_size
+            starts = [rc.num_tokens for rc in rcs]
+            h[o_ids:o_ids + B] = [e.tokens[0] for e in entries]
+            h[o_pos:o_pos + B] = starts
+            h[o_req:o_req + B] = range(B)
+            for g in range(len(cache.groups)):
+                o_sm = seg(f"slot_mapping{g}")
+                h[o_sm:o_sm + B] = [rc.pages[g][s // ps] * ps + s % ps for rc, s in zip(rcs, starts)]
+            rows = [b for b, e in enumerate(entries) for _ in e.want]
+            h[o_rows:o_rows + len(rows)] = rows
+            h[o_kv:o_kv + B] = [s + 1 for s in starts]
+            h[o_rs:o_rs + B] = [rc.slot for rc in rcs]
+            t, r = B, len(rows)
+            cu = list(range(B + 1))
+            max_kv = max(starts) + 1
+            sum_kv = sum(starts) + B
+        for b, (e, rc) in enumerate(() if one_token_each else zip(entries, rcs)):
             n = len(e.tokens)
             start = rc.num_tokens
             starts.append(start)
