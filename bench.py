@@ -564,6 +564,10 @@ def run_reference(args) -> dict:
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "ullm", "core")):
         return {"impl": "reference", "unavailable": "izmttk/ullm is not installed under baseline/_ref"}
+    import torch
+
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device here (the reference's engine process needs one)"}
     sys.path.insert(0, ref)
     cfg = dict(QWEN3_8B)
     full_layers = cfg["num_hidden_layers"]
