@@ -672,6 +672,11 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0
+    import torch
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device: this engine has no CPU path", file=sys.stderr)
+        return 1
     out = run_ours(args)
     print(json.dumps(out))
     return 0
