@@ -15,11 +15,12 @@ from tiny_configs import ALL
 # compared block.  float32: both sides are 32-bit, only the order of additions
 # differs.  bfloat16: weights are identical (rounded before both sides see
 # them); activations are rounded to 8 bits of mantissa after every kernel.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
-TOL_RMS = {"float32": 2e-5, "bfloat16": 1e-2}
+# float16 keeps 11 bits where bfloat16 keeps 8: an eighth of its limits.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2, "float16": 5e-3}
+TOL_RMS = {"float32": 2e-5, "bfloat16": 1e-2, "float16": 1.25e-3}
 # How much the tests that sharpen attention scale q_norm: enough that one wrong
 # key shows, little enough that bfloat16 rounding of q and k stays inside TOL.
-SHARPEN = {"float32": 6.0, "bfloat16": 2.0}
+SHARPEN = {"float32": 6.0, "bfloat16": 2.0, "float16": 3.0}
 
 
 def weights_for(tag: str, dtype: str, sharpen: float = 1.0):
@@ -29,8 +30,8 @@ def weights_for(tag: str, dtype: str, sharpen: float = 1.0):
         for n in w:
             if n.endswith("q_norm.weight"):
                 w[n] = w[n] * sharpen
-    if dtype == "bfloat16":
-        w = {n: t.to(torch.bfloat16) for n, t in w.items()}
+    if dtype in ("bfloat16", "float16"):
+        w = {n: t.to(getattr(torch, dtype)) for n, t in w.items()}
     return cfg, w, page
 
 
@@ -39,7 +40,7 @@ def write_model_dir(path: str, cfg: dict, w: dict) -> str:
 
     os.makedirs(path, exist_ok=True)
     c = dict(cfg)
-    c["torch_dtype"] = "bfloat16" if next(iter(w.values())).dtype == torch.bfloat16 else "float32"
+    c["torch_dtype"] = str(next(iter(w.values())).dtype).replace("torch.", "")
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(c, f)
     save_tensors(os.path.join(path, "model.safetensors"), w)

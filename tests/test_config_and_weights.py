@@ -31,6 +31,8 @@ def test_qwen3_config_defaults_follow_the_reference():
     assert c.head_dim == 64 // 4  # hidden_size // num_attention_heads
     assert c.rope_theta == 1000000.0  # getattr default in ullm/models/qwen3.py:144
     assert c.rms_norm_eps == 1e-6 and c.attention_bias is False
+    assert c.dtype == "float16"  # ullm/core/model_runner.py:38-51: neither "dtype" nor "torch_dtype" -> float16
+    assert Qwen3Config.from_dict(dict(d, dtype="bfloat16")).dtype == "bfloat16"  # "dtype" wins over "torch_dtype"
     # transformers 5 keeps theta under rope_parameters
     c2 = Qwen3Config.from_dict(dict(d, rope_parameters={"rope_theta": 5000.0, "rope_type": "default"}))
     assert c2.rope_theta == 5000.0

@@ -104,7 +104,8 @@ def test_graphs_recorded_at_start_up_are_the_ones_generation_replays(tmp_path):
 
     llm, cfg, w = make_llm(tmp_path, "D", dtype="bfloat16", max_bs=4, num_pages=64, warmup_graphs=True)
     dg = llm.engine.decode_graphs
-    assert set(dg.graphs) == {(s, r) for s in dg.sizes for r in ((False, True) if s > 1 else (False,))}
+    # per size one graph for even batches and (from two requests on) one for the attention mixer's "ragged" key
+    assert set(dg.graphs) == {(s, (r,)) for s in dg.sizes for r in (((), ("ragged",)) if s > 1 else ((),))}
     cache = llm.engine.runner.cache
     assert not cache.requests and cache.num_free_pages(0) == 64
     cache.check_invariants()

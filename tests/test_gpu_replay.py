@@ -15,7 +15,8 @@ from helpers import SHARPEN, assert_close, first_bad_row, plain_logits, random_i
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-CASES = [(t, d) for d in ("float32", "bfloat16") for t in "ABCDE"]
+# float16 (the reference's default when config.json names no dtype) runs the plain kernels: three configurations
+CASES = [(t, d) for d in ("float32", "bfloat16") for t in "ABCDE"] + [(t, "float16") for t in "ABD"]
 LENGTHS = {"A": 100, "B": 200, "C": 180, "D": 300, "E": 230}
 
 
@@ -124,7 +125,7 @@ def test_mixed_batches_with_page_reuse(tmp_path, tag, dtype):
     done_at = [0] * len(lens)
     waiting = list(range(len(lens)))
     live: list[int] = []
-    used_pages = set()
+    page_owners: dict[tuple, set] = {}  # (group, page) -> requests that held it
     steps = 0
     while waiting or live:
         while waiting and len(live) < 4:
@@ -143,7 +144,9 @@ def test_mixed_batches_with_page_reuse(tmp_path, tag, dtype):
             row += n
             done_at[i] += n
             for g in range(len(runner.cache.groups)):
-                used_pages.update((g, p) for p in runner.cache.requests[f"r{i}"].pages[g] if p >= 0)
+                for p in runner.cache.requests[f"r{i}"].pages[g]:
+                    if p >= 0:
+                        page_owners.setdefault((g, p), set()).add(i)
         for i in list(live):
             if not plans[i]:
                 runner.end_request(f"r{i}")
@@ -152,6 +155,7 @@ def test_mixed_batches_with_page_reuse(tmp_path, tag, dtype):
         steps += 1
     runner.check_device_status()
     assert sum(lens) > num_pages * page, "the pool must be too small to hold everything at once"
+    assert any(len(o) > 1 for o in page_owners.values()), "no page was held by two requests in turn: nothing was reused"
     for i in range(len(lens)):
         g = torch.cat(got[i])
         bad = first_bad_row(g, refs[i], dtype)

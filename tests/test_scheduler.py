@@ -259,14 +259,17 @@ def test_workspace_buffers_are_made_at_their_final_size():
 
     ws = Workspace(torch.device("cpu"), max_tokens=64, max_requests=8)
     a = ws.tokens("x", 5, 16, torch.float32)
-    assert a.shape == (5, 16) and ws.buffers["x"].shape == (64, 16) and ws.generation == 1
+    assert a.shape == (5, 16) and ws.buffers[("x", 16, torch.float32)].shape == (64, 16) and ws.generation == 1
     b = ws.tokens("x", 64, 16, torch.float32)
     assert b.data_ptr() == a.data_ptr() and ws.generation == 1
     r = ws.requests("head", 2, 10, torch.float32)
-    assert ws.buffers["head"].shape == (8, 10) and ws.generation == 2 and r.shape == (2, 10)
+    assert ws.buffers[("head", 10, torch.float32)].shape == (8, 10) and ws.generation == 2 and r.shape == (2, 10)
     ws.requests("head", 30, 10, torch.float32)  # a caller that wants logits at many places
-    assert ws.buffers["head"].shape == (30, 10) and ws.generation == 3
+    assert ws.buffers[("head", 10, torch.float32)].shape == (30, 10) and ws.generation == 3
     ws.get("scratch", 3, 4, torch.float32, reserve=100)
-    assert ws.buffers["scratch"].shape == (100, 4)
-    ws.tokens("x", 5, 32, torch.float32)  # another width: a new buffer
-    assert ws.buffers["x"].shape == (64, 32) and ws.generation == 5
+    assert ws.buffers[("scratch", 4, torch.float32)].shape == (100, 4)
+    c = ws.tokens("x", 5, 32, torch.float32)  # another width under the same name: a buffer of its own
+    assert ws.buffers[("x", 32, torch.float32)].shape == (64, 32) and ws.generation == 5
+    # ... and the first one is still there: layers of two widths alternate without a new allocation
+    assert ws.tokens("x", 7, 16, torch.float32).data_ptr() == a.data_ptr()
+    assert ws.tokens("x", 7, 32, torch.float32).data_ptr() == c.data_ptr() and ws.generation == 5

@@ -31,6 +31,9 @@ def _lib():
     lib.ullm_decode_attention_static_capacity.restype = c_longlong
     lib.ullm_decode_attention_scratch_floats.argtypes = [I, I, I, I]
     lib.ullm_decode_attention_scratch_floats.restype = c_longlong
+    lib.ullm_decode_attention_cluster_merge.argtypes = [I]
+    lib.ullm_decode_attention_cluster_merge.restype = None
+    lib.ullm_decode_attention_last_used_cluster.restype = c_int
     return lib
 
 
@@ -51,30 +54,41 @@ def _case(seed, batch, Hq, Hkv, D, page, lens):
 
 
 def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
+    """Three calls in a row on different inputs.  The kernel has two ways to merge a request's splits: inside a
+    thread-block cluster (2 to 8 splits; no scratch at all) or through the scratch arrays and a merge kernel.
+    Only the second reads the library's array, so it is forced: once by switching the cluster form off, once by
+    more splits than a cluster takes; the third call takes the cluster form."""
     lib = _lib()
     Hq, Hkv, D, page = 16, 4, 128, 16
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
-    for seed, batch, splits, lens in ((1, 3, 7, [700, 33, 1500]), (2, 5, 4, [64, 1, 999, 130, 17])):
-        c = _case(seed, batch, Hq, Hkv, D, page, lens)
-        need = lib.ullm_decode_attention_scratch_floats(batch, Hq, D, splits)
-        assert need <= lib.ullm_decode_attention_static_capacity()
-        scratch = torch.empty(need, dtype=torch.float32, device="cuda")
-        ref = torch.empty(batch, Hq * D, dtype=torch.bfloat16, device="cuda")
-        got = torch.full_like(ref, 3.0)
-        p = lambda t: c_void_p(t.data_ptr())
-        common = (p(c["k"]), p(c["v"]), p(c["bt"]), c["bt"].shape[1], p(c["slots"]), p(c["kv"]))
-        sizes = (batch, Hq, Hkv, D, page, 0, D ** -0.5, splits, c["pages"], p(status), stream)
-        rc = lib.ullm_decode_attention(p(c["qkv"]), c["qkv"].stride(0), *common, p(ref), p(scratch), *sizes)
-        assert rc == 0
-        rc = lib.ullm_decode_attention_static(p(c["qkv"]), c["qkv"].stride(0), *common, p(got), *sizes)
-        assert rc == 0
-        torch.cuda.synchronize()
-        assert status.tolist()[0] == 0
-        assert torch.isfinite(got.float()).all()
-        # same kernel, same split count: the two must agree to the tolerance of the kernel tests
-        err = (got.float() - ref.float()).abs().max().item() / max(ref.float().abs().max().item(), 1e-6)
-        assert err <= 2e-2, f"seed {seed}: max err {err:.3e} of scale"
+    cases = ((1, 3, 7, [700, 33, 1500], 0), (2, 5, 12, [64, 1, 999, 130, 17], 1), (3, 2, 4, [300, 41], 1))
+    try:
+        for seed, batch, splits, lens, cluster in cases:
+            lib.ullm_decode_attention_cluster_merge(cluster)
+            c = _case(seed, batch, Hq, Hkv, D, page, lens)
+            need = lib.ullm_decode_attention_scratch_floats(batch, Hq, D, splits)
+            assert need <= lib.ullm_decode_attention_static_capacity()
+            scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+            ref = torch.empty(batch, Hq * D, dtype=torch.bfloat16, device="cuda")
+            got = torch.full_like(ref, 3.0)
+            p = lambda t: c_void_p(t.data_ptr())
+            common = (p(c["k"]), p(c["v"]), p(c["bt"]), c["bt"].shape[1], p(c["slots"]), p(c["kv"]))
+            sizes = (batch, Hq, Hkv, D, page, 0, D ** -0.5, splits, c["pages"], p(status), stream)
+            rc = lib.ullm_decode_attention(p(c["qkv"]), c["qkv"].stride(0), *common, p(ref), p(scratch), *sizes)
+            assert rc == 0
+            rc = lib.ullm_decode_attention_static(p(c["qkv"]), c["qkv"].stride(0), *common, p(got), *sizes)
+            assert rc == 0
+            through_scratch = cluster == 0 or splits > 8
+            assert lib.ullm_decode_attention_last_used_cluster() == (0 if through_scratch else 1)
+            torch.cuda.synchronize()
+            assert status.tolist()[0] == 0
+            assert torch.isfinite(got.float()).all()
+            # same kernel, same split count: the two must agree to the tolerance of the kernel tests
+            err = (got.float() - ref.float()).abs().max().item() / max(ref.float().abs().max().item(), 1e-6)
+            assert err <= 2e-2, f"seed {seed}: max err {err:.3e} of scale"
+    finally:
+        lib.ullm_decode_attention_cluster_merge(1)  # the library's default
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
@@ -92,3 +106,15 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     torch.cuda.synchronize()
     assert rc == 5, "ULLM_ERR_SCRATCH_TOO_LARGE"
     assert (out == 0).all(), "a refused call launches nothing"
+    # one split has no partials and touches nothing of the array: a batch whose formula value is over the limit
+    # is taken all the same
+    big = 256
+    c = _case(4, big, 32, 8, 128, 16, [20] * big)
+    out = torch.zeros(big, 32 * 128, dtype=torch.bfloat16, device="cuda")
+    assert lib.ullm_decode_attention_scratch_floats(big, 32, 128, 1) > lib.ullm_decode_attention_static_capacity()
+    rc = lib.ullm_decode_attention_static(p(c["qkv"]), c["qkv"].stride(0), p(c["k"]), p(c["v"]), p(c["bt"]),
+                                          c["bt"].shape[1], p(c["slots"]), p(c["kv"]), p(out), big, 32, 8, 128, 16, 0,
+                                          128 ** -0.5, 1, c["pages"], p(status),
+                                          c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert rc == 0 and status.tolist()[0] == 0 and torch.isfinite(out.float()).all() and (out != 0).any()

@@ -26,6 +26,7 @@ prefix-cached group go to the tree instead and stay findable until evicted).
 
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -33,6 +34,9 @@ import torch
 
 from ..parts.base import CacheNeed, StateNeed
 from .pages import OutOfPages, PageAllocator, PrefixTree, SlotAllocator
+
+
+logger = logging.getLogger("ullm_b200")
 
 
 @dataclass
@@ -118,6 +122,12 @@ class CacheManager:
         has_state = any(s is not None for _, s, _ in self.needs)
         only_full = len(self.groups) == 1 and self.groups[0].need.window is None
         self.tree = PrefixTree(page_size) if (enable_prefix_cache and only_full and not has_state) else None
+        if enable_prefix_cache and self.tree is None:
+            why = ("a mixer keeps per-request state" if has_state else
+                   "a layer keeps only a window of its keys" if len(self.groups) == 1 else
+                   f"the layers form {len(self.groups)} cache groups with different needs")
+            logger.warning("prefix reuse is off for this model: %s (shared pages would have to hold what every "
+                           "layer needs of a prefix)", why)
         self.requests: dict[str, RequestCache] = {}
         # device side
         self.k_pools: list[torch.Tensor] = []
@@ -126,6 +136,10 @@ class CacheManager:
         self.block_tables_host: list[torch.Tensor] = []
         self.states: dict[int, torch.Tensor] = {}
         self._dirty: list[list[tuple[int, int, int]]] = [[] for _ in self.groups]
+        # pinned snapshots that the copies to the device read from, taken in turn (see flush_block_tables)
+        self._flush_ring: list[torch.Tensor] = []
+        self._flush_events: list = []
+        self._flush_next = 0
         if self.device is not None:
             pin = self.device.type == "cuda"
             for g in self.groups:
@@ -143,7 +157,10 @@ class CacheManager:
                 self.block_tables.append(
                     torch.full((max_requests, max_pages_per_request), -1, dtype=torch.int32, device=self.device))
                 self.block_tables_host.append(
-                    torch.full((max_requests, max_pages_per_request), -1, dtype=torch.int32, pin_memory=pin))
+                    torch.full((max_requests, max_pages_per_request), -1, dtype=torch.int32))
+            n = max(1, len(self.groups)) * max_requests * max_pages_per_request
+            self._flush_ring = [torch.empty(n, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
+            self._flush_events = [torch.cuda.Event() if pin else None for _ in range(4)]
             for i, (_need, state, _c) in enumerate(self.needs):
                 if state is not None:
                     self.states[i] = torch.zeros((max_requests, *state.shape), dtype=state.dtype, device=self.device)
@@ -317,9 +334,20 @@ class CacheManager:
 
     def flush_block_tables(self) -> None:
         """Copies the table rows that changed since the last call to the device
-        (stream-ordered, from pinned memory)."""
-        if self.device is None:
+        (stream-ordered).  The copies read a pinned SNAPSHOT of the changed
+        spans taken now, not the host mirror itself: `commit` and `release`
+        write -1 into the mirror right after a step is launched, possibly
+        before that step's copies have run, and the step must still see the
+        table as it was when it was prepared.  A snapshot buffer is reused only
+        after the copies that read it have run (its event)."""
+        if self.device is None or not any(self._dirty):
             return
+        k = self._flush_next
+        self._flush_next = (k + 1) % len(self._flush_ring)
+        if self._flush_events[k] is not None:
+            self._flush_events[k].synchronize()
+        snap = self._flush_ring[k]
+        off = 0
         for g, dirty in enumerate(self._dirty):
             if not dirty:
                 continue
@@ -328,8 +356,13 @@ class CacheManager:
                 lo, hi = spans.get(slot, (a, b))
                 spans[slot] = (min(lo, a), max(hi, b))
             for slot, (a, b) in spans.items():
-                self.block_tables[g][slot, a:b].copy_(self.block_tables_host[g][slot, a:b], non_blocking=True)
+                n = b - a
+                snap[off:off + n] = self.block_tables_host[g][slot, a:b]
+                self.block_tables[g][slot, a:b].copy_(snap[off:off + n], non_blocking=True)
+                off += n
             dirty.clear()
+        if self._flush_events[k] is not None:
+            self._flush_events[k].record()
 
     # -- views for the model --------------------------------------------------------
     def layer_caches(self, group_steps) -> list[LayerCache]:

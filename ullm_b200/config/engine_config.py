@@ -62,9 +62,10 @@ class EngineConfig:
         if self.max_num_batched_tokens <= 0:
             raise ValueError("max_num_batched_tokens must be positive")
         if self.dtype is not None:
-            self.dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(self.dtype, self.dtype)
-            if self.dtype not in ("bfloat16", "float32"):
-                raise ValueError(f"Unsupported dtype {self.dtype!r} (bfloat16 or float32)")
+            self.dtype = {"bf16": "bfloat16", "fp32": "float32", "fp16": "float16", "half": "float16"}.get(
+                self.dtype, self.dtype)
+            if self.dtype not in ("bfloat16", "float32", "float16"):
+                raise ValueError(f"Unsupported dtype {self.dtype!r} (bfloat16, float16 or float32)")
         if self.load_format not in ("safetensors", "random"):
             raise ValueError("load_format is 'safetensors' or 'random'")
         from .registry import read_config_json
@@ -111,7 +112,7 @@ class EngineConfig:
                             help="Disable asynchronous scheduling (read every step before launching the next)")
         parser.add_argument("--page-size", type=int, default=16, help="Tokens per KV page")
         parser.add_argument("--max-num-batched-tokens", type=int, default=2048, help="Token budget of one step")
-        parser.add_argument("--dtype", type=str, default=None, help="bfloat16 or float32 (default: config.json's)")
+        parser.add_argument("--dtype", type=str, default=None, help="bfloat16, float16 or float32 (default: config.json's; the fast attention kernels are bfloat16)")
         parser.add_argument("--load-format", type=str, default="safetensors", help="safetensors or random")
         parser.add_argument("--seed", type=int, default=0, help="Seed of random weights and of sampling")
         parser.add_argument("--num-pages", type=int, default=None, help="KV pages (default: from free memory)")

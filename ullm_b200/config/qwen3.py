@@ -59,7 +59,7 @@ class Qwen3Config:
     sliding_window: int | None = None
     max_window_layers: int = 0
     hidden_act: str = "silu"
-    dtype: str = "bfloat16"
+    dtype: str = "float16"  # ullm/core/model_runner.py:38-51: "dtype" or "torch_dtype", float16 when neither is there
     eos_token_id: int | None = None
 
     @staticmethod

@@ -601,7 +601,9 @@ extern "C" int ullm_decode_attention_static(const void* q, long long q_row_strid
                                             int num_kv, int head_dim, int page_size, int window, float scale,
                                             int num_splits, long long num_pages, int* status, void* stream) {
   if (batch < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || num_splits <= 0) return ULLM_ERR_BAD_SIZE;
-  if (ullm_decode_attention_scratch_floats(batch, num_q, head_dim, num_splits) > ULLM_STATIC_SCRATCH_FLOATS)
+  // a single split writes no partials: nothing of the array is touched, so nothing has to fit
+  if (num_splits > 1 &&
+      ullm_decode_attention_scratch_floats(batch, num_q, head_dim, num_splits) > ULLM_STATIC_SCRATCH_FLOATS)
     return ULLM_ERR_SCRATCH_TOO_LARGE;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= ULLM_MAX_DEVICES) return ULLM_ERR_LAUNCH;

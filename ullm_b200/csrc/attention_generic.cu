@@ -148,5 +148,9 @@ extern "C" int ullm_paged_attention_generic(int dtype, const void* q, long long 
     return launch_generic<__nv_bfloat16>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
                                          kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale,
                                          num_pages, status, st);
+  if (dtype == ULLM_DTYPE_F16)
+    return launch_generic<__half>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                  kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                  status, st);
   return ULLM_ERR_BAD_DTYPE;
 }

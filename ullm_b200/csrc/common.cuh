@@ -3,11 +3,13 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #define ULLM_DTYPE_F32 0
 #define ULLM_DTYPE_BF16 1
+#define ULLM_DTYPE_F16 2  // the plain templated kernels only: the tensor-core attention kernels are bfloat16
 
 // Error codes returned by the extern "C" launchers.
 #define ULLM_OK 0
@@ -34,6 +36,7 @@ __device__ __forceinline__ void ullm_report(int* status, int code, int index, in
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 
 template <typename T>
 __device__ __forceinline__ T from_f32(float v);
@@ -41,6 +44,8 @@ template <>
 __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

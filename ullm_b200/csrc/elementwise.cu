@@ -5,6 +5,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 #include <unordered_set>
 
 int g_ullm_pdl = 0;
@@ -82,6 +83,9 @@ extern "C" int ullm_embedding(int dtype, const int* ids, const void* table, void
   if (dtype == ULLM_DTYPE_BF16)
     return gather_rows_launch<__nv_bfloat16>(ids, table, out, tokens, hidden, hidden, hidden, vocab,
                                              ULLM_STATUS_TOKEN_ID, status, st, last_tokens, token_req, req_slots);
+  if (dtype == ULLM_DTYPE_F16)
+    return gather_rows_launch<__half>(ids, table, out, tokens, hidden, hidden, hidden, vocab, ULLM_STATUS_TOKEN_ID,
+                                      status, st, last_tokens, token_req, req_slots);
   return ULLM_ERR_BAD_DTYPE;
 }
 
@@ -95,6 +99,9 @@ extern "C" int ullm_gather_rows(int dtype, const int* rows_index, const void* sr
   if (dtype == ULLM_DTYPE_BF16)
     return gather_rows_launch<__nv_bfloat16>(rows_index, src, out, rows, cols, cols, cols, src_rows, ULLM_STATUS_ROW,
                                              status, st);
+  if (dtype == ULLM_DTYPE_F16)
+    return gather_rows_launch<__half>(rows_index, src, out, rows, cols, cols, cols, src_rows, ULLM_STATUS_ROW, status,
+                                      st);
   return ULLM_ERR_BAD_DTYPE;
 }
 
@@ -232,7 +239,7 @@ __global__ void add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* x, __nv_bfloat16*
   }
 }
 
-static int g_rmsnorm_smem_set[3] = {0, 0, 0};
+static int g_rmsnorm_smem_set[4] = {0, 0, 0, 0};
 
 template <typename T>
 static int add_rmsnorm_launch(int which, const void* x, void* residual, const float* w, void* out, int rows, int cols,
@@ -246,7 +253,7 @@ static int add_rmsnorm_launch(int which, const void* x, void* residual, const fl
       return ULLM_ERR_LAUNCH;
     g_rmsnorm_smem_set[which] = 1;
   }
-  if (sizeof(T) == 2 && cols % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+  if (std::is_same<T, __nv_bfloat16>::value && cols % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
       (residual == nullptr || (uintptr_t)residual % 16 == 0)) {
     if (smem > 48 * 1024 && !g_rmsnorm_smem_set[2]) {
       if (cudaFuncSetAttribute(add_rmsnorm_bf16x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
@@ -278,6 +285,7 @@ extern "C" int ullm_add_rmsnorm(int dtype, const void* x, void* residual, const 
   if (dtype == ULLM_DTYPE_F32) return add_rmsnorm_launch<float>(0, x, residual, weight, out, rows, cols, eps, st);
   if (dtype == ULLM_DTYPE_BF16)
     return add_rmsnorm_launch<__nv_bfloat16>(1, x, residual, weight, out, rows, cols, eps, st);
+  if (dtype == ULLM_DTYPE_F16) return add_rmsnorm_launch<__half>(3, x, residual, weight, out, rows, cols, eps, st);
   return ULLM_ERR_BAD_DTYPE;
 }
 
@@ -363,6 +371,11 @@ extern "C" int ullm_act_mul(int dtype, int act, const void* gate_up, void* out, 
       return ullm_launch_kernel(act_mul_kernel<__nv_bfloat16, 0>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
     else
       return ullm_launch_kernel(act_mul_kernel<__nv_bfloat16, 1>, dim3((int)blocks), dim3(threads), 0, st, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter);
+  } else if (dtype == ULLM_DTYPE_F16) {
+    if (act == 0)
+      return ullm_launch_kernel(act_mul_kernel<__half, 0>, dim3((int)blocks), dim3(threads), 0, st, (const __half*)gate_up, (__half*)out, (long long)rows, inter);
+    else
+      return ullm_launch_kernel(act_mul_kernel<__half, 1>, dim3((int)blocks), dim3(threads), 0, st, (const __half*)gate_up, (__half*)out, (long long)rows, inter);
   } else {
     return ULLM_ERR_BAD_DTYPE;
   }

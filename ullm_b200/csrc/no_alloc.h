@@ -15,13 +15,16 @@
 //   * The scratch is one file-scope device array of
 //     ULLM_STATIC_SCRATCH_FLOATS floats (4 MiB).  Every GPU on which the
 //     library is loaded holds it from load until the process exits.
-//   * A call needs batch * num_q * num_splits * (head_dim + 2) floats
-//     (ullm_decode_attention_scratch_floats).  A call that needs more is
-//     refused with ULLM_ERR_SCRATCH_TOO_LARGE (5) and launches nothing; use
-//     fewer splits, a smaller batch, or the regular entry point.
+//   * A call with two or more splits needs batch * num_q * num_splits *
+//     (head_dim + 2) floats (ullm_decode_attention_scratch_floats).  A call
+//     that needs more is refused with ULLM_ERR_SCRATCH_TOO_LARGE (5) and
+//     launches nothing; use fewer splits, a smaller batch, or the regular
+//     entry point.  With num_splits == 1 no partials exist, the array is not
+//     touched and any batch is taken.
 //   * The first call on a device looks up the array's device address (once per
 //     device, with that device current).  Make that first call before any
-//     stream capture begins on that device.
+//     stream capture begins on that device.  The address is the CURRENT
+//     device's: `stream` must belong to the device that is current at the call.
 //   * All calls share the one array and it keeps the previous call's contents.
 //     Nothing in it has to start at zero: every element a call reads was
 //     written by the same call.  Two calls that overlap on the GPU (different

@@ -16,7 +16,7 @@ import torch
 
 from .build import build
 
-_DT = {torch.float32: 0, torch.bfloat16: 1}
+_DT = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 _ERRORS = {
     1: "unsupported dtype",
     2: "bad size argument",
@@ -489,7 +489,8 @@ class Kernels:
             return "balanced"
         return "split"
 
-    def decode_fusion_applies(self, ctx, qkv, num_q, num_kv, head_dim, page_size, rotary_dim, cos) -> bool:
+    def decode_fusion_applies(self, ctx, qkv, num_q, num_kv, head_dim, page_size, rotary_dim, cos,
+                              ragged: bool = False) -> bool:
         """True when the step's attention is the per-request decode kernel and that kernel can prepare q, k and v
         itself (norm, rotation, cache write): the caller then skips `qk_norm_rope_store` and hands the pieces to
         `paged_attention(..., fuse=...)`."""
@@ -497,7 +498,7 @@ class Kernels:
         return bool(self.fuse_decode_rope and ctx is not None and ctx.decode_only and T == ctx.num_requests
                     and qkv.dtype == torch.bfloat16 and cos is not None and rotary_dim == head_dim
                     and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)
-                    and self._decode_choice(T, getattr(ctx, "ragged", False), num_q, num_kv, head_dim, page_size,
+                    and self._decode_choice(T, ragged, num_q, num_kv, head_dim, page_size,
                                             qkv.stride(0)) == "split")
 
     def _decode_rows(self, qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
@@ -561,11 +562,12 @@ class Kernels:
         return
 
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
-                        head_dim, page_size, window, scale, ctx=None, fuse=None):
+                        head_dim, page_size, window, scale, ctx=None, fuse=None, ragged: bool = False):
         """Attention of every row of the flat batch over its request's pages.
         `qkv` holds q in its first num_q * head_dim columns.  `fuse` (only after `decode_fusion_applies` said
         yes): q, k and v are as the projection left them, and the kernel norms, rotates and stores them itself;
-        a dict with q_w, k_w (or None), eps, cos, sin, positions, slot_mapping (or None)."""
+        a dict with q_w, k_w (or None), eps, cos, sin, positions, slot_mapping (or None).  `ragged` (decode
+        steps): the caller found the requests' lengths very unequal, which picks the batch-balanced kernel."""
         _need(qkv, "qkv")
         _need(out, "out", qkv.dtype)
         _need(k_pages, "k_pages", qkv.dtype)
@@ -582,7 +584,7 @@ class Kernels:
                      and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv))
         if decode_ok and ctx.decode_only and T == ctx.num_requests:
             self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
-                              page_size, window, scale, num_pages, getattr(ctx, "ragged", False), ctx, fuse)
+                              page_size, window, scale, num_pages, ragged, ctx, fuse)
             return
         if fuse is not None:
             raise KernelError("paged_attention: q and k were left unprepared, but this step is no decode step")

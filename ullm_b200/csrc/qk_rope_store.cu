@@ -229,6 +229,10 @@ extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num
     return ullm_launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (__nv_bfloat16*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
         positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status);
+  else if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(qk_norm_rope_store_kernel<__half>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
+        (__half*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
+        positions, slot_mapping, (__half*)k_cache, (__half*)v_cache, num_slots, status);
   else
     return ULLM_ERR_BAD_DTYPE;
   return ullm_launch_status();

@@ -38,26 +38,30 @@ class GroupStep:
 
 class Workspace:
     """Named activation buffers that persist across steps (so a captured CUDA
-    graph finds them at the same address).  `get` returns the first `rows` rows;
-    a buffer grows when more rows are asked for than it has, which bumps
-    `generation` (anything that recorded addresses must be re-recorded).  To
-    keep that rare, a buffer is made at once for what its caller says it may
-    ever need (`reserve` rows): per-token buffers for the largest step
-    (`max_tokens`), per-request buffers for all request slots (`max_requests`)."""
+    graph finds them at the same address).  A buffer is known by (name, columns,
+    dtype): two layers of different width that use the same name get a buffer
+    each, so a model whose layers differ neither reallocates per layer nor
+    invalidates recorded graphs.  `get` returns the first `rows` rows; a buffer
+    grows when more rows are asked for than it has, which bumps `generation`
+    (anything that recorded addresses must be re-recorded).  To keep that rare,
+    a buffer is made at once for what its caller says it may ever need
+    (`reserve` rows): per-token buffers for the largest step (`max_tokens`),
+    per-request buffers for all request slots (`max_requests`)."""
 
     def __init__(self, device, max_tokens: int = 0, max_requests: int = 0):
         self.device = device
         self.max_tokens = max_tokens
         self.max_requests = max_requests
-        self.buffers: dict[str, torch.Tensor] = {}
+        self.buffers: dict[tuple, torch.Tensor] = {}
         self.generation = 0
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype, reserve: int = 0) -> torch.Tensor:
-        buf = self.buffers.get(name)
-        if buf is None or buf.shape[0] < rows or buf.shape[1] != cols or buf.dtype != dtype:
+        key = (name, cols, dtype)
+        buf = self.buffers.get(key)
+        if buf is None or buf.shape[0] < rows:
             cap = max(rows, reserve, 0 if buf is None else buf.shape[0], 1)
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
-            self.buffers[name] = buf
+            self.buffers[key] = buf
             self.generation += 1
         return buf[:rows]
 
@@ -95,8 +99,8 @@ class StepContext:
     max_kv_len: int = 1
     decode_only: bool = False
     last_tokens: torch.Tensor | None = None  # int32 [request slots]: what each request sampled last (for id -1)
-    # decode steps: lengths differ so much that the longest request, times the batch, is well above the sum
-    ragged: bool = False
+    sum_kv_len: int = 0  # tokens all requests of the step hold after it, padding rows not counted
+    num_live_requests: int = 0  # requests of the step without padding rows
 
 
 class StepStaging:

@@ -82,7 +82,7 @@ def main(argv=None) -> int:
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--std", type=float, default=0.02)
     r.add_argument("--norm-std", type=float, default=0.0)
-    r.add_argument("--dtype", default=None, help="bfloat16 or float32 (default: the config's)")
+    r.add_argument("--dtype", default=None, help="bfloat16, float16 or float32 (default: the config's)")
     r.set_defaults(fn=_random_model)
     args = ap.parse_args(argv)
     return args.fn(args)

@@ -39,8 +39,8 @@ class DecodeGraphs:
         import os
 
         self.sizes = graph_batch_sizes(max_bs, int(os.environ.get("ULLM_B200_MIN_GRAPH_BATCH", "1")))
-        # (size, ragged) -> (graph, signature, kernels recorded): batches of very unequal lengths replay a
-        # graph that was recorded with the batch-balanced attention kernel
+        # (size, the mixers' graph keys) -> (graph, signature, kernels recorded): a step is replayed from a graph
+        # that was recorded with the kernels its mixers would choose for it (`Mixer.graph_key`)
         self.graphs: dict[tuple, tuple] = {}
         self.pool = None
         self.replays = 0
@@ -72,7 +72,7 @@ class DecodeGraphs:
         Bp = self.padded(B)
         ctx = r.prepare(entries, pad_to=Bp, staging=r.decode_staging)
         self.sampler.stage(params, seeds, counters, [r.cache.requests[e.request_id].slot for e in entries])
-        key = (Bp, bool(ctx.ragged))
+        key = (Bp, r.model.graph_key(ctx))
         held = self.graphs.get(key)
         from ..csrc import kernels
 

@@ -13,6 +13,8 @@ scheduler (engine.scheduler) or a replayed trace (bin/trace_run) does.
 
 from __future__ import annotations
 
+import logging
+
 import numpy as np
 import torch
 
@@ -23,24 +25,21 @@ from ..parts.model import DecoderModel
 from ..weights import files_have, fill_random_, load_weights
 from .batch import GroupStep, StepContext, StepEntry, StepStaging, Workspace
 
-_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.bfloat16}
+logger = logging.getLogger("ullm_b200")
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
 
 
 def engine_dtype(requested: str | None, checkpoint: str) -> torch.dtype:
-    """The compute dtype: the caller's choice, else the checkpoint's.  A
-    float16 checkpoint is served in bfloat16 (weights are kept in bfloat16)."""
+    """The compute dtype: the caller's choice, else the checkpoint's (ullm/core/model_runner.py:38-51 takes
+    config.json's).  float16 is served in float16: weights, cache and activations are float16, the arithmetic
+    inside the kernels is 32-bit as in the other two; its attention runs on the plain kernel (the tensor-core
+    attention kernels take bfloat16 only), so it is the slow one of the two 16-bit types."""
     name = requested or checkpoint
-    name = {"bf16": "bfloat16", "fp32": "float32"}.get(name, name)
+    name = {"bf16": "bfloat16", "fp32": "float32", "fp16": "float16", "half": "float16"}.get(name, name)
     if name not in _TORCH_DTYPES:
         raise ValueError(f"Unsupported dtype {name!r}")
     return _TORCH_DTYPES[name]
-
-
-def is_ragged(batch: int, max_kv: int, sum_kv: int) -> bool:
-    """A decode batch whose longest request, times the batch, is more than 1.5 times all the keys there are:
-    splitting every request alike would then leave most blocks waiting for the long one (measured: the
-    batch-balanced attention kernel wins from about this ratio on, and loses about 5 % on even batches)."""
-    return batch > 1 and 2 * batch * max_kv > 3 * sum_kv
 
 
 class ModelRunner:
@@ -70,6 +69,11 @@ class ModelRunner:
         self.device = torch.device(device)
         self.typed_config, self.spec = load_model_spec(config if config is not None else model_dir)
         self.dtype = engine_dtype(dtype, self.spec.dtype)
+        self.checkpoint_dtype = self.spec.dtype
+        if self.dtype == torch.float16:
+            logger.warning("serving in float16 (%s): correct, but attention runs on the plain kernel; the tensor-core "
+                           "attention kernels take bfloat16 (dtype='bfloat16' selects them)",
+                           "asked for" if dtype else "config.json's dtype, or its default when the key is absent")
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
             # a true 32-bit path: no reduced-precision matrix mode, ever
@@ -133,15 +137,12 @@ class ModelRunner:
         return int(pages)
 
     def _activation_bytes(self) -> int:
+        """Room for one step's work buffers: every part says how many elements per token it keeps in the
+        workspace (`Part.activation_elems`); layers reuse the buffers, so the widest layer counts."""
         s = self.spec
-        widest = 0
-        for ls in s.layers:
-            a = ls.feed_forward.args.get("intermediate_size", 0) * 3
-            m = ls.mixer.args
-            b = (m.get("num_heads", 0) * 2 + m.get("num_kv_heads", 0) * 2) * m.get("head_dim", 0)
-            widest = max(widest, a, b)
+        widest = max((b.activation_elems() for b in self.model.blocks), default=0)
         itemsize = torch.empty((), dtype=self.dtype).element_size()
-        acts = self.max_step_tokens * (widest + 4 * s.hidden_size) * itemsize
+        acts = self.max_step_tokens * (widest + 2 * s.hidden_size) * itemsize
         logits = self.max_requests * s.vocab_size * 4 * 2
         return int(acts + logits + (512 << 20))
 
@@ -306,7 +307,7 @@ class ModelRunner:
             cu_q_host=cu, req_slots_host=[rc.slot for rc in rcs] + [0] * (B - len(rcs)),
             start_positions_host=starts + [0] * (B - len(rcs)),
             max_q_len=max_q, max_kv_len=max_kv, decode_only=(max_q == 1), last_tokens=self.last_tokens,
-            ragged=is_ragged(len(entries), max_kv, sum_kv),
+            sum_kv_len=sum_kv, num_live_requests=len(entries),
         )
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:

@@ -18,6 +18,13 @@ from .linear import linear
 from .registry import build_norm, build_position_encoding, register_mixer
 
 
+def is_ragged(batch: int, max_kv: int, sum_kv: int) -> bool:
+    """A decode batch whose longest request, times the batch, is more than 1.5 times all the keys there are:
+    splitting every request alike would then leave most blocks waiting for the long one (measured: the
+    batch-balanced attention kernel wins from about this ratio on, and loses about 5 % on even batches)."""
+    return batch > 1 and 2 * batch * max_kv > 3 * sum_kv
+
+
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     def __init__(
@@ -91,10 +98,26 @@ class PagedAttention(Mixer):
     def cache_need(self):
         return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
 
+    def activation_elems(self):
+        # qkv, the attention's output, the projected output
+        return self.q_size + 2 * self.kv_size + self.q_size + self.hidden_size
+
+    # -- which kernels a decode step takes ---------------------------------
+    def graph_key(self, ctx):
+        return ("ragged",) if self._ragged(ctx) else ()
+
+    def graph_key_group(self):
+        return (type(self), self.num_heads, self.num_kv_heads, self.head_dim)
+
+    @staticmethod
+    def _ragged(ctx) -> bool:
+        return bool(ctx.decode_only and is_ragged(ctx.num_live_requests, ctx.max_kv_len, ctx.sum_kv_len))
+
     # -- one step ---------------------------------------------------------
     def forward(self, x, ctx, cache):
         K = kernels()
         T = x.shape[0]
+        ragged = self._ragged(ctx)
         qkv = ctx.workspace.tokens("attn.qkv", T, self.q_size + 2 * self.kv_size, x.dtype)
         linear(x, self.w_qkv, qkv, self.b_qkv)
         g = cache.group
@@ -106,7 +129,7 @@ class PagedAttention(Mixer):
         slot_mapping = g.slot_mapping if cache.writes else None
         fuse = None
         if K.decode_fusion_applies(ctx, qkv, self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, rotary_dim,
-                                   tables.get("cos")):
+                                   tables.get("cos"), ragged):
             # a decode step: the attention kernel norms and rotates q and k and writes k and v to their pages itself
             fuse = dict(q_w=q_w, k_w=k_w, eps=eps, cos=tables["cos"], sin=tables["sin"], positions=ctx.positions,
                         slot_mapping=slot_mapping)
@@ -120,7 +143,7 @@ class PagedAttention(Mixer):
             qkv, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len,
             ctx.token_req,
             self.num_heads, self.num_kv_heads, self.head_dim, g.page_size,
-            self.window or 0, self.scale, ctx, **({"fuse": fuse} if fuse is not None else {}),
+            self.window or 0, self.scale, ctx, ragged=ragged, **({"fuse": fuse} if fuse is not None else {}),
         )
         out = ctx.workspace.tokens("mixer.out", T, self.hidden_size, x.dtype)
         linear(attn, self.tensors["o_proj.weight"], out)

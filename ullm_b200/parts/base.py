@@ -13,6 +13,7 @@ Interfaces (what a new part must have):
 * PositionEncoding: `tables() -> dict of device tensors` handed to the mixer's
   kernel, plus `rotary_dim`.
 * Mixer: `cache_need() -> CacheNeed | None`, `state_need() -> StateNeed | None`,
+  `graph_key(ctx)` (what of a decode step changes its launches, default nothing),
   `forward(x[T, hidden], ctx, cache) -> [T, hidden]`; `cache` is the
   LayerCache of this execution (pages of its group + the group's step
   metadata, and its state rows if it asked for any).
@@ -75,6 +76,12 @@ class Part:
         """Nested parts by tensor-name prefix."""
         return {}
 
+    def activation_elems(self) -> int:
+        """Elements per token that this part (with its sub-parts) keeps in the step's workspace while it
+        runs; the engine sets that much memory aside before it sizes the cache pool.  A part that takes
+        buffers from `ctx.workspace` says here how wide they are together."""
+        return sum(p.activation_elems() for p in self.subparts().values())
+
     # -- walking a tree of parts ------------------------------------------
     def all_decls(self, prefix: str = "") -> dict[str, ParamDecl]:
         out = {prefix + n: d for n, d in self.param_decls().items()}
@@ -112,6 +119,16 @@ class Mixer(Part):
 
     def state_need(self) -> StateNeed | None:
         return None
+
+    def graph_key(self, ctx):
+        """What about a decode step, beyond its padded batch size, changes the kernels this mixer launches or
+        their grids (a mixer that picks a kernel by how unequal the requests' lengths are, say).  A recorded
+        CUDA graph is replayed only for steps with the same key.  Hashable; () when nothing does."""
+        return ()
+
+    def graph_key_group(self):
+        """Mixers with equal groups give equal graph keys for the same step (one of them is asked)."""
+        return type(self)
 
     def forward(self, x, ctx, cache):
         raise NotImplementedError

@@ -35,6 +35,11 @@ class PreNormResidualBlock(Block):
             self.names["feed_forward"]: self.feed_forward,
         }
 
+    def activation_elems(self):
+        # the normed rows, and the wider of the two sub-layers (they run one after the other)
+        size = getattr(self.mixer_norm, "size", 0)
+        return size + max(self.mixer.activation_elems(), self.feed_forward.activation_elems())
+
     def forward(self, x, residual, ctx, cache):
         """x: the previous sub-layer's output (the embedding for the first
         block, with residual None).  Returns (feed-forward output, residual);

@@ -28,6 +28,12 @@ class DecoderModel(Part):
         tied = spec.tie_embeddings and not untie_head
         self.head = OutputHead(spec.vocab_size, spec.hidden_size, self.embedding if tied else None)
         self.schedule = list(spec.schedule)
+        # one mixer of each group answers `graph_key` for all of its kind
+        seen: dict = {}
+        for e in self.schedule:
+            m = self.blocks[e.layer].mixer
+            seen.setdefault(m.graph_key_group(), m)
+        self._graph_key_mixers = list(seen.values())
         self.dtype: torch.dtype | None = None
         self.device = None
 
@@ -47,6 +53,10 @@ class DecoderModel(Part):
             m = self.blocks[e.layer].mixer
             out.append((m.cache_need(), m.state_need(), e.cache_of))
         return out
+
+    def graph_key(self, ctx) -> tuple:
+        """What of a decode step, beyond its padded size, decides the kernels its mixers launch."""
+        return tuple(m.graph_key(ctx) for m in self._graph_key_mixers)
 
     # -- allocation ---------------------------------------------------------
     def allocate(self, device, dtype: torch.dtype) -> None:

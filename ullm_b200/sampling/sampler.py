@@ -37,8 +37,14 @@ class Sampler:
         self.vocab_size = vocab_size
         self.last_tokens = last_tokens
         pin = self.device.type == "cuda"
-        # one pinned block: temperature, top_p, min_p, uniform (float32), top_k and request slot (int32 bits)
-        self.host = torch.zeros(6, max_rows, dtype=torch.float32, pin_memory=pin)
+        # pinned blocks taken in turn: temperature, top_p, min_p, uniform (float32), top_k and request slot
+        # (int32 bits).  A block is rewritten only after the copy that read it last has run (its event): with
+        # steps launched ahead, the copy of step N may still be queued behind step N's forward when the host
+        # stages step N + 1.
+        self._hosts = [torch.zeros(6, max_rows, dtype=torch.float32, pin_memory=pin) for _ in range(4)]
+        self._host_events = [torch.cuda.Event() if pin else None for _ in range(4)]
+        self._host_next = 0
+        self.host = self._hosts[0]
         self.dev = torch.zeros(6, max_rows, dtype=torch.float32, device=self.device)
         self.out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
         self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
@@ -52,6 +58,11 @@ class Sampler:
         R = len(params)
         if R > self.max_rows:
             raise ValueError(f"{R} rows to sample, room for {self.max_rows}")
+        k = self._host_next
+        self._host_next = (k + 1) % len(self._hosts)
+        if self._host_events[k] is not None:
+            self._host_events[k].synchronize()
+        self.host = self._hosts[k]
         h = self.host.numpy()
         hk = self.host[4].view(torch.int32).numpy()
         hs = self.host[5].view(torch.int32).numpy()
@@ -66,6 +77,8 @@ class Sampler:
         if slots is not None:
             hs[:R] = slots
         self.dev.copy_(self.host, non_blocking=True)
+        if self._host_events[k] is not None:
+            self._host_events[k].record()
 
     def run(self, logits: torch.Tensor, rows: int) -> torch.Tensor:
         """Samples rows 0..rows-1 of `logits` with the staged parameters; the
