@@ -519,13 +519,10 @@ def run_sampling_probe(args) -> int:
     return 0
 
 
-def _write_reference_model(path: str, cfg: dict) -> None:
-    """A model folder the reference can open: random weights (this repo's seeded writer), and a synthetic
-    byte-level tokenizer (its LLM loads a tokenizer unconditionally; ids go in and out as integers here, the
-    tokenizer only has to exist and to know every id)."""
-    from ullm_b200.weights import write_random_model
-
-    write_random_model(path, cfg, seed=0, std=0.02, norm_std=0.0, dtype="bfloat16")
+def write_synthetic_tokenizer(path: str, vocab_size: int) -> None:
+    """Tokenizer files that know every id of a `vocab_size`-token vocabulary (byte-level alphabet first, then
+    "tok0", "tok1", ...), and config.json's model_type: the reference's LLM loads a tokenizer unconditionally.
+    Ids go in and out as integers; the tokenizer only has to exist."""
     bs = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
     cs, n = bs[:], 0
     for b in range(256):
@@ -535,7 +532,7 @@ def _write_reference_model(path: str, cfg: dict) -> None:
             n += 1
     vocab = {chr(c): i for i, c in enumerate(cs)}
     i = 0
-    while len(vocab) < cfg["vocab_size"]:
+    while len(vocab) < vocab_size:
         t = f"tok{i}"
         i += 1
         if t not in vocab:
@@ -552,6 +549,15 @@ def _write_reference_model(path: str, cfg: dict) -> None:
     c["model_type"] = "qwen3"
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(c, f)
+
+
+def _write_reference_model(path: str, cfg: dict) -> None:
+    """A model folder the reference can open: random weights (this repo's seeded writer) and the synthetic
+    tokenizer."""
+    from ullm_b200.weights import write_random_model
+
+    write_random_model(path, cfg, seed=0, std=0.02, norm_std=0.0, dtype="bfloat16")
+    write_synthetic_tokenizer(path, cfg["vocab_size"])
 
 
 def run_reference(args) -> dict:

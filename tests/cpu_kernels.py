@@ -14,6 +14,7 @@ import torch
 class CpuKernels:
     def __init__(self):
         self.status = torch.zeros(4, dtype=torch.int32)
+        self.timer = None
         self.calls = {}
 
     def _count(self, name):
@@ -105,7 +106,7 @@ class CpuKernels:
             vf[sm[ok]] = v[ok].to(vf.dtype)
 
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req,
-                        num_q, num_kv, D, page_size, window, scale, ctx=None):
+                        num_q, num_kv, D, page_size, window, scale, ctx=None, ragged=False):
         self._count("paged_attention")
         T = out.shape[0]
         kf = k_pages.view(-1, num_kv, D).float()

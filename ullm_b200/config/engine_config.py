@@ -106,7 +106,7 @@ class EngineConfig:
         parser.add_argument("--context-len", type=int, default=2048, help="Max context length of the model")
         parser.add_argument("--enforce-eager", action="store_true", help="Enforce eager execution, disable CUDA graph")
         parser.add_argument("--log-level", type=str, default="info", help="Log level for the engine")
-        parser.add_argument("--profile", action="store_true", help="Print per-step timing")
+        parser.add_argument("--profile", action="store_true", help="Time every step (and the kernel groups of eager steps); printed and written to --profile-dir at the end")
         parser.add_argument("--profile-dir", type=str, default="./profiles", help="Directory to save profiling results")
         parser.add_argument("--disable-async-scheduling", action="store_true",
                             help="Disable asynchronous scheduling (read every step before launching the next)")

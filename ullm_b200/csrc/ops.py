@@ -29,6 +29,7 @@ STATUS_MESSAGES = {
     3: "cache slot out of range (token {index}: slot {value})",
     4: "row index out of range (row {index}: {value})",
     5: "page id out of range in a block table (token {index}: page {value})",
+    6: "a kernel gave up waiting on a barrier (place {index}, at {value}) and returned early",
 }
 
 MAX_HEAD_DIM = 512
@@ -64,6 +65,31 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
         raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
     if contiguous and not t.is_contiguous():
         raise KernelError(f"{name} must be contiguous")
+
+
+def _timed(group: str, nbytes=None):
+    """While a timer is installed (`Kernels.timer`, see engine/profiler.py), the wrapped call is bracketed by
+    two CUDA events and booked under `group`; `nbytes(*args)` says what it had to read, if that is known."""
+
+    def outer(fn):
+        def inner(self, *a, **k):
+            t = self.timer
+            if t is None:
+                return fn(self, *a, **k)
+            start = t.begin()
+            try:
+                return fn(self, *a, **k)
+            finally:
+                t.end(group, start, nbytes(*a) if (nbytes is not None and start is not None) else 0)
+
+        inner.__name__, inner.__doc__ = fn.__name__, fn.__doc__
+        return inner
+
+    return outer
+
+
+def _weight_bytes(x, weight, *rest):
+    return weight.numel() * weight.element_size()
 
 
 class Kernels:
@@ -116,6 +142,7 @@ class Kernels:
         self._lt_ok = None
         self._lt_ws = None
         self._lt_tuned = set()
+        self.timer = None  # a KernelGroupTimer while a profile is being taken
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
@@ -149,6 +176,8 @@ class Kernels:
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        L.ullm_wait_selftest.argtypes = [I, P, P, P]
+        L.ullm_wait_selftest.restype = c_int
         L.ullm_decode_attention_supported.argtypes = [I, I, I]
         L.ullm_decode_attention_supported.restype = c_int
         L.ullm_decode_attention_balanced_supported.argtypes = [I, I, I, I, I]
@@ -212,6 +241,15 @@ class Kernels:
                 flags.zero_()  # likewise the merge flags of the balanced decode attention
             msg = STATUS_MESSAGES.get(s[0], "status {code}").format(index=s[1], value=s[2], code=s[0])
             raise KernelError(f"a kernel refused an index: {msg}")
+
+    def wait_selftest(self, limit: int = 4096) -> int:
+        """Runs the kernels' give-up path on purpose (see csrc/wait_selftest.cu): a one-block kernel waits
+        `limit` polls on a barrier nobody arrives at, records the timeout in the status word, frees its tensor
+        memory and returns.  Returns 1 when the wait ran out; the status word is left set for the caller
+        (`raise_on_status` reads and clears it)."""
+        out = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self._check(self.lib.ullm_wait_selftest(int(limit), _ptr(self.status), _ptr(out), _stream()), "wait_selftest")
+        return int(out.item())
 
     # -- library matrix products ---------------------------------------------
     def small_m_linear(self, x, weight, out, bias=None, act: int | None = None) -> bool:
@@ -342,6 +380,7 @@ class Kernels:
             return self.large_linear(x, weight, out, bias, act)
         return False
 
+    @_timed("linear", _weight_bytes)
     def linear(self, x, weight, out, bias=None):
         """out = x @ weight.T (+ bias).  Few bfloat16 rows: a hand-written kernel when one is switched on.
         Otherwise the vendor library's matrix product, float32 without any reduced-precision mode."""
@@ -357,6 +396,7 @@ class Kernels:
             torch.mm(x, weight.t(), out=out)
         return out
 
+    @_timed("linear_gate_up_act", _weight_bytes)
     def linear_act_mul(self, x, weight, out, gate_up, act: int = 0):
         """out[T, I] = act(x @ Wg.T) * (x @ Wu.T) for weight = [Wg; Wu] ([2 I, K]).  Few bfloat16 rows: one
         kernel, the activation in the product's epilogue (gate and up never leave the chip).  Otherwise the
@@ -375,6 +415,7 @@ class Kernels:
         self.act_mul(gate_up, out, act)
         return out
 
+    @_timed("linear_head", _weight_bytes)
     def linear_f32_out(self, x, weight, out):
         """out (float32) = x @ weight.T for x/weight in float32 or bfloat16."""
         _need(out, "out", torch.float32)
@@ -399,6 +440,7 @@ class Kernels:
         return out
 
     # -- hand-written kernels ----------------------------------------------------
+    @_timed("embedding")
     def embedding(self, ids, table, out, last_tokens=None, token_req=None, req_slots=None):
         """out[t] = table[ids[t]].  With `last_tokens` (and the batch row of each token and the request
         slot of each batch row), an id of -1 means the token that request sampled last."""
@@ -415,6 +457,7 @@ class Kernels:
                                             table.shape[0], _ptr(last_tokens), _ptr(token_req), _ptr(req_slots),
                                             _ptr(self.status), _stream()), "embedding")
 
+    @_timed("gather_rows")
     def gather_rows(self, src, rows, out):
         _need(src, "src")
         _need(rows, "rows", torch.int32)
@@ -425,6 +468,7 @@ class Kernels:
         self._check(self.lib.ullm_gather_rows(_DT[src.dtype], _ptr(rows), _ptr(src), _ptr(out), R, C, src.shape[0],
                                               _ptr(self.status), _stream()), "gather_rows")
 
+    @_timed("add_rmsnorm")
     def add_rmsnorm(self, x, residual, weight, eps, out):
         _need(x, "x")
         _need(weight, "weight", torch.float32)
@@ -439,6 +483,7 @@ class Kernels:
         self._check(self.lib.ullm_add_rmsnorm(_DT[x.dtype], _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), rows,
                                               cols, float(eps), _stream()), f"add_rmsnorm (row length {cols})")
 
+    @_timed("act_mul")
     def act_mul(self, gate_up, out, act: int = 0):
         _need(gate_up, "gate_up")
         _need(out, "out", gate_up.dtype)
@@ -451,6 +496,7 @@ class Kernels:
     def check_attention_sizes(self, *a):
         check_attention_sizes(*a)
 
+    @_timed("qk_norm_rope_store")
     def qk_norm_rope_store(self, qkv, num_q, num_kv, head_dim, q_w, k_w, eps, cos, sin, rotary_dim, positions,
                            slot_mapping, k_pages, v_pages):
         _need(qkv, "qkv")
@@ -561,6 +607,7 @@ class Kernels:
         self.attention_path = "decode"
         return
 
+    @_timed("attention")
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
                         head_dim, page_size, window, scale, ctx=None, fuse=None, ragged: bool = False):
         """Attention of every row of the flat batch over its request's pages.
@@ -635,6 +682,7 @@ class Kernels:
             int(window), float(scale), num_pages, _ptr(self.status), _stream()),
             f"paged_attention (head_dim {head_dim})")
 
+    @_timed("sampling")
     def argmax(self, logits, out):
         _need(logits, "logits", torch.float32, contiguous=False)
         _need(out, "out", torch.int32)
@@ -655,6 +703,7 @@ class Kernels:
     def sample_used_cluster(self) -> bool:
         return bool(self.lib.ullm_sample_last_used_cluster())
 
+    @_timed("sampling")
     def sample(self, logits, temperature, top_k, top_p, min_p, uniform, out, probs_out=None, row_slots=None,
                last_tokens=None):
         _need(logits, "logits", torch.float32, contiguous=False)

@@ -32,9 +32,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// false: gave up (the caller records it and stops waiting).  test_wait first: it is the cheaper
-// instruction when the phase is already complete, which is the common case while a ring drains.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// false: gave up after `limit` polls (the caller records it and stops waiting).  test_wait first: it is the
+// cheaper instruction when the phase is already complete, which is the common case while a ring drains.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, int limit) {
   uint32_t ok;
   asm volatile(
       "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -42,9 +42,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
       : "r"(lin_smem(bar)), "r"(parity)
       : "memory");
   if (ok) return true;
-  for (int i = 0; i < WAIT_LIMIT; ++i)
+  for (int i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_limited(bar, parity, WAIT_LIMIT);
 }
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(

@@ -38,6 +38,7 @@ def _generate(args) -> int:
     t0 = time.time()
     outs = llm.generate_batch(prompts, sp)
     dt = time.time() - t0
+    llm.engine.shutdown()  # (ends a --profile run: its tables are printed and written here)
     for o in outs:
         print(json.dumps({"prompt_tokens": o.num_prompt_tokens, "token_ids": o.token_ids, "text": o.text,
                           "finish_reason": o.finish_reason.name if o.finish_reason else None}))

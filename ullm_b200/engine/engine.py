@@ -57,11 +57,14 @@ class Engine:
 
             self.decode_graphs = DecodeGraphs(self.runner, self.sampler, config.max_bs)
         self._seed_counter = 0
-        self.profile_steps = config.profile
-        self.step_times: list[tuple[int, int, float]] = []
+        from .profiler import StepProfiler
+
+        self.profiler = StepProfiler(config.profile_dir, self._cuda)
         if config.warmup_graphs:
             n = self.warm_up_graphs()
             logger.info("recorded %d decode graphs", n)
+        if config.profile:
+            self.profile("start")
 
     # -- requests -------------------------------------------------------------------
     def add_sequence(self, sequence_id: str, prompt_token_ids: list[int], sampling_params: SamplingParams) -> None:
@@ -123,7 +126,7 @@ class Engine:
                 results += self._collect(self._inflight)
                 self._inflight = None
             return results
-        t0 = time.perf_counter() if self.profile_steps else 0.0
+        rec = self.profiler.step_begin(sched.scheduled) if self.profiler.started else None
         sampling = [s for s in sched.scheduled if s.samples]
         params = [s.seq.sampling_params for s in sampling]
         seeds = [s.seq.seed for s in sampling]
@@ -146,6 +149,10 @@ class Engine:
                 from ..csrc import kernels
 
                 handle = self.sampler.fetch_async(len(sampling), kernels().status if self._cuda else None)
+        if rec is not None:
+            self.profiler.step_launched(rec)
+            if handle is None:
+                self.profiler.step_read(rec)
         # bookkeeping that needs no token value: the portion is computed, the sampled token is a placeholder
         pending = []
         for s in sched.scheduled:
@@ -154,7 +161,7 @@ class Engine:
                 idx = self.scheduler.append_placeholder(s.seq)
                 s.seq.will_finish = self._length_reached(s.seq, idx + 1)
                 pending.append((s.seq, idx))
-        this_step = (handle, pending, len(sched.scheduled), sched.num_tokens, t0) if handle is not None else None
+        this_step = (handle, pending, rec) if handle is not None else None
         if self._inflight is not None:  # read the step before while this one runs
             results += self._collect(self._inflight)
             self._inflight = None
@@ -182,7 +189,7 @@ class Engine:
         return any(need[g] > cache.num_available_pages(g) for g in range(len(need)))
 
     def _collect(self, step) -> list[EngineStepResult]:
-        handle, pending, n_seqs, n_tokens, t0 = step
+        handle, pending, rec = step
         ids, status = self.sampler.wait(handle)
         if status:
             self.runner.check_device_status()
@@ -198,8 +205,8 @@ class Engine:
                 self.scheduler.finish_sequence(seq, reason)
             results.append(EngineStepResult(seq.seq_id, tok, finished, reason, seq.num_prompt_tokens,
                                             idx + 1 - seq.num_prompt_tokens))
-        if self.profile_steps:
-            self.step_times.append((n_seqs, n_tokens, time.perf_counter() - t0))
+        if rec is not None:
+            self.profiler.step_read(rec)
         return results
 
     def _length_reached(self, seq: Sequence, length: int) -> bool:
@@ -281,5 +288,19 @@ class Engine:
                  steps_run=self.runner.steps_run)
         return d
 
+    def profile(self, action: str) -> dict | None:
+        """"start": steps are timed from now on (per step, and per kernel group for the steps that run
+        eagerly).  "stop": the tables are printed and written as JSON into `profile_dir`; returns the report.
+        The reference's engine starts and stops a torch profiler the same way (ullm/core/engine.py:210-238)."""
+        if action == "start":
+            self.profiler.start()
+            return None
+        if action == "stop":
+            return self.profiler.stop()
+        logger.warning("Unknown profiling action: %s, ignoring.", action)
+        return None
+
     def shutdown(self) -> None:
+        if self.profiler.started:
+            self.profiler.stop()
         self.decode_graphs = None

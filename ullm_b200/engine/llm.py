@@ -185,10 +185,10 @@ class LLM:
         self.engine.shutdown()
 
     async def profile(self, action: str) -> None:
-        """"start" / "stop" per-step timing (the reference starts and stops a
-        torch profiler, ullm/core/engine.py:210-238)."""
+        """"start" / "stop" the timing of steps and kernel groups; "stop" prints the tables and writes them
+        to `profile_dir` (the reference starts and stops a torch profiler, ullm/core/engine.py:210-238)."""
         self._check_alive()
-        self.engine.profile_steps = action == "start"
+        self.engine.profile(action)
 
     # -- synchronous batch --------------------------------------------------------------
     def generate_batch(
