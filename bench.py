@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen3-8B layer sizes
+# The benchmark configuration: Qwen3-8B layer sizes
 QWEN3_8B = {
     "architectures": ["Qwen3ForCausalLM"],
     "num_hidden_layers": 36,
@@ -47,10 +47,45 @@ QWEN3_8B = {
     "max_position_embeddings": 40960,
     "torch_dtype": "bfloat16",
 }
+# Qwen3-32B layer sizes (65.5 GB of bfloat16 weights): the memory-planning case
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+# Qwen3-0.6B layer sizes, the model of the reference's own published benchmark (tied head)
+QWEN3_0_6B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, intermediate_size=3072,
+                  tie_word_embeddings=True)
+SHAPES = {"8b": ("Qwen3-8B shape", QWEN3_8B), "32b": ("Qwen3-32B shape", QWEN3_32B),
+          "0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B)}
 CONTEXT_LEN = 4096
 START_CONTEXT = 2048
 PREFILL_TOKENS = 2048
 PAGE_SIZE = 16
+# the serving workload: 256 requests, prompt and output lengths uniform in 100..1024, seed 5, eos ignored
+SERVE_REQUESTS, SERVE_MIN, SERVE_MAX, SERVE_SEED = 256, 100, 1024, 5
+
+
+def metric_name(batch: int, label: str) -> str:
+    """Both arms print this string, so that their values can be set side by side."""
+    return f"decode tok/s at batch {batch}, {label}"
+
+
+def common_config(label: str, cfg: dict, layers: int, batch: int) -> dict:
+    """The keys both arms' `config` has (each arm adds `timing`, `cuda_graph`, `l2`, `peaks`, `kv_dtype`)."""
+    return {
+        "model": label, "global_batch": batch, "seq_len": CONTEXT_LEN, "parallelism": "single-gpu",
+        "layers": layers, "layers_of_config": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
+        "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
+        "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"],
+        "vocab_size": cfg["vocab_size"], "start_context": START_CONTEXT, "page_size": PAGE_SIZE,
+    }
+
+
+def serve_workload(vocab: int):
+    """(prompts, output lengths) of the serving workload, from its seed."""
+    import random
+
+    rng = random.Random(SERVE_SEED)
+    prompts = [[rng.randrange(vocab) for _ in range(rng.randint(SERVE_MIN, SERVE_MAX))] for _ in range(SERVE_REQUESTS)]
+    outs = [rng.randint(SERVE_MIN, SERVE_MAX) for _ in range(SERVE_REQUESTS)]
+    return prompts, outs
 
 
 def peaks() -> dict:
@@ -129,33 +164,46 @@ def prefill_flops(cfg: dict, layers: int, T: int) -> float:
     return gemm + attn
 
 
+def _make_llm(cfg: dict, layers: int, max_bs: int, num_pages, budget: int = 4096, context: int = CONTEXT_LEN,
+              utilization: float = 0.9):
+    from ullm_b200.config import EngineConfig
+    from ullm_b200.engine.llm import LLM
+
+    cfg = dict(cfg, num_hidden_layers=layers)
+    tmp = tempfile.mkdtemp(prefix="ullm_b200_bench_")
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    ec = EngineConfig(
+        model=tmp, max_bs=max_bs, context_len=context, page_size=PAGE_SIZE, num_pages=num_pages,
+        gpu_memory_utilization=utilization, max_num_batched_tokens=budget, dtype="bfloat16", load_format="random",
+        seed=0, enable_prefix_caching=False, log_level="warning",
+    )
+    return LLM(ec), ec
+
+
 def run_ours(args) -> dict:
+    """Decode and prefill at the layer sizes of `--workload` (8b, the default line, or 32b)."""
     import torch
 
-    from ullm_b200.config import EngineConfig
     from ullm_b200.csrc import kernels
-    from ullm_b200.engine.llm import LLM
     from ullm_b200.sampling import SamplingParams
 
-    cfg = dict(QWEN3_8B)
+    label, shape = SHAPES[args.workload]
+    cfg = dict(shape)
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
     pk = peaks()
     nums = model_numbers(cfg, layers)
     K, W = args.steps, args.warmup
+    KP = max(K, 64)  # steps of the points at batch 1 and 64
     max_bs = 64
-    tmp = tempfile.mkdtemp(prefix="ullm_b200_bench_")
-    with open(os.path.join(tmp, "config.json"), "w") as f:
-        json.dump(cfg, f)
-    tokens_per_req = START_CONTEXT + 2 * (K + W) + 64
-    num_pages = max_bs * (-(-tokens_per_req // PAGE_SIZE)) + 64
-    ec = EngineConfig(
-        model=tmp, max_bs=max_bs, context_len=CONTEXT_LEN, page_size=PAGE_SIZE, num_pages=num_pages,
-        max_num_batched_tokens=4096, dtype="bfloat16", load_format="random", seed=0, enable_prefix_caching=False,
-        log_level="warning",
-    )
-    llm = LLM(ec)
+    if args.workload == "8b":
+        tokens_per_req = START_CONTEXT + 2 * (KP + W) + 64
+        num_pages = max_bs * (-(-tokens_per_req // PAGE_SIZE)) + 64
+    else:
+        num_pages = None  # planned from the memory that is free once the weights are resident
+    llm, ec = _make_llm(shape, layers, max_bs, num_pages)
     eng = llm.engine
     runner = eng.runner
     kern = kernels()
@@ -178,9 +226,30 @@ def run_ours(args) -> dict:
     def stop_batch(ids):
         for sid in ids:
             eng.abort_sequence(sid)
+        while eng.has_unfinished_sequences():
+            eng.step()
 
-    def time_decode(B, tag, steps, warmup):
-        """Device-timed decode through Engine.step: (ms per step, wall seconds per step, launches per step)."""
+    def even_graph(B):
+        dg = eng.decode_graphs
+        if dg is None or not dg.takes(B):
+            return None
+        held = [v for k, v in dg.graphs.items() if k[0] == dg.padded(B) and not any(k[1])]
+        return held[0][0] if held else None
+
+    def replay_ms(graph, steps):
+        """The device side alone: the captured step replayed back to back (it rewrites the same cache slots)."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def time_decode(B, tag, steps, warmup, ablate=False):
+        """Device-timed decode through Engine.step: (ms per step, wall seconds per step, launches per step,
+        mean context, device-only ms, group times)."""
         ids = start_batch(B, tag)
         for _ in range(warmup):
             eng.step()
@@ -197,22 +266,31 @@ def run_ours(args) -> dict:
         ms = e0.elapsed_time(e1) / steps
         launches = (kern.launches - l0) / steps
         ctx = START_CONTEXT + warmup + steps / 2.0
-        # the device side alone: the captured step replayed back to back (it rewrites the same cache slots)
-        graph_ms = None
-        dg = eng.decode_graphs
-        even = [v for k, v in (dg.graphs.items() if dg is not None else ()) if k[0] == dg.padded(B) and not any(k[1])]
-        if dg is not None and dg.takes(B) and even:
-            g0 = even[0][0]
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(steps):
-                g0.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            graph_ms = e0.elapsed_time(e1) / steps
+        graph = even_graph(B)
+        graph_ms = replay_ms(graph, steps) if graph is not None else None
+        groups = None
+        if ablate and graph is not None:
+            # What each group of kernels costs inside the step: the step recorded again without it (its results
+            # are then meaningless), replayed back to back, and the difference to the whole step.
+            groups = {}
+            sets = {"products": ("linear", "linear_gate_up_act"), "attention": ("attention",),
+                    "small": ("add_rmsnorm", "act_mul", "embedding", "gather_rows", "qk_norm_rope_store"),
+                    "head": ("linear_head",), "sampling": ("sampling",)}
+            dg = eng.decode_graphs
+            try:
+                for name, skip in sets.items():
+                    kern.skip_groups = frozenset(skip)
+                    dg.graphs.clear()
+                    eng.step()  # runs eagerly and records
+                    eng.step()
+                    gr = even_graph(B)
+                    if gr is not None:
+                        groups[name] = max(graph_ms - replay_ms(gr, steps), 0.0)
+            finally:
+                kern.skip_groups = frozenset()
+                dg.graphs.clear()
         stop_batch(ids)
-        time_decode.graph_ms = graph_ms
-        return ms, wall / steps, launches, ctx
+        return ms, wall / steps, launches, ctx, graph_ms, groups
 
     # ---- prefill of 2,048 tokens ---------------------------------------------------
     pre_ms = []
@@ -229,19 +307,19 @@ def run_ours(args) -> dict:
     pre = statistics.median(pre_ms[3:])
     pflops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / (pre / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre, 3),
-               "frac": round(pflops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pflops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "frac_of_sustained": round(pflops / (pre / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
 
     # ---- decode ----------------------------------------------------------------------
     B = args.batch
     with ClockSampler() as clk:
-        ms, wall, launches, ctx = time_decode(B, "d", K, W)
+        ms, wall, launches, ctx, graph_ms, groups = time_decode(B, "d", K, W, ablate=not args.no_groups)
     clocks = clk.summary()
-    graph_ms = time_decode.graph_ms
     value = B / (ms / 1e3)
-    # End to end through the call a user makes: LLM.generate_batch, token ids in, token ids out.  Two calls on
-    # fresh prompts of the same lengths, W and W + K new tokens each: their prompt work is the same, the
+    # End to end through the call a user makes: LLM.generate_batch, token ids in, token ids out.  Pairs of calls
+    # on fresh prompts of the same lengths, W and W + K new tokens each: their prompt work is the same, the
     # difference of their wall times is K decode steps (each with its staging copy from pinned memory and the
-    # read of its sampled ids) as the user sees them.
+    # read of its sampled ids) as the user sees them.  The median of five such differences.
     def user_call(n_new):
         ps = [prompt(START_CONTEXT) for _ in range(B)]
         torch.cuda.synchronize()
@@ -251,38 +329,53 @@ def run_ours(args) -> dict:
         assert all(len(o.token_ids) == n_new for o in outs)
         return dt
     user_call(W)  # warm
-    t_short = min(user_call(W) for _ in range(2))
-    t_long = min(user_call(W + K) for _ in range(2))
-    e2e_value = B * K / max(t_long - t_short, 1e-9)
+    KE = max(K, 32)
+    diffs = []
+    for _ in range(5):
+        t_short = user_call(W)
+        diffs.append(user_call(W + KE) - t_short)
+    e2e_value = B * KE / max(statistics.median(diffs), 1e-9)
     e2e_steps_value = B / wall  # the same loop as `value`, by the wall clock
     dbytes = decode_bytes(nums, B, ctx, cfg["hidden_size"])
     achieved = dbytes / (ms / 1e3) / 1e9
-    points = {}
-    for pb in (1, 64):
-        pms, _pw, _pl, _pc = time_decode(pb, f"b{pb}_", max(8, K // 2), max(3, W))
+    points = {f"decode_b{B}": round(value, 1)}
+    for pb in (1, 8, 64):
+        if pb == B:
+            pms, pctx, pgraph = ms, ctx, graph_ms
+        else:
+            pms, _pw, _pl, pctx, pgraph, _g = time_decode(pb, f"b{pb}_", KP, max(3, W))
         points[f"decode_b{pb}"] = round(pb / (pms / 1e3), 1)
-        if time_decode.graph_ms:
-            points[f"decode_b{pb}_device_only_ms"] = round(time_decode.graph_ms, 4)
-            points[f"decode_b{pb}_ms"] = round(pms, 4)
+        points[f"decode_b{pb}_ms"] = round(pms, 4)
+        points[f"decode_b{pb}_frac"] = round(decode_bytes(nums, pb, pctx, cfg["hidden_size"]) / (pms / 1e3) / 1e9
+                                             / pk["hbm_gbs"], 4)
+        if pgraph:
+            points[f"decode_b{pb}_device_only_ms"] = round(pgraph, 4)
+    out_groups = None
+    if groups:
+        # milliseconds of the step that go to each group, and for the three that stream memory the fraction of
+        # the copy bandwidth they reach on the bytes they have to read
+        gbytes = {"products": layers * nums["layer_weight_elems"] * 2,
+                  "attention": B * ctx * nums["kv_bytes_per_token"], "head": nums["head_elems"] * 2}
+        out_groups = {"method": "difference to the step recorded without the group, device only"}
+        for name, gms in groups.items():
+            out_groups[f"{name}_ms"] = round(gms, 4)
+            if name in gbytes and gms > 0:
+                out_groups[f"{name}_frac"] = round(gbytes[name] / (gms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
     st = runner.decode_staging
     h2d = st.layout(st.max_tokens, st.max_requests)["_end"][0] * 4 + eng.sampler.host.numel() * 4
+    config = common_config(label, shape, layers, B)
+    config.update({"kv_dtype": "bf16", "l2": "inputs>L2 (each step streams all weights)", "peaks": pk["source"],
+                   "cuda_graph": not ec.enforce_eager, "timing": "CUDA events around Engine.step",
+                   "num_pages": runner.cache.num_pages})
     out = {
-        "metric": "decode tok/s at batch 8, Qwen3-8B shape (also batch 1/64 and 2048-token prefill)",
+        "metric": metric_name(B, label),
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
-        "config": {
-            "model": "Qwen3-8B shape", "global_batch": B, "seq_len": CONTEXT_LEN, "parallelism": "single-gpu",
-            "layers": layers, "layers_of_config": full_layers, "hidden_size": cfg["hidden_size"],
-            "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
-            "head_dim": cfg["head_dim"], "intermediate_size": cfg["intermediate_size"],
-            "vocab_size": cfg["vocab_size"], "start_context": START_CONTEXT, "page_size": PAGE_SIZE,
-            "kv_dtype": "bf16", "l2": "inputs>L2 (each step streams all weights)", "peaks": pk["source"],
-            "cuda_graph": not ec.enforce_eager,
-        },
+        "config": config,
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(B * 4), "api": "LLM.generate_batch",
+                "d2h_bytes_per_step": int(B * 4), "api": "LLM.generate_batch", "steps": KE, "pairs": len(diffs),
                 "engine_step_wall_value": round(e2e_steps_value, 1)},
         "gpu_launches": int(round(launches * K)),
         "device_only_ms_per_step": round(graph_ms, 4) if graph_ms else None,
@@ -291,7 +384,85 @@ def run_ours(args) -> dict:
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
     }
+    if out_groups:
+        out["groups"] = out_groups
     return out
+
+
+def run_serve(args) -> dict:
+    """`--workload serve-0.6b`: the reference's own published workload (its bench.py: 256 requests, random prompt
+    and output lengths, continuous batching) at Qwen3-0.6B layer sizes, through `LLM.generate_batch`: host token
+    ids in, host token ids out, wall clock from the call to its return.  Each request generates exactly its
+    output length (`max_new_tokens`; the reference's script passes `max_tokens`, which bounds the total length
+    in its current tree)."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.sampling import SamplingParams
+
+    label, shape = SHAPES["0.6b"]
+    layers = args.layers or shape["num_hidden_layers"]
+    llm, ec = _make_llm(shape, layers, SERVE_REQUESTS, None, budget=8192, utilization=0.8)
+    prompts, outs = serve_workload(shape["vocab_size"])
+    sps = [SamplingParams(temperature=0.6, ignore_eos=True, max_new_tokens=n, seed=i) for i, n in enumerate(outs)]
+    # warm-up: a short run over every batch size on the way down records the decode graphs and times the
+    # library's products
+    llm.generate_batch(prompts[:SERVE_REQUESTS], [SamplingParams(temperature=0.6, ignore_eos=True,
+                                                                   max_new_tokens=4 + i % 3, seed=i)
+                                                    for i in range(SERVE_REQUESTS)])
+    kern = kernels()
+    torch.cuda.synchronize()
+    l0 = kern.launches
+    with ClockSampler() as clk:
+        t0 = time.perf_counter()
+        res = llm.generate_batch(prompts, sps)
+        dt = time.perf_counter() - t0
+    assert [len(o.token_ids) for o in res] == outs
+    gen, pro = sum(outs), sum(len(p) for p in prompts)
+    st = llm.engine.stats()
+    config = common_config(label, shape, layers, SERVE_REQUESTS)
+    config.update({"requests": SERVE_REQUESTS, "prompt_tokens": pro, "generated_tokens": gen,
+                   "lengths": f"uniform {SERVE_MIN}..{SERVE_MAX}, seed {SERVE_SEED}", "temperature": 0.6,
+                   "timing": "wall clock around LLM.generate_batch"})
+    config.pop("start_context")
+    return {
+        "metric": f"generated tok/s, {SERVE_REQUESTS} requests under continuous batching, {label}",
+        "value": round(gen / dt, 1), "unit": "tok/s", "n_gpus": 1, "steps": int(st.get("steps_run", 0)), "warmup": 1,
+        "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (random weights, uniform random token ids)", "config": config,
+        "clocks": clk.summary(), "seconds": round(dt, 3), "total_tok_s": round((gen + pro) / dt, 1),
+        "e2e": {"value": round(gen / dt, 1), "unit": "tok/s", "api": "LLM.generate_batch"},
+        "gpu_launches": int(kern.launches - l0), "preemptions": st.get("preemptions"),
+    }
+
+
+def run_extra_shapes(args, impl: str) -> dict:
+    """The two further workloads, each in a process of its own (the 32B shape needs the device to itself), as
+    flat entries for `points`."""
+    points = {}
+    jobs = [("serve-0.6b", "qwen3_0_6b_serve")] + ([("32b", "qwen3_32b")] if impl == "ours" else [])
+    for workload, key in jobs:
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", workload, "--impl", impl, "--steps",
+               str(args.steps), "--warmup", str(args.warmup), "--no-groups"]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+            line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
+            d = json.loads(line)
+        except Exception as e:  # noqa: BLE001 - a failed side run must not lose the main line
+            points[f"{key}_error"] = f"{type(e).__name__}: {e}"[:200]
+            continue
+        if "unavailable" in d:
+            points[f"{key}_unavailable"] = d["unavailable"][:200]
+        elif workload == "32b":
+            for k, v in d["points"].items():
+                points[f"{key}_{k}"] = v
+            points[f"{key}_prefill_tok_s"] = d["prefill"]["value"]
+            points[f"{key}_prefill_frac"] = d["prefill"]["frac"]
+        else:
+            points[f"{key}_generated_tok_s"] = d["value"]
+            points[f"{key}_total_tok_s"] = d.get("total_tok_s")
+            points[f"{key}_seconds"] = d.get("seconds")
+    return points
 
 
 def run_probe(args) -> int:
@@ -560,94 +731,185 @@ def _write_reference_model(path: str, cfg: dict) -> None:
     write_synthetic_tokenizer(path, cfg["vocab_size"])
 
 
+def _reference_available() -> str | None:
+    """None when the reference can run here, else the reason it cannot."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "ullm", "core")):
+        return "izmttk/ullm is not installed under baseline/_ref"
+    import torch
+
+    if not torch.cuda.is_available():
+        return "no CUDA device here (the reference's engine process needs one)"
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    return None
+
+
+class _StdoutToStderr:
+    """The reference logs to standard output, from child processes too: descriptor 1 goes to standard error
+    while it runs, so that this program's standard output holds the one JSON line only."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def __exit__(self, *a):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def run_reference(args) -> dict:
     """izmttk/ullm itself, unmodified, from baseline/_ref, through its own `LLM.generate`: the same metric
     (decode tokens per second at the given batch, requests holding 2,048 tokens) by the wall clock between
     streamed tokens.  Requests are started one after the other, each once the one before has its first token:
-    the reference's default (asynchronous) scheduling raises on a prefill step that holds several requests
-    (ullm/core/input_batch.py:185 broadcasts [tokens] against [requests])."""
+    the reference raises on a prefill step that holds several new requests (ullm/core/input_batch.py:185
+    broadcasts [tokens] against [requests])."""
     import asyncio
 
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref, "ullm", "core")):
-        return {"impl": "reference", "unavailable": "izmttk/ullm is not installed under baseline/_ref"}
-    import torch
-
-    if not torch.cuda.is_available():
-        return {"impl": "reference", "unavailable": "no CUDA device here (the reference's engine process needs one)"}
-    sys.path.insert(0, ref)
-    cfg = dict(QWEN3_8B)
+    why = _reference_available()
+    if why:
+        return {"impl": "reference", "unavailable": why}
+    label, shape = SHAPES[args.workload]
+    cfg = dict(shape)
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
     K, W, B = args.steps, args.warmup, args.batch
-    # the reference logs to standard output, from child processes too: send descriptor 1 to standard error
-    # while it runs, so that this program's standard output holds the one JSON line only
-    sys.stdout.flush()
-    saved_stdout = os.dup(1)
-    os.dup2(2, 1)
-    try:
-        import torch
+    with _StdoutToStderr():
+        try:
+            import torch
 
-        tmp = tempfile.mkdtemp(prefix="ullm_ref_model_")
-        _write_reference_model(tmp, cfg)
-        from ullm import LLM, EngineConfig, SamplingParams  # the reference's public API
+            tmp = tempfile.mkdtemp(prefix="ullm_ref_model_")
+            _write_reference_model(tmp, cfg)
+            from ullm import LLM, EngineConfig, SamplingParams  # the reference's public API
 
-        g = torch.Generator().manual_seed(1)
-        prompts = [torch.randint(0, cfg["vocab_size"], (START_CONTEXT,), generator=g).tolist() for _ in range(B + 1)]
-        stamps: list[list[float]] = [[] for _ in prompts]
-        result: dict = {}
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, cfg["vocab_size"], (START_CONTEXT,), generator=g).tolist() for _ in range(B + 1)]
+            stamps: list[list[float]] = [[] for _ in prompts]
+            result: dict = {}
 
-        async def main_async():
-            llm = LLM(EngineConfig(model=tmp, gpu_memory_utilization=0.8, max_bs=max(B, 8), tp_size=1, pp_size=1,
-                                   nccl_port=29533, device_ids=[0], context_len=CONTEXT_LEN))
-            first = [asyncio.Event() for _ in prompts]
+            async def main_async():
+                llm = LLM(EngineConfig(model=tmp, gpu_memory_utilization=0.8, max_bs=max(B, 8), tp_size=1, pp_size=1,
+                                       nccl_port=29533, device_ids=[0], context_len=CONTEXT_LEN))
+                first = [asyncio.Event() for _ in prompts]
 
-            async def run(i, n_new):
-                sp = SamplingParams(temperature=1.0, top_k=1, ignore_eos=True, max_new_tokens=n_new)
-                async for _out in llm.generate(prompts[i], sp):
-                    stamps[i].append(time.perf_counter())
-                    first[i].set()
+                async def run(i, n_new):
+                    sp = SamplingParams(temperature=1.0, top_k=1, ignore_eos=True, max_new_tokens=n_new)
+                    async for _out in llm.generate(prompts[i], sp):
+                        stamps[i].append(time.perf_counter())
+                        first[i].set()
 
-            # prefill of one 2,048-token prompt: submit -> first token (after one untimed run, which also
-            # pays for the attention library's just-in-time compilation)
-            await run(B, 1)
-            stamps[B].clear()
-            t0 = time.perf_counter()
-            await run(B, 1)
-            result["prefill_s"] = stamps[B][0] - t0
-            tasks = []
-            for i in range(B):
-                tasks.append(asyncio.create_task(run(i, 2 * B + W + K + 8)))
-                await first[i].wait()
-            await asyncio.gather(*tasks)
-            await llm.shutdown()
+                # prefill of one 2,048-token prompt: submit -> first token (after one untimed run, which also
+                # pays for the attention library's just-in-time compilation)
+                await run(B, 1)
+                stamps[B].clear()
+                t0 = time.perf_counter()
+                await run(B, 1)
+                result["prefill_s"] = stamps[B][0] - t0
+                tasks = []
+                for i in range(B):
+                    tasks.append(asyncio.create_task(run(i, 2 * B + W + K + 8)))
+                    await first[i].wait()
+                await asyncio.gather(*tasks)
+                await llm.shutdown()
 
-        asyncio.run(main_async())
-        # the window in which all B requests decode: from token (B + W) of the last-started request on
-        start = max(s[-(K + 1)] for s in stamps[:B])
-        end = max(s[-1] for s in stamps[:B])
-        steps_ms = (end - start) / K * 1e3
-        value = B * K / (end - start)
-        return {
-            "impl": "reference", "metric": "decode tok/s at batch 8, Qwen3-8B shape", "value": round(value, 1),
-            "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(steps_ms, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (random weights, uniform random token ids)",
-            "config": {"model": "Qwen3-8B shape", "global_batch": B, "seq_len": CONTEXT_LEN,
-                       "parallelism": "single-gpu", "layers": layers, "layers_of_config": full_layers,
-                       "start_context": START_CONTEXT, "timing": "wall clock between streamed tokens"},
-            "e2e": {"value": round(value, 1), "unit": "tok/s"},
-            "prefill": {"value": round(PREFILL_TOKENS / result["prefill_s"], 1), "tokens": PREFILL_TOKENS,
-                        "ms": round(result["prefill_s"] * 1e3, 3)},
-        }
-    except BaseException as e:  # the reference kills its process tree on errors; report, do not propagate
-        msg = f"{type(e).__name__}: {e}".splitlines()[0][:300]
-        return {"impl": "reference", "unavailable": f"izmttk/ullm failed to run here: {msg}"}
-    finally:
-        sys.stdout.flush()
-        os.dup2(saved_stdout, 1)
-        os.close(saved_stdout)
+            asyncio.run(main_async())
+            # the window in which all B requests decode: from token (B + W) of the last-started request on
+            start = max(s[-(K + 1)] for s in stamps[:B])
+            end = max(s[-1] for s in stamps[:B])
+            steps_ms = (end - start) / K * 1e3
+            value = B * K / (end - start)
+            config = common_config(label, shape, layers, B)
+            config.update({"kv_dtype": "bf16", "l2": "inputs>L2 (each step streams all weights)", "peaks": "n/a",
+                           "cuda_graph": True, "timing": "wall clock between streamed tokens", "num_pages": None})
+            return {
+                "impl": "reference", "metric": metric_name(B, label), "value": round(value, 1),
+                "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(steps_ms, 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic (random weights, uniform random token ids)",
+                "config": config,
+                "e2e": {"value": round(value, 1), "unit": "tok/s", "api": "LLM.generate"},
+                "prefill": {"value": round(PREFILL_TOKENS / result["prefill_s"], 1), "tokens": PREFILL_TOKENS,
+                            "ms": round(result["prefill_s"] * 1e3, 3)},
+                "points": {f"decode_b{B}": round(value, 1)},
+            }
+        except BaseException as e:  # the reference kills its process tree on errors; report, do not propagate
+            msg = f"{type(e).__name__}: {e}".splitlines()[0][:300]
+            return {"impl": "reference", "unavailable": f"izmttk/ullm failed to run here: {msg}"}
+
+
+def run_reference_serve(args) -> dict:
+    """The serving workload through the reference: the same prompts and output lengths as `run_serve`, streamed
+    through its `LLM.generate`.  As in its own bench.py all requests are submitted from one task list, except
+    that each is submitted once the one before has its first token (a prefill step that holds several new
+    requests raises in its current tree, ullm/core/input_batch.py:185); decoding goes on meanwhile, so the
+    batch grows as in continuous batching."""
+    import asyncio
+
+    why = _reference_available()
+    if why:
+        return {"impl": "reference", "unavailable": why}
+    label, shape = SHAPES["0.6b"]
+    cfg = dict(shape)
+    layers = args.layers or cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers
+    with _StdoutToStderr():
+        try:
+            tmp = tempfile.mkdtemp(prefix="ullm_ref_model_")
+            # the reference never ties the head: its loader wants lm_head.weight in the file
+            _write_reference_model(tmp, dict(cfg, tie_word_embeddings=False))
+            from ullm import LLM, EngineConfig, SamplingParams
+
+            prompts, outs = serve_workload(cfg["vocab_size"])
+            done = [0] * len(prompts)
+            result: dict = {}
+
+            async def main_async():
+                llm = LLM(EngineConfig(model=tmp, gpu_memory_utilization=0.8, max_bs=SERVE_REQUESTS, tp_size=1,
+                                       pp_size=1, nccl_port=29534, device_ids=[0], context_len=CONTEXT_LEN))
+                first = [asyncio.Event() for _ in prompts]
+
+                async def run(i, n_new):
+                    sp = SamplingParams(temperature=0.6, ignore_eos=True, max_new_tokens=n_new)
+                    async for _out in llm.generate(prompts[i], sp):
+                        done[i] += 1
+                        first[i].set()
+
+                await run(0, 8)  # untimed: the attention library compiles at its first call
+                done[0] = 0
+                first[0].clear()
+                t0 = time.perf_counter()
+                tasks = []
+                for i, n in enumerate(outs):
+                    tasks.append(asyncio.create_task(run(i, n)))
+                    await first[i].wait()
+                await asyncio.gather(*tasks)
+                result["s"] = time.perf_counter() - t0
+                await llm.shutdown()
+
+            asyncio.run(main_async())
+            if done != outs:
+                raise RuntimeError(f"{sum(done)} tokens came back, {sum(outs)} were asked for")
+            gen, pro, dt = sum(outs), sum(len(p) for p in prompts), result["s"]
+            config = common_config(label, shape, layers, SERVE_REQUESTS)
+            config.update({"requests": SERVE_REQUESTS, "prompt_tokens": pro, "generated_tokens": gen,
+                           "lengths": f"uniform {SERVE_MIN}..{SERVE_MAX}, seed {SERVE_SEED}", "temperature": 0.6,
+                           "timing": "wall clock around the generate tasks"})
+            config.pop("start_context")
+            return {
+                "impl": "reference",
+                "metric": f"generated tok/s, {SERVE_REQUESTS} requests under continuous batching, {label}",
+                "value": round(gen / dt, 1), "unit": "tok/s", "n_gpus": 1, "steps": 0, "warmup": 1,
+                "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "config": config,
+                "seconds": round(dt, 3), "total_tok_s": round((gen + pro) / dt, 1),
+                "e2e": {"value": round(gen / dt, 1), "unit": "tok/s", "api": "LLM.generate"},
+            }
+        except BaseException as e:
+            msg = f"{type(e).__name__}: {e}".splitlines()[0][:300]
+            return {"impl": "reference", "unavailable": f"izmttk/ullm failed to run here: {msg}"}
 
 
 def main() -> int:
@@ -657,6 +919,12 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b"],
+                    help="8b: the default line (Qwen3-8B layer sizes); 32b: the same at Qwen3-32B layer sizes; "
+                         "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes")
+    ap.add_argument("--no-extra-shapes", action="store_true",
+                    help="the default line without the 32b and serve-0.6b runs that it adds to `points`")
+    ap.add_argument("--no-groups", action="store_true", help="skip the per-kernel-group times of the decode step")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "sampling"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
@@ -676,15 +944,25 @@ def main() -> int:
         return run_sampling_probe(args)
     if args.probe:
         return run_probe(args)
+    extra = args.workload == "8b" and not args.no_extra_shapes and not args.layers
     if args.impl == "reference":
-        print(json.dumps(run_reference(args)))
+        out = run_reference_serve(args) if args.workload == "serve-0.6b" else run_reference(args)
+        if extra and "unavailable" not in out:
+            out.setdefault("points", {}).update(run_extra_shapes(args, "reference"))
+        print(json.dumps(out))
         return 0
     import torch
 
     if not torch.cuda.is_available():
         print("bench.py: no CUDA device: this engine has no CPU path", file=sys.stderr)
         return 1
-    out = run_ours(args)
+    out = run_serve(args) if args.workload == "serve-0.6b" else run_ours(args)
+    if extra:
+        import gc
+
+        gc.collect()  # this run's engine goes first: the further shapes run in processes of their own
+        torch.cuda.empty_cache()
+        out["points"].update(run_extra_shapes(args, "ours"))
     print(json.dumps(out))
     return 0
 

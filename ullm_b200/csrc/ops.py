@@ -73,6 +73,8 @@ def _timed(group: str, nbytes=None):
 
     def outer(fn):
         def inner(self, *a, **k):
+            if self.skip_groups and group in self.skip_groups:
+                return None  # a measurement leaves this group out (the step's results are then meaningless)
             t = self.timer
             if t is None:
                 return fn(self, *a, **k)
@@ -143,6 +145,9 @@ class Kernels:
         self._lt_ws = None
         self._lt_tuned = set()
         self.timer = None  # a KernelGroupTimer while a profile is being taken
+        # groups of kernels (the names `_timed` books them under) that are NOT launched: only for measuring what a
+        # group costs inside a step, by the difference; the step's results are wrong while this is set
+        self.skip_groups: frozenset = frozenset()
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
