@@ -551,6 +551,10 @@ def run_linear_probe(args) -> int:
             t["256-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], out, None, None, 2), copies)
         if M <= 32:
             t["skinny"] = timeit(lambda i: K.skinny_linear(x, ws[i], out), copies)
+            for bps in (1, 2):
+                K.lib.ullm_linear_stream_blocks_per_sm(bps)
+                t[f"stream x{bps}"] = timeit(lambda i: K.stream_linear(x, ws[i], out), copies)
+            K.lib.ullm_linear_stream_blocks_per_sm(1)
         line = "  ".join(f"{k} {v:7.1f} ({nbytes / v / 1e6:4.2f} TB/s)" for k, v in t.items())
         print(f"{name:8s} N={N:6d} K={Kd:5d}  {line}  ideal {nbytes / (pk['hbm_gbs'] * 1e9) * 1e6:6.1f}")
         if name == "gate_up":
@@ -563,6 +567,7 @@ def run_linear_probe(args) -> int:
                 t["256-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], act, None, 0, 2), copies)
             if M <= 32:
                 t["skinny fused"] = timeit(lambda i: K.skinny_linear(x, ws[i], act, None, 0), copies)
+                t["stream fused"] = timeit(lambda i: K.stream_linear(x, ws[i], act, None, 0), copies)
             print("         with the gate activation:  " + "  ".join(f"{k} {v:7.1f}" for k, v in t.items()))
         del ws
     K.raise_on_status()

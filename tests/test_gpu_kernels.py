@@ -564,6 +564,74 @@ def test_skinny_linear_with_fused_gate_activation(M, I, Kd, act):
             assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
 
 
+@pytest.mark.parametrize("M,N,Kd", [
+    (1, 16, 8), (1, 128, 64), (8, 4096, 4096), (8, 6144, 4096), (3, 4096, 12288), (16, 1000, 520), (17, 331, 80),
+    (32, 777, 4104), (5, 151936, 1024), (24, 130, 72), (9, 24576, 4096), (16, 33, 256), (2, 4097, 776),
+])
+def test_stream_linear(M, N, Kd):
+    """The weight-streaming TMA product for decode-sized batches against a float32 reference, with and without
+    bias and residual, both output types; row counts that fill 1, 2 and 4 batch tiles, N that is no multiple of
+    the 32-row unit (also fewer units than blocks and several units per block), K that is no multiple of the
+    256-wide stage or of the 64-wide box."""
+    x = rnd(M, Kd, seed=80, dtype=torch.bfloat16)
+    w = rnd(N, Kd, seed=81, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(N, seed=82, dtype=torch.bfloat16)
+    res = rnd(M, N, seed=83, dtype=torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for b, rs in ((None, None), (bias, None), (None, res), (bias, res)):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+            assert K().stream_linear(x, w, out, b, None, rs)
+            K().raise_on_status()
+            r = ref + (b.float() if b is not None else 0) + (rs.float() if rs is not None else 0)
+            err = (out.float() - r).abs().max().item() / max(r.abs().max().item(), 1e-6)
+            assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+    # the residual may be the output itself (the residual stream updated in place)
+    acc = res.clone()
+    assert K().stream_linear(x, w, acc, None, None, acc)
+    r = ref + res.float()
+    assert (acc.float() - r).abs().max().item() / r.abs().max().item() <= 1e-2
+
+
+@pytest.mark.parametrize("M,I,Kd,act", [
+    (1, 16, 32, 0), (8, 12288, 4096, 0), (16, 200, 520, 1), (31, 331, 264, 0), (5, 96, 8192, 1), (12, 3072, 1024, 0),
+])
+def test_stream_linear_with_fused_gate_activation(M, I, Kd, act):
+    x = rnd(M, Kd, seed=90, dtype=torch.bfloat16)
+    w = rnd(2 * I, Kd, seed=91, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(2 * I, seed=92, dtype=torch.bfloat16)
+    for b in (None, bias):
+        y = x.float() @ w.float().t() + (b.float() if b is not None else 0)
+        g, u = y[:, :I], y[:, I:]
+        ref = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, I), 7.0, dtype=out_dtype, device="cuda")
+            assert K().stream_linear(x, w, out, b, act)
+            K().raise_on_status()
+            err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+            assert err <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * Kd ** 0.5), f"max err {err:.3e} of scale"
+
+
+def test_stream_linear_is_deterministic_and_refuses_what_it_does_not_take():
+    x = rnd(16, 4096, seed=70, dtype=torch.bfloat16)
+    w = rnd(6144, 4096, seed=71, dtype=torch.bfloat16, scale=0.05)
+    outs = []
+    for bps in (1, 2, 1):  # one or two blocks per SM deal the units differently; the sums do not change
+        K().lib.ullm_linear_stream_blocks_per_sm(bps)
+        out = torch.empty(16, 6144, dtype=torch.float32, device="cuda")
+        assert K().stream_linear(x, w, out)
+        outs.append(out)
+    one = torch.empty(1, 6144, dtype=torch.float32, device="cuda")
+    assert K().stream_linear(x[:1].contiguous(), w, one)
+    K().raise_on_status()
+    assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])
+    assert torch.equal(one[0], outs[0][0]), "a row's result does not depend on the other rows of the batch"
+    assert not K().stream_linear(rnd(40, 64, seed=1, dtype=torch.bfloat16), rnd(128, 64, seed=2, dtype=torch.bfloat16),
+                                 torch.empty(40, 128, dtype=torch.bfloat16, device="cuda"))
+    assert not K().stream_linear(rnd(4, 60, seed=1, dtype=torch.bfloat16), rnd(128, 60, seed=2, dtype=torch.bfloat16),
+                                 torch.empty(4, 128, dtype=torch.bfloat16, device="cuda"))
+
+
 def test_skinny_linear_is_deterministic_and_refuses_what_it_does_not_take():
     x = rnd(16, 4096, seed=70, dtype=torch.bfloat16)
     w = rnd(512, 4096, seed=71, dtype=torch.bfloat16, scale=0.05)

@@ -134,8 +134,9 @@ class Kernels:
         # the stream-K tcgen05 kernel (M <= 64)
         mode = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "0")
         self.small_m_mode = {"1": "tcgen05", "0": None, "": None}.get(mode, mode)
-        if self.small_m_mode not in (None, "tcgen05", "skinny"):
-            raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: 0, skinny or tcgen05")
+        if self.small_m_mode not in (None, "tcgen05", "skinny", "stream"):
+            raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: 0, stream, skinny or tcgen05")
+        self.stream_rows = int(os.environ.get("ULLM_B200_STREAM_ROWS", "32"))  # rows up to which "stream" applies
         # rows from which the gated feed-forward's first product runs on the own tcgen05 kernel with the activation
         # fused (0 rows would mean always; a huge number never)
         self.fused_mlp_rows = int(os.environ.get("ULLM_B200_FUSED_MLP_ROWS", "4096"))
@@ -171,6 +172,7 @@ class Kernels:
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
+            "ullm_linear_stream": [P, P, P, P, P, I, I, I, I, I, P, P],
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_lt_linear": [P, P, P, I, I, I, I, P, LL, I, P, LL, P],
@@ -221,6 +223,10 @@ class Kernels:
         L.ullm_linear_tcgen05_large_supported.restype = c_int
         L.ullm_linear_skinny_supported.argtypes = [I, I, I]
         L.ullm_linear_skinny_supported.restype = c_int
+        L.ullm_linear_stream_supported.argtypes = [I, I, I]
+        L.ullm_linear_stream_supported.restype = c_int
+        L.ullm_linear_stream_blocks_per_sm.argtypes = [I]
+        L.ullm_linear_stream_blocks_per_sm.restype = None
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
@@ -304,6 +310,29 @@ class Kernels:
                     f"linear_skinny ({M}x{K} . {N}x{K})")
         return True
 
+    def stream_linear(self, x, weight, out, bias=None, act: int | None = None, residual=None) -> bool:
+        """The weight-streaming product for few rows (M <= 32; csrc/linear_stream.cu): a TMA ring per block that
+        is filled with weight tiles before the kernel in front has finished (programmatic dependent launch),
+        mma.sync on the swizzled tiles.  Same contract as `small_m_linear`; `residual` ([M, n_out], bfloat16;
+        may be `out`) is added to the product in 32-bit before the one rounding."""
+        M, K = x.shape
+        N = weight.shape[0]
+        n_out = N // 2 if act is not None else N
+        if (x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous()
+                or not weight.is_contiguous() or not out.is_contiguous() or weight.shape[1] != K
+                or out.shape != (M, n_out) or out.dtype not in (torch.bfloat16, torch.float32)
+                or (bias is not None and bias.dtype != torch.bfloat16) or (act is not None and N % 2)
+                or (residual is not None and (residual.dtype != torch.bfloat16 or residual.shape != (M, n_out)
+                                              or not residual.is_contiguous()))
+                or not self.lib.ullm_linear_stream_supported(M, N, K)
+                or x.data_ptr() % 16 or weight.data_ptr() % 16):
+            return False
+        self._check(self.lib.ullm_linear_stream(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
+                                                1 if out.dtype == torch.float32 else 0,
+                                                0 if act is None else act + 1, _ptr(self.status), _stream()),
+                    f"linear_stream ({M}x{K} . {N}x{K})")
+        return True
+
     def large_linear(self, x, weight, out, bias=None, act: int | None = None, variant: int = 0) -> bool:
         """The persistent tcgen05/TMA product for many rows (prompt portions): tiles of 128 x 256, two accumulators
         in tensor memory, bias and the gate activation in the epilogue.  Same contract as `small_m_linear`."""
@@ -379,6 +408,8 @@ class Kernels:
         """Tries the hand-written few-row product that the mode names; False: the caller uses the library."""
         if self.small_m_mode == "skinny":
             return x.shape[0] <= 32 and self.skinny_linear(x, weight, out, bias, act)
+        if self.small_m_mode == "stream":
+            return x.shape[0] <= self.stream_rows and self.stream_linear(x, weight, out, bias, act)
         if self.small_m_mode == "tcgen05":
             if x.shape[0] <= 64:
                 return self.small_m_linear(x, weight, out, bias, act)
