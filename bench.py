@@ -532,6 +532,20 @@ def run_linear_probe(args) -> int:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / (2 * iters) * 1000.0
 
+    if args.only:
+        # one kernel on one shape, launched eagerly a few times: what a profiler is pointed at
+        N, Kd = shapes[args.shape]
+        ws = [torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(2)]
+        x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = {"stream": K.stream_linear, "skinny": K.skinny_linear, "tcgen05": K.small_m_linear,
+              "library": lambda a, b, c: torch.mm(a, b.t(), out=c)}[args.only]
+        for i in range(args.steps):
+            fn(x, ws[i % 2], out)
+        torch.cuda.synchronize()
+        K.raise_on_status()
+        print(f"probe linear: {args.only} on {args.shape} ({N} x {Kd}), {M} rows, {args.steps} launches")
+        return 0
     print(f"rows {M}; microseconds per product (weights streamed at the copy peak: 'ideal')")
     for name, (N, Kd) in shapes.items():
         nbytes = N * Kd * 2
@@ -551,12 +565,11 @@ def run_linear_probe(args) -> int:
             t["256-row tiles"] = timeit(lambda i: K.large_linear(x, ws[i], out, None, None, 2), copies)
         if M <= 32:
             t["skinny"] = timeit(lambda i: K.skinny_linear(x, ws[i], out), copies)
-            for bps in (1, 2):
-                K.lib.ullm_linear_stream_blocks_per_sm(bps)
-                t[f"stream x{bps}"] = timeit(lambda i: K.stream_linear(x, ws[i], out), copies)
-            K.lib.ullm_linear_stream_blocks_per_sm(1)
-        line = "  ".join(f"{k} {v:7.1f} ({nbytes / v / 1e6:4.2f} TB/s)" for k, v in t.items())
-        print(f"{name:8s} N={N:6d} K={Kd:5d}  {line}  ideal {nbytes / (pk['hbm_gbs'] * 1e9) * 1e6:6.1f}")
+            for ks in (1, 8):
+                K.lib.ullm_linear_stream_ksplit_max(ks)
+                t["stream" + (", no clusters" if ks == 1 else "")] = timeit(lambda i: K.stream_linear(x, ws[i], out), copies)
+        line = "  ".join(f"{k} {v:.1f} ({nbytes / v / 1e6:4.2f})" for k, v in t.items())
+        print(f"{name:8s} N={N:6d} K={Kd:5d}  ideal {nbytes / (pk['hbm_gbs'] * 1e9) * 1e6:.1f}  us (TB/s): {line}")
         if name == "gate_up":
             act = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
             t = {"library+act_mul": timeit(lambda i: (torch.mm(x, ws[i].t(), out=out), K.act_mul(out, act, 0)), copies)}
@@ -933,6 +946,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "sampling"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
+    ap.add_argument("--only", default=None, choices=["stream", "skinny", "tcgen05", "library"],
+                    help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
+    ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
+                    help="--probe linear --only: which of the decode step's products")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
     args = ap.parse_args()

@@ -10,14 +10,20 @@
 //     the ring never drains between units.  A stage holds 32 rows x 256 k of the weight (16 KB) and the same
 //     256 k of all batch rows, both brought in by TMA (boxes of 16 rows x 64 k, 128-byte swizzle; rows and
 //     columns outside the matrices read as zeros, so any N, any M <= 32 and any K that is a multiple of 8 work).
-//   * One producer thread issues the TMA copies; eight consumer warps multiply: warp w takes the 16-row half
-//     w & 1 and the 64-wide k quarter w >> 1 of every stage, with the weight rows on the M side of
-//     mma.sync.m16n8k16 and the batch rows on its N side (ldmatrix from the swizzled boxes).  The four k
-//     quarters of a half meet in shared memory at the end of a unit and are added in a fixed order.
+//   * One producer thread issues the TMA copies (a stage is one copy per matrix when K is a multiple of 64);
+//     eight consumer warps multiply: warp w takes the 16-row half w & 1 and the 64-wide k quarter w >> 1 of
+//     every stage, reads its fragments (ldmatrix from the swizzled boxes), gives the stage back and only then
+//     issues the tensor instructions, with the weight rows on the M side of mma.sync.m16n8k16 and the batch
+//     rows on its N side.  The four k quarters of a half meet in shared memory at the end of a unit and are
+//     added in a fixed order.
 //   * The weights do not depend on the kernel before this one in the stream.  Under programmatic dependent
 //     launch the producer fills the whole ring with weight tiles BEFORE griddepcontrol.wait and asks for the
 //     batch rows after it, so that this kernel's first megabytes stream while the kernel before it drains.
 //     A block needs at most 112 KB of shared memory: its successor's blocks fit beside it on the SM.
+//   * A narrow output has too few units to give every SM something to stream.  Then 2, 4 or 8 blocks form a
+//     thread-block cluster around one unit, each takes a range of K, and ranks 1.. put their sums into rank 0's
+//     shared memory (distributed shared memory, released by an arrival at rank 0's barrier); rank 0 adds them in
+//     rank order and writes the result.
 //   * Every mbarrier wait is bounded; a wait that runs out records ULLM_STATUS_TIMEOUT, the block stops
 //     computing but keeps arriving at its barriers, waits (bounded) for the copies it still has in flight, and
 //     returns.
@@ -28,7 +34,7 @@
 #define LS_UNIT_ROWS 32
 #define LS_BK 256                 // k per stage
 #define LS_W_STAGE_BYTES 16384    // 32 rows x 256 k x 2 bytes
-#define LS_MAX_SMEM (112 * 1024)
+#define LS_MAX_STAGES 16
 
 struct LsParams {
   const __nv_bfloat16* bias;      // [N] or null
@@ -41,8 +47,52 @@ struct LsParams {
   int num_units;
   int k_blocks;                   // ceil(K / 256)
   int stages;
+  int chunked;                    // K is a multiple of 64: a stage comes in by one copy per matrix (3-D boxes)
+  int ksplit;                     // 1, 2, 4 or 8: blocks of a cluster that share a unit, each with a range of K
   int* status;
 };
+
+// A matrix [rows, cols] with cols a multiple of 64, seen as [cols / 64][rows][64]: one box brings 64-wide k
+// chunks c .. c + 3 of `box_rows` rows, laid out chunk after chunk, each chunk rows x 128 bytes (128-byte
+// swizzle): the same layout as four two-dimensional boxes, for a quarter of the copies.
+static bool ls_chunked_map(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+  struct Key {
+    const void* ptr;
+    long long rows, cols;
+    int box_rows;
+    bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^
+             (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows * 7919;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> maps;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  Key key{ptr, rows, cols, box_rows};
+  auto it = maps.find(key);
+  if (it != maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr || cols % 64) return false;
+  cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 4};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (maps.size() > 4096) maps.clear();
+  maps[key] = m;
+  *out = m;
+  return true;
+}
 
 __device__ __forceinline__ void ls_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -63,24 +113,62 @@ __device__ __forceinline__ void ls_bar_sync_consumers() {
   asm volatile("bar.sync 1, %0;" ::"n"(LS_CONSUMER_WARPS * 32) : "memory");
 }
 
+// ---- cluster helpers: a block's rank, a peer's shared-memory address, remote stores and barrier arrivals ------
+__device__ __forceinline__ uint32_t ls_map_to_rank(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void ls_st_cluster_f4(uint32_t addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void ls_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+// bounded wait that also makes the peers' stores (released at cluster scope) visible
+__device__ __forceinline__ bool ls_wait_cluster(uint64_t* bar, uint32_t parity) {
+  for (int i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(lin_smem(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void ls_cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // NT: tiles of 8 batch rows (M <= 8 NT).
 template <int NT>
-__global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_constant__ CUtensorMap w_map,
+__global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __grid_constant__ CUtensorMap w_map,
+                                                                   const __grid_constant__ CUtensorMap w32_map,
                                                                    const __grid_constant__ CUtensorMap x_map,
                                                                    const LsParams p) {
   constexpr int XR = 8 * NT;                                    // batch rows of a stage
   constexpr int X_BOX_BYTES = XR * 128;                         // one box: XR rows x 64 k
   constexpr int STAGE_BYTES = LS_W_STAGE_BYTES + 4 * X_BOX_BYTES;
   extern __shared__ unsigned char ls_smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8];
+  __shared__ __align__(8) uint64_t full_bar[LS_MAX_STAGES], empty_bar[LS_MAX_STAGES];
+  __shared__ __align__(8) uint64_t peer_bar;  // rank 0: the peers' partial sums of the current unit have arrived
   __shared__ int abort_flag;
   pdl_launch_dependents();
   unsigned char* ring = (unsigned char*)(((uintptr_t)ls_smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int NP = NT > 1 ? 2 : 1;                            // batch tiles that meet per pass
   float* red = reinterpret_cast<float*>(ring + p.stages * STAGE_BYTES);  // [8 warps][32 lanes][NP][4]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int my_units = p.num_units > (int)blockIdx.x ? (p.num_units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-  const int total_it = my_units * p.k_blocks;
+  // A cluster of `ksplit` blocks (consecutive blockIdx.x) shares its units: rank r takes k blocks
+  // [r * kper, (r + 1) * kper) of each, rank 0 gathers the partial sums and writes the result.
+  const int rank = (int)blockIdx.x % p.ksplit, cid = (int)blockIdx.x / p.ksplit, ncl = (int)gridDim.x / p.ksplit;
+  const int kper = (p.k_blocks + p.ksplit - 1) / p.ksplit;
+  const int kb0 = rank * kper;
+  const int nkb = p.k_blocks - kb0 < kper ? (p.k_blocks - kb0 > 0 ? p.k_blocks - kb0 : 0) : kper;  // this block's k blocks
+  const int my_units = p.num_units > cid ? (p.num_units - 1 - cid) / ncl + 1 : 0;
+  const int total_it = my_units * nkb;
   const int half_rows = p.act ? p.N / 2 : 0;
 
   if (threadIdx.x == 0) {
@@ -89,49 +177,63 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], LS_CONSUMER_WARPS);
     }
+    mbar_init(&peer_bar, 64 * (p.ksplit > 1 ? p.ksplit - 1 : 1));  // every lane of the peers' two finishing warps
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  if (p.ksplit > 1) ls_cluster_sync_all();  // the peers' barriers exist before anyone arrives at them
 
   if (warp == LS_CONSUMER_WARPS) {
     // ---- producer ---------------------------------------------------------------------------------
-    if (lane == 0) {
-      // weight rows of unit u: plain, 32 consecutive rows; with an activation 16 gate rows and the 16 up rows
-      // of the same columns
+    // K a multiple of 64: lane 0 brings a stage with one copy per matrix (three-dimensional boxes).  Otherwise
+    // lanes 0 to 3 each bring one 64-wide k quarter with two-dimensional boxes, whose ragged last columns read
+    // as zeros.  A stage: weight rows of unit u (plain: 32 consecutive rows; with an activation 16 gate rows
+    // and the 16 up rows of the same columns), then the batch rows.
+    const int lanes = p.chunked ? 1 : 4;
+    if (lane < lanes) {
+      const int kc = lane;
       auto issue_w = [&](int it) {
+        const int u = cid + (it / nkb) * ncl;
+        const int kb = kb0 + it % nkb;
         const int s = it % p.stages;
-        const int u = (int)blockIdx.x + (it / p.k_blocks) * (int)gridDim.x;
-        const int kb = it % p.k_blocks;
         unsigned char* st = ring + s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        const int r0 = p.act ? u * 16 : u * 32;
-        const int r1 = p.act ? half_rows + u * 16 : u * 32 + 16;
-#pragma unroll
-        for (int kc = 0; kc < 4; ++kc) {
-          tma_load_2d(st + (0 * 4 + kc) * 2048, &w_map, &full_bar[s], kb * LS_BK + kc * 64, r0);
-          tma_load_2d(st + (1 * 4 + kc) * 2048, &w_map, &full_bar[s], kb * LS_BK + kc * 64, r1);
+        if (lane == 0) mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        if (p.chunked) {
+          if (p.act) {
+            tma_load_3d(st, &w_map, &full_bar[s], 0, u * 16, kb * 4);
+            tma_load_3d(st + 8192, &w_map, &full_bar[s], 0, half_rows + u * 16, kb * 4);
+          } else {
+            tma_load_3d(st, &w32_map, &full_bar[s], 0, u * 32, kb * 4);
+          }
+          return;
+        }
+        __syncwarp(0xf);
+        if (p.act) {
+          tma_load_2d(st + (0 * 4 + kc) * 2048, &w_map, &full_bar[s], kb * LS_BK + kc * 64, u * 16);
+          tma_load_2d(st + (1 * 4 + kc) * 2048, &w_map, &full_bar[s], kb * LS_BK + kc * 64, half_rows + u * 16);
+        } else {
+          tma_load_2d(st + kc * 4096, &w32_map, &full_bar[s], kb * LS_BK + kc * 64, u * 32);
         }
       };
       auto issue_x = [&](int it) {
+        const int kb = kb0 + it % nkb;
         const int s = it % p.stages;
-        const int kb = it % p.k_blocks;
         unsigned char* st = ring + s * STAGE_BYTES + LS_W_STAGE_BYTES;
-#pragma unroll
-        for (int kc = 0; kc < 4; ++kc) tma_load_2d(st + kc * X_BOX_BYTES, &x_map, &full_bar[s], kb * LS_BK + kc * 64, 0);
+        if (p.chunked)
+          tma_load_3d(st, &x_map, &full_bar[s], 0, 0, kb * 4);
+        else
+          tma_load_2d(st + kc * X_BOX_BYTES, &x_map, &full_bar[s], kb * LS_BK + kc * 64, 0);
       };
       const int first = total_it < p.stages ? total_it : p.stages;
       for (int it = 0; it < first; ++it) issue_w(it);  // the weights: before the kernel in front has finished
       pdl_wait();
       for (int it = 0; it < first; ++it) issue_x(it);  // the batch rows: what that kernel wrote
-      bool failed = false;
-      for (int it = first; it < total_it && !failed; ++it) {
-        const int s = it % p.stages;
-        if (!mbar_wait(&empty_bar[s], ((it / p.stages) - 1) & 1)) {
+      for (int it = first; it < total_it; ++it) {
+        if (!mbar_wait(&empty_bar[it % p.stages], ((it / p.stages) - 1) & 1)) {
           ullm_report(p.status, ULLM_STATUS_TIMEOUT, 51, it);
           abort_flag = 1;
-          failed = true;
-          break;
+          break;  // (the four lanes wait on the same barrier: all of them give up or none)
         }
         issue_w(it);
         issue_x(it);
@@ -150,14 +252,14 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_
     const int b_row = (lane & 7) + (lane >> 4) * 8;        // matrices 0, 1: batch rows 0-7 (k 0-7, 8-15); 2, 3: rows 8-15
     const int b_chunk = (lane >> 3) & 1;
     bool failed = false;
-    int it = 0;
     for (int ui = 0; ui < my_units; ++ui) {
       float acc[NT][4];
 #pragma unroll
       for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int it = ui * nkb + kb;
         const int s = it % p.stages;
         if (!failed && !mbar_wait(&full_bar[s], (it / p.stages) & 1)) {
           ullm_report(p.status, ULLM_STATUS_TIMEOUT, 52, it);
@@ -165,35 +267,69 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_
           failed = true;
         }
         if (!failed) {
-          const uint32_t wbox = lin_smem(ring + s * STAGE_BYTES + (mt * 4 + kq) * 2048);
+          const uint32_t wbox = lin_smem(ring + s * STAGE_BYTES + (p.act ? (mt * 4 + kq) * 2048 : kq * 4096 + mt * 2048));
           const uint32_t xbox = lin_smem(ring + s * STAGE_BYTES + LS_W_STAGE_BYTES + kq * X_BOX_BYTES);
+          // the quarter's fragments first, then the tensor instructions: the stage goes back as soon as it is read
+          uint32_t a[4][4], b[4][NT * 2];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {  // k16 steps of the 64-wide quarter
-            uint32_t a[4];
-            ls_ldmatrix4(a, wbox + a_row * 128 + (((j * 2 + a_chunk) ^ (a_row & 7)) << 4));
+            ls_ldmatrix4(a[j], wbox + a_row * 128 + (((j * 2 + a_chunk) ^ (a_row & 7)) << 4));
             if (NT == 1) {
-              uint32_t b0, b1;
               const int r = lane & 7, c = (lane >> 3) & 1;
-              ls_ldmatrix2(b0, b1, xbox + r * 128 + (((j * 2 + c) ^ r) << 4));
-              ls_mma(acc[0], a, b0, b1);
+              ls_ldmatrix2(b[j][0], b[j][1], xbox + r * 128 + (((j * 2 + c) ^ r) << 4));
             } else {
 #pragma unroll
               for (int n2 = 0; n2 < NT / 2; ++n2) {
-                uint32_t b[4];
+                uint32_t t4[4];
                 const int r = b_row + n2 * 16;
-                ls_ldmatrix4(b, xbox + r * 128 + (((j * 2 + b_chunk) ^ (r & 7)) << 4));
-                ls_mma(acc[n2 * 2], a, b[0], b[1]);
-                ls_mma(acc[n2 * 2 + 1], a, b[2], b[3]);
+                ls_ldmatrix4(t4, xbox + r * 128 + (((j * 2 + b_chunk) ^ (r & 7)) << 4));
+                b[j][n2 * 4] = t4[0], b[j][n2 * 4 + 1] = t4[1], b[j][n2 * 4 + 2] = t4[2], b[j][n2 * 4 + 3] = t4[3];
               }
             }
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[s]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int n = 0; n < NT; ++n) ls_mma(acc[n], a[j], b[j][n * 2], b[j][n * 2 + 1]);
+        } else {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[s]);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);
       }
       // ---- the four k quarters of each half meet (two batch tiles per pass); warps 0 and 1 (quarter 0)
       // finish the unit --------------------------------------------------------------------------------
-      const int u = (int)blockIdx.x + ui * (int)gridDim.x;
+      const int u = cid + ui * ncl;
+      // the end of an output element: bias, activation, residual, one rounding, the store
+      auto finish = [&](int n_tile, const float (&v)[4], const float (&up)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          // accumulator element i: weight row g + 8 (i >> 1), batch row 8 n_tile + 2 t + (i & 1)
+          const int row = g + 8 * (i >> 1);
+          const int m = n_tile * 8 + 2 * t + (i & 1);
+          const int col = p.act ? u * 16 + row : u * 32 + mt * 16 + row;  // column of out
+          if (m >= p.M || col >= p.n_out) continue;
+          float r = v[i];
+          if (p.act) {
+            float gate = r, upv = up[i];
+            if (p.bias != nullptr) {
+              gate += __bfloat162float(p.bias[col]);
+              upv += __bfloat162float(p.bias[half_rows + col]);
+            }
+            r = (p.act == 1 ? act_silu(gate) : act_gelu_tanh(gate)) * upv;
+          } else if (p.bias != nullptr) {
+            r += __bfloat162float(p.bias[col]);
+          }
+          const size_t o = (size_t)m * p.n_out + col;
+          if (p.residual != nullptr) r += __bfloat162float(p.residual[o]);
+          if (p.out_f32)
+            reinterpret_cast<float*>(p.out)[o] = r;
+          else
+            reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(r);
+        }
+      };
+      float v_all[NT][4];  // (clusters) this block's sums of the unit, kept until the peers' have arrived
 #pragma unroll
       for (int n0 = 0; n0 < NT; n0 += NP) {
 #pragma unroll
@@ -201,7 +337,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_
           *reinterpret_cast<float4*>(red + ((size_t)(warp * 32 + lane) * NP + n) * 4) =
               make_float4(acc[n0 + n][0], acc[n0 + n][1], acc[n0 + n][2], acc[n0 + n][3]);
         ls_bar_sync_consumers();
-        if (!failed && kq == 0 && (p.act == 0 || mt == 0)) {
+        if (kq == 0 && (p.act == 0 || mt == 0)) {
 #pragma unroll
           for (int n = 0; n < NP; ++n) {
             float v[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
@@ -214,34 +350,45 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_
                 up[0] += pu.x, up[1] += pu.y, up[2] += pu.z, up[3] += pu.w;
               }
             }
+            if (p.ksplit == 1) {
+              if (!failed) finish(n0 + n, v, up);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              // accumulator element i: weight row g + 8 (i >> 1), batch row 8 (n0 + n) + 2 t + (i & 1)
-              const int row = g + 8 * (i >> 1);
-              const int m = (n0 + n) * 8 + 2 * t + (i & 1);
-              const int col = p.act ? u * 16 + row : u * 32 + mt * 16 + row;  // column of out
-              if (m >= p.M || col >= p.n_out) continue;
-              float r = v[i];
-              if (p.act) {
-                float gate = r, upv = up[i];
-                if (p.bias != nullptr) {
-                  gate += __bfloat162float(p.bias[col]);
-                  upv += __bfloat162float(p.bias[half_rows + col]);
-                }
-                r = (p.act == 1 ? act_silu(gate) : act_gelu_tanh(gate)) * upv;
-              } else if (p.bias != nullptr) {
-                r += __bfloat162float(p.bias[col]);
-              }
-              const size_t o = (size_t)m * p.n_out + col;
-              if (p.residual != nullptr) r += __bfloat162float(p.residual[o]);
-              if (p.out_f32)
-                reinterpret_cast<float*>(p.out)[o] = r;
-              else
-                reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(r);
+              for (int i = 0; i < 4; ++i) v_all[n0 + n][i] = v[i];
             }
           }
         }
         ls_bar_sync_consumers();  // the partial sums are read: the next pass may overwrite them
+      }
+      if (p.ksplit > 1 && kq == 0) {
+        // ---- the blocks of the cluster meet: ranks 1.. put their sums into rank 0's buffer (distributed shared
+        // memory) and arrive at its barrier; rank 0 adds them in rank order and finishes the unit.  (The host
+        // gives a cluster at most one unit, so the buffer is written once.)
+        float* xbuf = red + LS_CONSUMER_WARPS * 32 * NP * 4;  // [ksplit - 1][2 halves][32 lanes][NT][4]
+        if (rank > 0) {
+          const uint32_t dst = ls_map_to_rank(lin_smem(xbuf + ((size_t)((rank - 1) * 2 + mt) * 32 + lane) * NT * 4), 0);
+#pragma unroll
+          for (int n = 0; n < NT; ++n)
+            ls_st_cluster_f4(dst + n * 16, make_float4(v_all[n][0], v_all[n][1], v_all[n][2], v_all[n][3]));
+          ls_arrive_cluster(ls_map_to_rank(lin_smem(&peer_bar), 0));
+        } else {
+          if (!failed && !ls_wait_cluster(&peer_bar, ui & 1)) {
+            ullm_report(p.status, ULLM_STATUS_TIMEOUT, 53, ui);
+            abort_flag = 1;
+            failed = true;
+          }
+          if (!failed) {
+            const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+              for (int r = 1; r < p.ksplit; ++r) {
+                const float4 pv = *reinterpret_cast<const float4*>(xbuf + (((size_t)((r - 1) * 2 + mt) * 32 + lane) * NT + n) * 4);
+                v_all[n][0] += pv.x, v_all[n][1] += pv.y, v_all[n][2] += pv.z, v_all[n][3] += pv.w;
+              }
+              finish(n, v_all[n], zero);
+            }
+          }
+        }
       }
     }
   }
@@ -249,45 +396,81 @@ __global__ void __launch_bounds__(LS_THREADS) linear_stream_kernel(const __grid_
   if (abort_flag && threadIdx.x == 0) {
     // a wait ran out: copies may still be on their way into the ring; wait (bounded) for the last phase of
     // every stage before the block gives its shared memory back
-    const int issued = total_it;
     for (int s = 0; s < p.stages; ++s) {
       int last = -1;
-      for (int it = s; it < issued; it += p.stages) last = it;
+      for (int it = s; it < total_it; it += p.stages) last = it;
       if (last >= 0) mbar_wait(&full_bar[s], (last / p.stages) & 1);
     }
   }
+  if (p.ksplit > 1) ls_cluster_sync_all();  // no block leaves while a peer may still write to it or arrive at its barrier
 }
 
 static int g_ls_sms = 0;
 static int g_ls_attr[3] = {0, 0, 0};
-static int g_ls_blocks_per_sm = 1;  // blocks the launcher aims for per SM (1 leaves room for the next kernel's blocks)
+static int g_ls_blocks_per_sm = 2;  // blocks the launcher aims for per SM
+static int g_ls_smem_kb = 108;      // shared memory a block may take (ring + partial sums): two blocks per SM
 
 extern "C" void ullm_linear_stream_blocks_per_sm(int n) { g_ls_blocks_per_sm = n < 1 ? 1 : (n > 2 ? 2 : n); }
+extern "C" void ullm_linear_stream_smem_kb(int kb) { g_ls_smem_kb = kb < 72 ? 72 : (kb > 224 ? 224 : kb); }
 
 extern "C" int ullm_linear_stream_supported(int M, int N, int K) {
   return M >= 1 && M <= 32 && N >= 1 && K >= 8 && K % 8 == 0;
 }
 
+static int g_ls_ksplit_max = 8;  // 1 switches the clusters off (measurements compare)
+extern "C" void ullm_linear_stream_ksplit_max(int n) { g_ls_ksplit_max = n < 1 ? 1 : (n > 8 ? 8 : n); }
+
 template <int NT>
-static int ls_launch(int which, const CUtensorMap& wm, const CUtensorMap& xm, LsParams p, cudaStream_t st) {
+static int ls_launch(int which, const CUtensorMap& wm, const CUtensorMap& wm32, const CUtensorMap& xm, LsParams p,
+                     cudaStream_t st) {
   constexpr int STAGE_BYTES = LS_W_STAGE_BYTES + 4 * 8 * NT * 128;
+  const int slots = g_ls_sms * g_ls_blocks_per_sm;
+  // Few units (a narrow output): the blocks of a cluster share a unit, each with a range of K, so that every SM
+  // has something to stream.  Only plain products (no activation), one unit per cluster, at least two k blocks
+  // per block.
+  int ksplit = 1;
+  if (p.act == 0)
+    while (ksplit * 2 <= g_ls_ksplit_max && p.num_units * ksplit * 2 <= slots && p.k_blocks >= ksplit * 4) ksplit *= 2;
+  p.ksplit = ksplit;
   const int red_bytes = LS_CONSUMER_WARPS * 32 * (NT > 1 ? 2 : 1) * 4 * (int)sizeof(float);
-  int stages = (LS_MAX_SMEM - 1024 - red_bytes) / STAGE_BYTES;
-  if (stages > 8) stages = 8;
+  const int xbuf_bytes = (ksplit - 1) * 2 * 32 * NT * 4 * (int)sizeof(float);
+  int stages = (g_ls_smem_kb * 1024 - 1024 - red_bytes - xbuf_bytes) / STAGE_BYTES;
+  if (stages > LS_MAX_STAGES) stages = LS_MAX_STAGES;
   if (stages < 2) return ULLM_ERR_UNSUPPORTED;
   p.stages = stages;
-  const size_t smem = (size_t)stages * STAGE_BYTES + red_bytes + 1024;
+  const size_t smem = (size_t)stages * STAGE_BYTES + red_bytes + xbuf_bytes + 1024;
   if (!g_ls_attr[which]) {
-    if (cudaFuncSetAttribute(linear_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, LS_MAX_SMEM) !=
+    if (cudaFuncSetAttribute(linear_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) !=
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
     cudaFuncSetAttribute(linear_stream_kernel<NT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     g_ls_attr[which] = 1;
   }
-  int grid = g_ls_sms * g_ls_blocks_per_sm;
-  if (grid > p.num_units) grid = p.num_units;
-  return ullm_launch_kernel(linear_stream_kernel<NT>, dim3(grid), dim3(LS_THREADS), smem, st, wm, xm, p);
+  if (ksplit == 1) {
+    int grid = slots;
+    if (grid > p.num_units) grid = p.num_units;
+    return ullm_launch_kernel(linear_stream_kernel<NT>, dim3(grid), dim3(LS_THREADS), smem, st, wm, wm32, xm, p);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.num_units * ksplit);
+  cfg.blockDim = dim3(LS_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)ksplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_ullm_pdl ? 2 : 1;
+  if (cudaLaunchKernelEx(&cfg, linear_stream_kernel<NT>, wm, wm32, xm, p) != cudaSuccess) {
+    cudaGetLastError();
+    return ULLM_ERR_LAUNCH;
+  }
+  return ULLM_OK;
 }
 
 // act: 0 none, 1 silu gate, 2 gelu_tanh gate (weight = [gate rows; up rows], out [M, N / 2]).
@@ -303,9 +486,16 @@ extern "C" int ullm_linear_stream(const void* x, const void* w, const void* bias
       return ULLM_ERR_LAUNCH;
   }
   const int NT = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-  CUtensorMap wm, xm;
+  CUtensorMap wm, wm32, xm;
+  const int chunked = K % 64 == 0;
   // x as a matrix of exactly M rows: boxes of 8 NT rows read zeros past them
-  if (!get_map(w, N, K, 16, &wm) || !get_map(x, M, K, 8 * NT, &xm)) return ULLM_ERR_LAUNCH;
+  if (chunked) {
+    if (!ls_chunked_map(w, N, K, 16, &wm) || !ls_chunked_map(w, N, K, 32, &wm32) ||
+        !ls_chunked_map(x, M, K, 8 * NT, &xm))
+      return ULLM_ERR_LAUNCH;
+  } else if (!get_map(w, N, K, 16, &wm) || !get_map(w, N, K, 32, &wm32) || !get_map(x, M, K, 8 * NT, &xm)) {
+    return ULLM_ERR_LAUNCH;
+  }
   LsParams p;
   p.bias = (const __nv_bfloat16*)bias;
   p.residual = (const __nv_bfloat16*)residual;
@@ -317,8 +507,10 @@ extern "C" int ullm_linear_stream(const void* x, const void* w, const void* bias
   p.num_units = act ? (N / 2 + 15) / 16 : (N + 31) / 32;
   p.k_blocks = (K + LS_BK - 1) / LS_BK;
   p.stages = 0;
+  p.chunked = chunked;
+  p.ksplit = 1;
   p.status = status;
-  if (NT == 1) return ls_launch<1>(0, wm, xm, p, (cudaStream_t)stream);
-  if (NT == 2) return ls_launch<2>(1, wm, xm, p, (cudaStream_t)stream);
-  return ls_launch<4>(2, wm, xm, p, (cudaStream_t)stream);
+  if (NT == 1) return ls_launch<1>(0, wm, wm32, xm, p, (cudaStream_t)stream);
+  if (NT == 2) return ls_launch<2>(1, wm, wm32, xm, p, (cudaStream_t)stream);
+  return ls_launch<4>(2, wm, wm32, xm, p, (cudaStream_t)stream);
 }

@@ -227,6 +227,10 @@ class Kernels:
         L.ullm_linear_stream_supported.restype = c_int
         L.ullm_linear_stream_blocks_per_sm.argtypes = [I]
         L.ullm_linear_stream_blocks_per_sm.restype = None
+        L.ullm_linear_stream_smem_kb.argtypes = [I]
+        L.ullm_linear_stream_smem_kb.restype = None
+        L.ullm_linear_stream_ksplit_max.argtypes = [I]
+        L.ullm_linear_stream_ksplit_max.restype = None
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
