@@ -104,6 +104,9 @@ class StepProfiler:
             torch.cuda.synchronize()
             groups = self.timer.totals() if self.timer is not None else {}
         self._close_open()
+        for rec in self.steps:
+            rec.pop("t0", None)
+            rec.pop("_e0", None)
         report = {"steps": self.steps, "by_kind": self.summary(), "kernel_groups": groups}
         os.makedirs(self.profile_dir, exist_ok=True)
         path = os.path.join(self.profile_dir, f"ullm_b200_engine_{os.getpid()}.json")
@@ -134,7 +137,9 @@ class StepProfiler:
         self._open.append((rec, rec.pop("_e0"), e1))
 
     def step_read(self, rec: dict) -> None:
-        rec["host_ms"] = round((time.perf_counter() - rec.pop("t0")) * 1e3, 4)
+        t0 = rec.pop("t0", None)
+        if t0 is not None:
+            rec["host_ms"] = round((time.perf_counter() - t0) * 1e3, 4)
         self._close_open()
 
     def _close_open(self) -> None:
@@ -145,8 +150,7 @@ class StepProfiler:
                 continue
             if e1 is not None:
                 rec["device_ms"] = round(e0.elapsed_time(e1), 4)
-            rec.pop("t0", None)
-            self.steps.append(rec)
+            self.steps.append(rec)  # (its host time is filled in when its tokens are read)
         self._open = still
         if not self.started:  # stopping: wait for the rest
             for rec, e0, e1 in self._open:
