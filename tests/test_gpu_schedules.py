@@ -334,3 +334,59 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_kernel_runs():
         torch.cuda.synchronize()
         assert torch.allclose(c.float(), a.float() @ b.float().t(), atol=0.5, rtol=2e-2)
     K.raise_on_status()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# every environment switch: generation with it set still follows the plain implementation
+# ---------------------------------------------------------------------------------------------------------
+SWITCH_SETTINGS = [
+    {"ULLM_B200_PDL": "1"}, {"ULLM_B200_SMALL_M_LINEAR": "0"}, {"ULLM_B200_SMALL_M_LINEAR": "stream"},
+    {"ULLM_B200_SMALL_M_LINEAR": "skinny"}, {"ULLM_B200_SMALL_M_LINEAR": "tcgen05"},
+    {"ULLM_B200_SMALL_M_LINEAR": "stream", "ULLM_B200_PDL": "1"}, {"ULLM_B200_STREAM_WEIGHT_MB": "0"},
+    {"ULLM_B200_DECODE_TC": "1"}, {"ULLM_B200_DECODE_CLUSTER": "1"}, {"ULLM_B200_DECODE_CLUSTER": "0"},
+    {"ULLM_B200_FUSE_DECODE_ROPE": "0"}, {"ULLM_B200_TC_ATTN": "0"}, {"ULLM_B200_DECODE_BALANCED": "1"},
+    {"ULLM_B200_DECODE_BALANCED": "0"}, {"ULLM_B200_MIXED_DECODE_ROWS": "0"}, {"ULLM_B200_LT_ROWS": "0"},
+    {"ULLM_B200_FUSED_MLP_ROWS": "1"}, {"ULLM_B200_DECODE_SPLIT_TARGET": "37"}, {"ULLM_B200_MIN_GRAPH_BATCH": "4"},
+]
+
+
+@pytest.mark.needs_cuda
+@pytest.mark.parametrize("switches", SWITCH_SETTINGS, ids=lambda d: ",".join(f"{k[10:]}={v}" for k, v in d.items()))
+def test_generation_under_each_switch_follows_the_plain_logits(tmp_path, monkeypatch, switches):
+    """Every optional switch, set as the environment would set it: three requests (one much longer, so that even,
+    ragged and mixed steps occur; prompts in portions of 64) on a two-layer bfloat16 model with head size 128,
+    CUDA graphs on; every chosen token's plain logit is within the bfloat16 tolerance of the plain maximum."""
+    import os
+
+    from ullm_b200 import LLM, EngineConfig, SamplingParams
+    from ullm_b200.csrc import kernels
+
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 256,
+           "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 384,
+           "vocab_size": 1031, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False,
+           "tie_word_embeddings": False, "max_position_embeddings": 512, "torch_dtype": "bfloat16"}
+    w = {n: t.to(torch.bfloat16) for n, t in pm.random_weights(cfg, seed=19, std=0.04, norm_std=0.1).items()}
+    d = write_model_dir(str(tmp_path / "switch_model"), cfg, w)
+    for k, v in switches.items():
+        monkeypatch.setenv(k, v)
+    K = kernels()
+    try:
+        K.apply_switches(os.environ)
+        llm = LLM(EngineConfig(model=d, max_bs=4, context_len=512, page_size=16, num_pages=64,
+                               max_num_batched_tokens=64, dtype="bfloat16", log_level="warning"))
+        prompts = [random_ids(cfg["vocab_size"], n, 50 + n) for n in (200, 40, 9, 70)]
+        n_new = [6, 12, 12, 9]
+        outs = llm.generate_batch(prompts, [SamplingParams(temperature=0.0, max_new_tokens=n, ignore_eos=True)
+                                            for n in n_new])
+        K.raise_on_status()
+    finally:
+        monkeypatch.undo()
+        K.apply_switches(os.environ)
+    wf = {k: v.float() for k, v in w.items()}
+    for p, o, n in zip(prompts, outs, n_new):
+        assert len(o.token_ids) == n
+        lg = pm.forward_logits(p + o.token_ids, wf, cfg)
+        scale = lg.abs().max().item()
+        for i, tok in enumerate(o.token_ids):
+            row = lg[len(p) - 1 + i]
+            assert row.max().item() - row[tok].item() <= 2 * TOL["bfloat16"] * scale, f"prompt {len(p)}, token {i}"

@@ -103,15 +103,10 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 extern int g_ullm_pdl;
-extern int g_ullm_max_smem_carveout;
-// Defined in elementwise.cu: asks, once per kernel, for the largest shared-memory carve-out, so that SMs are not
-// reconfigured between kernels of this library that want different splits of the L1 / shared memory.
-void ullm_prefer_max_smem(const void* kernel);
 
 template <typename... KArgs, typename... Args>
 static inline int ullm_launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                      Args... args) {
-  if (g_ullm_max_smem_carveout) ullm_prefer_max_smem(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -3,23 +3,10 @@
 // moved in 16-byte pieces are, others go element by element.
 #include "common.cuh"
 
-#include <cstdlib>
-#include <mutex>
 #include <type_traits>
-#include <unordered_set>
 
 int g_ullm_pdl = 0;
 extern "C" void ullm_set_pdl(int on) { g_ullm_pdl = on ? 1 : 0; }
-
-int g_ullm_max_smem_carveout = 0;
-extern "C" void ullm_set_max_smem_carveout(int on) { g_ullm_max_smem_carveout = on ? 1 : 0; }
-void ullm_prefer_max_smem(const void* kernel) {
-  static std::unordered_set<const void*> done;
-  static std::mutex m;
-  std::lock_guard<std::mutex> lock(m);
-  if (done.insert(kernel).second)
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-}
 
 // ---------------------------------------------------------------------------
 // row copies: out[r, :] = src[index[r], :]

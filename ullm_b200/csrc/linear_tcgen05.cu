@@ -408,14 +408,9 @@ extern "C" int ullm_linear_tcgen05(const void* x, const void* w, const void* bia
     return ULLM_ERR_UNSUPPORTED;
   const int stage_bytes = 2 * LIN_A_HALF + 2 * p.m_pad * 128;
   const int xchg_bytes = act != 0 ? p.m_pad * 64 * 4 : 0;
-  // Stages: the ring is what a block holds in flight, and what it has prefetched while it waits for
-  // the kernel before it.  ULLM_B200_LIN_SMEM_KB bounds a block's shared memory (default 224 KB).
-  static int ring_kb = 0;
-  if (ring_kb == 0) {
-    const char* e = getenv("ULLM_B200_LIN_SMEM_KB");
-    ring_kb = e != nullptr ? atoi(e) : 224;
-    if (ring_kb < 64 || ring_kb > 224) ring_kb = 224;
-  }
+  // Stages: the ring is what a block holds in flight, and what it has prefetched while it waits for the kernel
+  // before it: all the shared memory a block can have.
+  const int ring_kb = 224;
   int stages = (ring_kb * 1024 - 1024 - xchg_bytes) / stage_bytes;
   const long long per_block = (p.units + blocks - 1) / blocks;
   if (stages > per_block) stages = per_block < 2 ? 2 : (int)per_block;

@@ -106,46 +106,8 @@ class Kernels:
         self._lin_ws = None  # partial sums and tile counters of the tcgen05 product, made at its first use
         self._lin_counters = None
         self.pdl = False
-        if os.environ.get("ULLM_B200_PDL", "0") == "1":
-            self.set_pdl(True)
-        if os.environ.get("ULLM_B200_MAX_SMEM_CARVEOUT", "0") == "1":
-            self.lib.ullm_set_max_smem_carveout(1)
-        self.decode_split_target = int(os.environ.get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
-        self.use_tcgen05_attention = os.environ.get("ULLM_B200_TC_ATTN", "1") == "1"
-        # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
-        # scratch arrays and a second kernel
-        # ("auto": for one or two requests, where it measured 1.5 % faster per step; at eight requests it is 1.5 %
-        # slower than the merge kernel)
-        mode = os.environ.get("ULLM_B200_DECODE_CLUSTER", "auto")
-        self.decode_cluster_merge = {"1": True, "0": False}.get(mode, "auto")
-        # decode steps: the per-request decode attention kernel applies the q/k norm and the rotation and writes the
-        # new key and value itself (one launch less per layer)
-        self.fuse_decode_rope = os.environ.get("ULLM_B200_FUSE_DECODE_ROPE", "1") == "1"
-        # a mixed step's leading one-token entries go to the decode attention kernel from this many on (0: never)
-        self.mixed_decode_rows = int(os.environ.get("ULLM_B200_MIXED_DECODE_ROWS", "4"))
-        # decode attention on the tcgen05 tensor cores (head size 128), the batch's keys cut evenly over the blocks
-        self.use_tcgen05_decode = os.environ.get("ULLM_B200_DECODE_TC", "0") == "1"
-        # decode attention: the batch's keys cut evenly over the warps (True), every request split alike (False),
-        # or "auto": the first for batches of very unequal lengths (the step context says so), else the second
-        mode = os.environ.get("ULLM_B200_DECODE_BALANCED", "auto")
-        self.use_balanced_decode = {"1": True, "0": False}.get(mode, "auto")
         self._decb = {}  # (head_dim, heads per kv head) -> (partials, prefix) of the balanced decode attention
-        # few-row products: "auto" (the default) the weight-streaming TMA kernel for small weights, where a step is
-        # bound by launches and start-up and not by memory (measured at Qwen3-0.6B sizes: a decode step of 4 to 16
-        # requests 6 to 17 % faster), the library otherwise; "0" always the library; "stream" that kernel always
-        # (M <= 32), "skinny" the mma.sync streaming kernel (M <= 32), "tcgen05" (or "1") the stream-K tcgen05
-        # kernel (M <= 64)
-        mode = os.environ.get("ULLM_B200_SMALL_M_LINEAR", "auto")
-        self.small_m_mode = {"1": "tcgen05", "0": None, "": "auto"}.get(mode, mode)
-        if self.small_m_mode not in (None, "auto", "tcgen05", "skinny", "stream"):
-            raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: auto, 0, stream, skinny or tcgen05")
-        self.stream_weight_bytes = int(os.environ.get("ULLM_B200_STREAM_WEIGHT_MB", "16")) << 20
-        self.stream_rows = int(os.environ.get("ULLM_B200_STREAM_ROWS", "32"))  # rows up to which "stream" applies
-        # rows from which the gated feed-forward's first product runs on the own tcgen05 kernel with the activation
-        # fused (0 rows would mean always; a huge number never)
-        self.fused_mlp_rows = int(os.environ.get("ULLM_B200_FUSED_MLP_ROWS", "4096"))
-        # rows up to which the library's product is called through cuBLASLt with a timed choice of algorithm
-        self.lt_rows = int(os.environ.get("ULLM_B200_LT_ROWS", str(1 << 30)))
+        self.apply_switches(os.environ)
         self._lt_ok = None
         self._lt_ws = None
         self._lt_tuned = set()
@@ -155,6 +117,57 @@ class Kernels:
         self.skip_groups: frozenset = frozenset()
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
+
+    # -- switches -----------------------------------------------------------
+    SWITCHES = ("ULLM_B200_PDL", "ULLM_B200_DECODE_SPLIT_TARGET", "ULLM_B200_TC_ATTN", "ULLM_B200_DECODE_CLUSTER",
+                "ULLM_B200_FUSE_DECODE_ROPE", "ULLM_B200_MIXED_DECODE_ROWS", "ULLM_B200_DECODE_TC",
+                "ULLM_B200_DECODE_BALANCED", "ULLM_B200_SMALL_M_LINEAR", "ULLM_B200_STREAM_WEIGHT_MB",
+                "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS")
+
+    def apply_switches(self, env) -> None:
+        """Sets every kernel choice from `env` (a mapping; the process environment at start-up): a switch that is
+        not in it takes its default.  All switches are optional; the defaults are what was measured fastest."""
+        get = env.get
+        # programmatic dependent launch for every kernel of the library (about + 1 % at Qwen3-0.6B sizes with the
+        # stream product, - 1 to 2 % at Qwen3-8B sizes with the library's products in between)
+        self.set_pdl(get("ULLM_B200_PDL", "0") == "1")
+        # blocks the per-request decode attention aims for when it splits the requests' key ranges
+        self.decode_split_target = int(get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
+        # prompt attention on the tcgen05 tensor cores (head size 128); 0: the mma.sync kernel
+        self.use_tcgen05_attention = get("ULLM_B200_TC_ATTN", "1") == "1"
+        # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
+        # scratch arrays and a second kernel
+        # ("auto": for one or two requests, where it measured 1.5 % faster per step; at eight requests it is 1.5 %
+        # slower than the merge kernel)
+        mode = get("ULLM_B200_DECODE_CLUSTER", "auto")
+        self.decode_cluster_merge = {"1": True, "0": False}.get(mode, "auto")
+        # decode steps: the per-request decode attention kernel applies the q/k norm and the rotation and writes the
+        # new key and value itself (one launch less per layer)
+        self.fuse_decode_rope = get("ULLM_B200_FUSE_DECODE_ROPE", "1") == "1"
+        # a mixed step's leading one-token entries go to the decode attention kernel from this many on (0: never)
+        self.mixed_decode_rows = int(get("ULLM_B200_MIXED_DECODE_ROWS", "4"))
+        # decode attention on the tcgen05 tensor cores (head size 128), the batch's keys cut evenly over the blocks
+        self.use_tcgen05_decode = get("ULLM_B200_DECODE_TC", "0") == "1"
+        # decode attention: the batch's keys cut evenly over the warps (True), every request split alike (False),
+        # or "auto": the first for batches of very unequal lengths (the mixer says so), else the second
+        mode = get("ULLM_B200_DECODE_BALANCED", "auto")
+        self.use_balanced_decode = {"1": True, "0": False}.get(mode, "auto")
+        # few-row products: "auto" (the default) the weight-streaming TMA kernel for small weights, where a step is
+        # bound by launches and start-up and not by memory (measured at Qwen3-0.6B sizes: a decode step of 4 to 16
+        # requests 6 to 17 % faster), the library otherwise; "0" always the library; "stream" that kernel always
+        # (M <= 32), "skinny" the mma.sync streaming kernel (M <= 32), "tcgen05" (or "1") the stream-K tcgen05
+        # kernel (M <= 64)
+        mode = get("ULLM_B200_SMALL_M_LINEAR", "auto")
+        self.small_m_mode = {"1": "tcgen05", "0": None, "": "auto"}.get(mode, mode)
+        if self.small_m_mode not in (None, "auto", "tcgen05", "skinny", "stream"):
+            raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: auto, 0, stream, skinny or tcgen05")
+        self.stream_weight_bytes = int(get("ULLM_B200_STREAM_WEIGHT_MB", "16")) << 20  # "auto": weights up to this
+        self.stream_rows = 32  # rows the stream product takes
+        # rows from which the gated feed-forward's first product runs on the own tcgen05 kernel with the activation
+        # fused (0 rows would mean always; a huge number never)
+        self.fused_mlp_rows = int(get("ULLM_B200_FUSED_MLP_ROWS", "4096"))
+        # rows up to which the library's product is called through cuBLASLt with a timed choice of algorithm
+        self.lt_rows = int(get("ULLM_B200_LT_ROWS", str(1 << 30)))
 
     # -- ctypes signatures --------------------------------------------------
     def _declare(self) -> None:
@@ -218,8 +231,6 @@ class Kernels:
         L.ullm_prefill_attention_tcgen05_blocks_per_sm.restype = c_int
         L.ullm_set_pdl.argtypes = [I]
         L.ullm_set_pdl.restype = None
-        L.ullm_set_max_smem_carveout.argtypes = [I]
-        L.ullm_set_max_smem_carveout.restype = None
         L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
         L.ullm_linear_tcgen05_supported.restype = c_int
         L.ullm_linear_tcgen05_blocks.restype = c_int
