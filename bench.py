@@ -908,9 +908,11 @@ def run_reference_serve(args) -> dict:
                 await llm.shutdown()
 
             asyncio.run(main_async())
-            if done != outs:
+            # (the reference hands back one token fewer than max_new_tokens for most requests; what counts is what
+            # came back)
+            if any(d < n - 1 or d > n for d, n in zip(done, outs)):
                 raise RuntimeError(f"{sum(done)} tokens came back, {sum(outs)} were asked for")
-            gen, pro, dt = sum(outs), sum(len(p) for p in prompts), result["s"]
+            gen, pro, dt = sum(done), sum(len(p) for p in prompts), result["s"]
             config = common_config(label, shape, layers, SERVE_REQUESTS)
             config.update({"requests": SERVE_REQUESTS, "prompt_tokens": pro, "generated_tokens": gen,
                            "lengths": f"uniform {SERVE_MIN}..{SERVE_MAX}, seed {SERVE_SEED}", "temperature": 0.6,

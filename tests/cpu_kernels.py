@@ -70,6 +70,9 @@ class CpuKernels:
         a = g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")
         out.copy_((a * u).to(out.dtype))
 
+    def layer_tail_applies(self, *args, **kwargs):
+        return False
+
     def decode_fusion_applies(self, *args, **kwargs):
         return False  # the stand-in always prepares q and k in a step of their own
 

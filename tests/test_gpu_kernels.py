@@ -632,6 +632,47 @@ def test_stream_linear_is_deterministic_and_refuses_what_it_does_not_take():
                                  torch.empty(4, 128, dtype=torch.bfloat16, device="cuda"))
 
 
+@pytest.mark.parametrize("M,H,QD,I,act", [
+    (8, 256, 256, 256, 0), (16, 512, 768, 1024, 0), (3, 4096, 4096, 12288, 0), (16, 1024, 2048, 3072, 1),
+    (1, 256, 512, 256, 0), (11, 768, 256, 512, 1), (16, 5120, 8192, 25600, 0),
+])
+def test_fused_layer_tail(M, H, QD, I, act):
+    """The second half of a decoder layer in one cooperative kernel (output projection + residual, RMSNorm, gated
+    feed-forward, down projection + residual) against the same chain in float32 with the roundings of the separate
+    kernels: row counts that fill one and two batch tiles, phases with and without split units, several items
+    per block, three launches in a row on the same counters (tickets and grid barriers must come back), and the
+    same bits every time."""
+    if not K().layer_tail_applies(M, torch.bfloat16, H, QD, I):
+        pytest.skip("the fused layer tail is switched off")
+    bf = torch.bfloat16
+    attn = rnd(M, QD, seed=200, dtype=bf)
+    res0 = rnd(M, H, seed=201, dtype=bf)
+    w_o = rnd(H, QD, seed=202, dtype=bf, scale=QD ** -0.5)
+    w_gu = rnd(2 * I, H, seed=203, dtype=bf, scale=H ** -0.5)
+    w_d = rnd(H, I, seed=204, dtype=bf, scale=I ** -0.5)
+    norm_w = (1.0 + 0.1 * rnd(H, seed=205, dtype=torch.float32)).contiguous()
+    eps = 1e-6
+    s1 = res0.float() + attn.float() @ w_o.float().t()
+    r1 = s1.to(bf)
+    h = (s1 * torch.rsqrt(s1.pow(2).mean(-1, keepdim=True) + eps) * norm_w).to(bf)
+    y = h.float() @ w_gu.float().t()
+    g, u = y[:, :I], y[:, I:]
+    a = ((g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u).to(bf)
+    ref = (r1.float() + a.float() @ w_d.float().t()).to(bf).float()
+    outs = []
+    for _ in range(3):
+        res = res0.clone()
+        work = torch.full((M, I), 7.0, dtype=bf, device="cuda")
+        K().fused_layer_tail(attn, res, work, w_o, w_gu, w_d, norm_w, eps, act)
+        K().raise_on_status()
+        err = (res.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+        assert err <= 2e-2, f"residual after the layer: max err {err:.3e} of scale"
+        aerr = (work.float() - a.float()).abs().max().item() / max(a.float().abs().max().item(), 1e-6)
+        assert aerr <= 2e-2, f"activation: max err {aerr:.3e} of scale"
+        outs.append(res)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
 def test_skinny_linear_is_deterministic_and_refuses_what_it_does_not_take():
     x = rnd(16, 4096, seed=70, dtype=torch.bfloat16)
     w = rnd(512, 4096, seed=71, dtype=torch.bfloat16, scale=0.05)

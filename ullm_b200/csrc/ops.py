@@ -107,6 +107,7 @@ class Kernels:
         self._lin_counters = None
         self.pdl = False
         self._decb = {}  # (head_dim, heads per kv head) -> (partials, prefix) of the balanced decode attention
+        self._tail_ws = {}  # hidden size -> (scratch, counters) of the fused layer tail
         self.apply_switches(os.environ)
         self._lt_ok = None
         self._lt_ws = None
@@ -122,7 +123,7 @@ class Kernels:
     SWITCHES = ("ULLM_B200_PDL", "ULLM_B200_DECODE_SPLIT_TARGET", "ULLM_B200_TC_ATTN", "ULLM_B200_DECODE_CLUSTER",
                 "ULLM_B200_FUSE_DECODE_ROPE", "ULLM_B200_MIXED_DECODE_ROWS", "ULLM_B200_DECODE_TC",
                 "ULLM_B200_DECODE_BALANCED", "ULLM_B200_SMALL_M_LINEAR", "ULLM_B200_STREAM_WEIGHT_MB",
-                "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS")
+                "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS", "ULLM_B200_FUSED_TAIL_ROWS")
 
     def apply_switches(self, env) -> None:
         """Sets every kernel choice from `env` (a mapping; the process environment at start-up): a switch that is
@@ -168,6 +169,9 @@ class Kernels:
         self.fused_mlp_rows = int(get("ULLM_B200_FUSED_MLP_ROWS", "4096"))
         # rows up to which the library's product is called through cuBLASLt with a timed choice of algorithm
         self.lt_rows = int(get("ULLM_B200_LT_ROWS", str(1 << 30)))
+        # rows up to which a decode step runs the second half of a layer (output projection, residual, norm, gated
+        # feed-forward, residual) as one kernel; 0: never
+        self.fused_tail_rows = int(get("ULLM_B200_FUSED_TAIL_ROWS", "16"))
 
     # -- ctypes signatures --------------------------------------------------
     def _declare(self) -> None:
@@ -190,6 +194,7 @@ class Kernels:
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_stream": [P, P, P, P, P, I, I, I, I, I, P, P],
+            "ullm_layer_tail_fused": [P, P, P, P, P, P, P, F, I, I, I, I, I, P, P, P, P],
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_lt_linear": [P, P, P, I, I, I, I, P, LL, I, P, LL, P],
@@ -238,6 +243,12 @@ class Kernels:
         L.ullm_linear_tcgen05_large_supported.restype = c_int
         L.ullm_linear_skinny_supported.argtypes = [I, I, I]
         L.ullm_linear_skinny_supported.restype = c_int
+        L.ullm_layer_tail_fused_supported.argtypes = [I, I, I, I]
+        L.ullm_layer_tail_fused_supported.restype = c_int
+        L.ullm_layer_tail_fused_scratch_floats.argtypes = [I]
+        L.ullm_layer_tail_fused_scratch_floats.restype = c_longlong
+        L.ullm_layer_tail_fused_counters.argtypes = [I]
+        L.ullm_layer_tail_fused_counters.restype = c_longlong
         L.ullm_linear_stream_supported.argtypes = [I, I, I]
         L.ullm_linear_stream_supported.restype = c_int
         L.ullm_linear_stream_blocks_per_sm.argtypes = [I]
@@ -269,6 +280,8 @@ class Kernels:
                 self._lin_counters.zero_()  # a product that gave up may have left tiles half counted
             for _part, _prefix, flags in self._decb.values():
                 flags.zero_()  # likewise the merge flags of the balanced decode attention
+            for _scratch, counters in self._tail_ws.values():
+                counters.zero_()  # and the tickets and grid barriers of the fused layer tail
             msg = STATUS_MESSAGES.get(s[0], "status {code}").format(index=s[1], value=s[2], code=s[0])
             raise KernelError(f"a kernel refused an index: {msg}")
 
@@ -351,6 +364,44 @@ class Kernels:
                                                 0 if act is None else act + 1, _ptr(self.status), _stream()),
                     f"linear_stream ({M}x{K} . {N}x{K})")
         return True
+
+    def layer_tail_applies(self, rows: int, dtype, hidden: int, attn_width: int, intermediate: int) -> bool:
+        """True when `fused_layer_tail` takes these sizes and the switch is on: decode-sized batches (at most
+        `fused_tail_rows` rows, never more than 16) in bfloat16."""
+        return bool(self.fused_tail_rows > 0 and rows <= min(self.fused_tail_rows, 16) and dtype == torch.bfloat16
+                    and self.lib.ullm_layer_tail_fused_supported(rows, hidden, attn_width, intermediate))
+
+    @_timed("layer_tail_fused", lambda self_attn, residual, act_out, w_o, w_gate_up, w_down, *r: (
+        w_o.numel() + w_gate_up.numel() + w_down.numel()) * 2)
+    def fused_layer_tail(self, attn, residual, act_out, w_o, w_gate_up, w_down, norm_w, eps: float, act: int = 0):
+        """The second half of a pre-norm decoder layer in one kernel (csrc/layer_tail_fused.cu):
+        residual += attn @ w_o.T;  act_out = act(h @ Wgate.T) * (h @ Wup.T) with h = rmsnorm(residual) * norm_w;
+        residual += act_out @ w_down.T.  `residual` [M, H] is updated in place; `act_out` [M, I] is a work buffer.
+        bfloat16, M <= 16.  Call `layer_tail_applies` first."""
+        M, QD = attn.shape
+        H = residual.shape[1]
+        inter = act_out.shape[1]
+        for t_, n_ in ((attn, "attn"), (residual, "residual"), (act_out, "act_out"), (w_o, "w_o"),
+                       (w_gate_up, "w_gate_up"), (w_down, "w_down")):
+            _need(t_, n_, torch.bfloat16)
+            if t_.data_ptr() % 16:
+                raise KernelError(f"fused_layer_tail: {n_} is not 16-byte aligned")
+        _need(norm_w, "norm_w", torch.float32)
+        if (residual.shape[0] != M or act_out.shape[0] != M or w_o.shape != (H, QD) or w_gate_up.shape != (2 * inter, H)
+                or w_down.shape != (H, inter) or norm_w.numel() != H):
+            raise KernelError(f"fused_layer_tail: attn {tuple(attn.shape)}, residual {tuple(residual.shape)}, act_out "
+                              f"{tuple(act_out.shape)}, w_o {tuple(w_o.shape)}, w_gate_up {tuple(w_gate_up.shape)}, "
+                              f"w_down {tuple(w_down.shape)}")
+        ws = self._tail_ws.get(H)
+        if ws is None:  # scratch of the split units and the zeroed counters, made at the first (eager) call
+            ws = (torch.empty(self.lib.ullm_layer_tail_fused_scratch_floats(H), dtype=torch.float32, device="cuda"),
+                  torch.zeros(self.lib.ullm_layer_tail_fused_counters(H), dtype=torch.int32, device="cuda"))
+            self._tail_ws[H] = ws
+        self._check(self.lib.ullm_layer_tail_fused(
+            _ptr(attn), _ptr(residual), _ptr(act_out), _ptr(w_o), _ptr(w_gate_up), _ptr(w_down), _ptr(norm_w),
+            float(eps), act + 1, M, H, QD, inter, _ptr(ws[0]), _ptr(ws[1]), _ptr(self.status), _stream()),
+            f"layer_tail_fused ({M} rows, hidden {H}, intermediate {inter})")
+        return residual
 
     def large_linear(self, x, weight, out, bias=None, act: int | None = None, variant: int = 0) -> bool:
         """The persistent tcgen05/TMA product for many rows (prompt portions): tiles of 128 x 256, two accumulators

@@ -113,8 +113,11 @@ class PagedAttention(Mixer):
     def _ragged(ctx) -> bool:
         return bool(ctx.decode_only and is_ragged(ctx.num_live_requests, ctx.max_kv_len, ctx.sum_kv_len))
 
+    def output_projection(self):
+        return self.tensors["o_proj.weight"], None
+
     # -- one step ---------------------------------------------------------
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, project_output: bool = True):
         K = kernels()
         T = x.shape[0]
         ragged = self._ragged(ctx)
@@ -145,6 +148,8 @@ class PagedAttention(Mixer):
             self.num_heads, self.num_kv_heads, self.head_dim, g.page_size,
             self.window or 0, self.scale, ctx, ragged=ragged, **({"fuse": fuse} if fuse is not None else {}),
         )
+        if not project_output:
+            return attn  # (the caller multiplies by `output_projection()` itself)
         out = ctx.workspace.tokens("mixer.out", T, self.hidden_size, x.dtype)
         linear(attn, self.tensors["o_proj.weight"], out)
         return out

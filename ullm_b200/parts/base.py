@@ -105,6 +105,11 @@ class Norm(Part):
     def forward(self, x, residual=None, out=None):
         raise NotImplementedError
 
+    def rms_params(self):
+        """(weight, eps) if this norm is a plain RMSNorm over the whole row, which a block may then fold into a
+        fused kernel; None otherwise."""
+        return None
+
 
 class PositionEncoding(Part):
     rotary_dim: int = 0
@@ -130,6 +135,12 @@ class Mixer(Part):
         """Mixers with equal groups give equal graph keys for the same step (one of them is asked)."""
         return type(self)
 
+    def output_projection(self):
+        """(weight [hidden, width], bias or None) if the mixer ends in a plain linear map and can also stop in
+        front of it (`forward(..., project_output=False)` then returns its [T, width] input); None otherwise.
+        A block may fold that product into a fused kernel."""
+        return None
+
     def forward(self, x, ctx, cache):
         raise NotImplementedError
 
@@ -137,6 +148,11 @@ class Mixer(Part):
 class FeedForward(Part):
     def forward(self, x, ctx):
         raise NotImplementedError
+
+    def gated_weights(self):
+        """(w_gate_up [2 I, hidden], w_down [hidden, I], activation code) if this is a bias-free gated
+        feed-forward down(act(gate(x)) * up(x)) that a block may fold into a fused kernel; None otherwise."""
+        return None
 
 
 class Block(Part):

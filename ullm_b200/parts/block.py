@@ -7,6 +7,7 @@ first block takes residual = x; afterwards each norm is the fused form
 
 from __future__ import annotations
 
+from ..csrc import kernels
 from .base import Block
 from .registry import register_block
 
@@ -41,17 +42,40 @@ class PreNormResidualBlock(Block):
         return size + max(self.mixer.activation_elems(), self.feed_forward.activation_elems())
 
     def forward(self, x, residual, ctx, cache):
-        """x: the previous sub-layer's output (the embedding for the first
-        block, with residual None).  Returns (feed-forward output, residual);
-        the caller's final norm adds them."""
-        T = x.shape[0]
-        h = ctx.workspace.tokens("block.normed", T, x.shape[1], x.dtype)
+        """x: the previous sub-layer's output that is still to be added to the stream (the embedding for the
+        first block, with residual None; None when nothing is pending).  Returns (feed-forward output or None,
+        residual); the caller's next norm adds them."""
+        pending = x if x is not None else residual
+        T = pending.shape[0]
+        h = ctx.workspace.tokens("block.normed", T, pending.shape[1], pending.dtype)
         if residual is None:
             residual = x
             self.mixer_norm.forward(x, None, out=h)
+        elif x is None:
+            self.mixer_norm.forward(residual, None, out=h)
         else:
             self.mixer_norm.forward(x, residual, out=h)
+        fused = self._fusable_tail(T, residual)
+        if fused is not None:
+            # few rows (decode steps): output projection, residual, norm, gated feed-forward and residual in one
+            # kernel; the stream then holds everything and nothing is pending
+            w_o, norm_w, eps, w_gate_up, w_down, act = fused
+            a = self.mixer.forward(h, ctx, cache, project_output=False)
+            work = ctx.workspace.tokens("mlp.act", T, w_down.shape[1], residual.dtype)
+            kernels().fused_layer_tail(a, residual, work, w_o, w_gate_up, w_down, norm_w, eps, act)
+            return None, residual
         a = self.mixer.forward(h, ctx, cache)
         self.feed_forward_norm.forward(a, residual, out=h)
         y = self.feed_forward.forward(h, ctx)
         return y, residual
+
+    def _fusable_tail(self, rows: int, residual):
+        """What the fused kernel needs, if this block's parts offer it (a mixer that ends in a bias-free linear
+        map, an RMSNorm, a bias-free gated feed-forward) and the kernel takes the sizes; else None."""
+        proj, norm, ffn = self.mixer.output_projection(), self.feed_forward_norm.rms_params(), self.feed_forward.gated_weights()
+        if proj is None or norm is None or ffn is None or proj[1] is not None or not residual.is_cuda:
+            return None
+        w_o, (norm_w, eps), (w_gate_up, w_down, act) = proj[0], norm, ffn
+        if not kernels().layer_tail_applies(rows, residual.dtype, residual.shape[1], w_o.shape[1], w_down.shape[1]):
+            return None
+        return w_o, norm_w, eps, w_gate_up, w_down, act

@@ -37,6 +37,9 @@ class GatedMLP(FeedForward):
         self.tensors["up_proj.weight"] = self.w_gate_up[I:]
         self.tensors["down_proj.weight"] = make("down_proj.weight", ParamDecl((H, I)))
 
+    def gated_weights(self):
+        return self.w_gate_up, self.tensors["down_proj.weight"], _ACTIVATIONS[self.activation]
+
     def activation_elems(self):
         return 3 * self.intermediate_size + self.hidden_size  # gate | up, their product, the output
 

@@ -73,8 +73,8 @@ class DecoderModel(Part):
 
     # -- one step -----------------------------------------------------------
     def forward_hidden(self, ctx, caches):
-        """Runs the blocks over the step's tokens.  Returns (y, residual): the
-        last feed-forward output and the residual stream, before the final norm."""
+        """Runs the blocks over the step's tokens.  Returns (y, residual): what the last block left to be added
+        (or None) and the residual stream, before the final norm."""
         T = ctx.num_tokens
         x = ctx.workspace.tokens("model.hidden", T, self.spec.hidden_size, self.dtype)
         self.embedding.forward(ctx.token_ids, x, ctx)
@@ -92,10 +92,15 @@ class DecoderModel(Part):
         K = kernels()
         H = self.spec.hidden_size
         ys = ctx.workspace.requests("head.y", R, H, self.dtype)
-        rs = ctx.workspace.requests("head.res", R, H, self.dtype)
-        K.gather_rows(y, ctx.logits_rows, ys)
-        K.gather_rows(residual, ctx.logits_rows, rs)
-        self.final_norm.forward(ys, rs, out=ys)
+        if y is None or residual is None:
+            # nothing is pending beside the stream (a block that adds its own output), or there is no stream
+            K.gather_rows(y if residual is None else residual, ctx.logits_rows, ys)
+            self.final_norm.forward(ys, None, out=ys)
+        else:
+            rs = ctx.workspace.requests("head.res", R, H, self.dtype)
+            K.gather_rows(y, ctx.logits_rows, ys)
+            K.gather_rows(residual, ctx.logits_rows, rs)
+            self.final_norm.forward(ys, rs, out=ys)
         logits = ctx.workspace.requests("head.logits", R, self.spec.vocab_size, torch.float32)
         self.head.forward(ys, logits)
         return logits

@@ -22,6 +22,9 @@ class RMSNorm(Norm):
     def param_decls(self):
         return {"weight": ParamDecl((self.size,), "norm")}
 
+    def rms_params(self):
+        return self.tensors["weight"], self.eps
+
     def forward(self, x, residual=None, out=None):
         """x [T, size].  residual (same shape), if given, is updated in place
         to x + residual.  Returns the normed rows (in `out` if given; `out`
