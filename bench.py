@@ -16,6 +16,7 @@ exits 2: this engine runs on one GPU.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -532,7 +533,7 @@ def run_linear_probe(args) -> int:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / (2 * iters) * 1000.0
 
-    if args.only:
+    if args.only and args.only != "tail":
         # one kernel on one shape, launched eagerly a few times: what a profiler is pointed at
         N, Kd = shapes[args.shape]
         ws = [torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(2)]
@@ -547,6 +548,45 @@ def run_linear_probe(args) -> int:
         print(f"probe linear: {args.only} on {args.shape} ({N} x {Kd}), {M} rows, {args.steps} launches")
         return 0
     print(f"rows {M}; microseconds per product (weights streamed at the copy peak: 'ideal')")
+    if M <= 16:
+        # the second half of a layer: output projection + residual, norm, gate_up + activation, down + residual
+        QD = QWEN3_8B["num_attention_heads"] * QWEN3_8B["head_dim"]
+        sets = [(torch.randn(H, QD, device="cuda", dtype=torch.bfloat16) * 0.02,
+                 torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.02,
+                 torch.randn(H, I, device="cuda", dtype=torch.bfloat16) * 0.02) for _ in range(2)]
+        attn = torch.randn(M, QD, device="cuda", dtype=torch.bfloat16)
+        res = torch.randn(M, H, device="cuda", dtype=torch.bfloat16)
+        nw = torch.ones(H, device="cuda")
+        hbuf, o_out = torch.empty_like(res), torch.empty_like(res)
+        gu = torch.empty(M, 2 * I, device="cuda", dtype=torch.bfloat16)
+        act = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+
+        def separate(i):
+            wo, wgu, wd = sets[i]
+            K.linear(attn, wo, o_out)
+            K.add_rmsnorm(o_out, res, nw, 1e-6, hbuf)
+            K.linear_act_mul(hbuf, wgu, act, gu, 0)
+            K.linear(act, wd, o_out)
+
+        def fused(i):
+            wo, wgu, wd = sets[i]
+            K.fused_layer_tail(attn, res, act, wo, wgu, wd, nw, 1e-6, 0)
+
+        nbytes = sum(t.numel() for t in sets[0]) * 2
+        ts, tf = timeit(separate, 2), timeit(fused, 2)
+        print(f"layer tail ({nbytes / 1e6:.0f} MB of weights, ideal {nbytes / (pk['hbm_gbs'] * 1e9) * 1e6:.1f} us): "
+              f"separate kernels {ts:.1f} us, fused {tf:.1f} us ({nbytes / tf / 1e6:.2f} TB/s), grid "
+              f"{K.lib.ullm_layer_tail_fused_last_grid()}")
+        K.raise_on_status()
+        if args.only == "tail":
+            K.lib.ullm_layer_tail_fused_phase_mask.argtypes = [ctypes.c_int]
+            for mask, what in ((0, "no product at all (launch, barriers, norm)"), (1, "output projection alone"), (2, "gate_up alone"), (4, "down alone"), (3, "o + gate_up"),
+                               (6, "gate_up + down")):
+                K.lib.ullm_layer_tail_fused_phase_mask(mask)
+                print(f"   phases {what}: {timeit(fused, 2):.1f} us")
+                K._tail_ws[H][1].zero_()
+            K.lib.ullm_layer_tail_fused_phase_mask(7)
+            return 0
     for name, (N, Kd) in shapes.items():
         nbytes = N * Kd * 2
         copies = max(2, int(300e6 // nbytes) + 1)
@@ -948,7 +988,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "sampling"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
-    ap.add_argument("--only", default=None, choices=["stream", "skinny", "tcgen05", "library"],
+    ap.add_argument("--only", default=None, choices=["stream", "skinny", "tcgen05", "library", "tail"],
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
     ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
                     help="--probe linear --only: which of the decode step's products")

@@ -642,8 +642,7 @@ def test_fused_layer_tail(M, H, QD, I, act):
     kernels: row counts that fill one and two batch tiles, phases with and without split units, several items
     per block, three launches in a row on the same counters (tickets and grid barriers must come back), and the
     same bits every time."""
-    if not K().layer_tail_applies(M, torch.bfloat16, H, QD, I):
-        pytest.skip("the fused layer tail is switched off")
+    assert K().lib.ullm_layer_tail_fused_supported(M, H, QD, I)
     bf = torch.bfloat16
     attn = rnd(M, QD, seed=200, dtype=bf)
     res0 = rnd(M, H, seed=201, dtype=bf)

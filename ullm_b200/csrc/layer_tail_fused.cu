@@ -24,9 +24,12 @@
 //     takes a ticket for the unit, and the second one adds the two in half order (the same sum whoever comes
 //     second), adds the residual, rounds once and stores.  In phase 0 it also leaves the unit's sum of squares
 //     per row, from which every block computes the rows' 1/rms after the barrier.
-//   * The norm is applied where phase 1 reads its operand: the fragments of r that ldmatrix delivers are scaled
-//     by 1/rms of their row and the norm weight of their column in 32-bit and rounded to bfloat16, the value the
-//     separate norm kernel would have stored (up to the rounding of r itself, which that kernel does not see).
+//   * The norm between phases 0 and 1 needs whole rows, but only for one number per row: rmsnorm(r) * w =
+//     (1 / rms(r)) * (r * w).  So phase 0's epilogue writes r * w (32-bit product of the unrounded sum, rounded
+//     once) as the operand of phase 1, together with the unit's sums of squares, and phase 1 multiplies its
+//     32-bit sums by the row's 1 / rms before the activation: one grid barrier between the two, no pass over r.
+//     (The separate norm kernel rounds r * w / rms; here r * w is rounded and 1 / rms applied in 32-bit after
+//     the product.)
 #include <cooperative_groups.h>
 
 #include "linear_stream_core.cuh"
@@ -44,13 +47,14 @@ struct LtPhase {
 
 struct LtMaps {
   CUtensorMap w[3];  // Wo (boxes of 32 rows), Wgate|Wup (boxes of 16 rows), Wdown (boxes of 32 rows)
-  CUtensorMap x[3];  // attn, residual, act_out
+  CUtensorMap x[3];  // attn, normed, act_out
 };
 
 struct LtParams {
   LtPhase ph[3];
   __nv_bfloat16* residual;  // [M, H], updated in place
   __nv_bfloat16* act_out;   // [M, I]
+  __nv_bfloat16* normed;    // [M, H]: (residual after phase 0) * norm_w, the operand of phase 1
   const float* norm_w;      // [H]
   float eps;
   int act;                  // 1 silu, 2 gelu_tanh
@@ -59,7 +63,7 @@ struct LtParams {
   float* pair;              // partial sums of split units: [2 halves][units][2][32 lanes][NT][4]
   float* sq;                // phase 0's sums of squares: [units][2][16]
   unsigned* tickets;        // [units] per split phase (phase 0, then phase 2)
-  unsigned* bars;           // [0], [1]: grid barriers after phases 0 and 1; [2]: blocks that have finished
+  unsigned* bars;           // grid barriers after phases 0 and 1; [2]: blocks that have finished
   int* status;
 };
 
@@ -87,17 +91,11 @@ __device__ __forceinline__ bool lt_mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// one bfloat16 pair of the operand, scaled by the row's 1/rms and the columns' norm weights
-__device__ __forceinline__ uint32_t lt_scale_pair(uint32_t v, float rstd, float2 w) {
-  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v);
-  const float2 f = __bfloat1622float2(b);
-  const __nv_bfloat162 o = __floats2bfloat162_rn(f.x * rstd * w.x, f.y * rstd * w.y);
-  return *reinterpret_cast<const uint32_t*>(&o);
-}
-
 // a position in a block's list of stages: phase, item of the phase, k block of the item
 struct LtCursor {
-  int ph, j, kb, it;
+  int ph, j, kb, it;       // phase, item of the phase, k block of the item, stage count
+  int slot, round;         // ring slot and how often the ring has been gone round
+  int unit, half, kper, kbase;  // of the current item
 };
 
 template <int NT>
@@ -137,50 +135,56 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
   if (warp == LS_CONSUMER_WARPS) {
     // ---- producer ---------------------------------------------------------------------------------------
     if (lane == 0) {
-      auto advance = [&](LtCursor& q) {
-        ++q.it;
-        if (++q.kb == p.ph[q.ph].kper) {
-          q.kb = 0;
-          ++q.j;
-        }
+      // One thread's instruction stream paces the ring, so a position in the block's list of stages is carried
+      // along and stepped: nothing is divided per stage (unit and half of an item are worked out once per item).
+      auto enter_item = [&](LtCursor& q) {
         while (q.ph < 3 && q.j >= n_my[q.ph]) {
           ++q.ph;
           q.j = 0;
         }
+        if (q.ph < 3) {
+          const LtPhase& ph = p.ph[q.ph];
+          const int item = c + q.j * G;
+          q.half = item / ph.n_units;
+          q.unit = item - q.half * ph.n_units;
+          q.kper = ph.kper;
+          q.kbase = q.half * ph.kper;
+        }
       };
-      LtCursor w = {0, 0, 0, 0}, x = {0, 0, 0, 0};
-      while (w.ph < 3 && n_my[w.ph] == 0) ++w.ph;
-      x = w;
-      int seen = 0;  // grid barriers known to be passed: the operand of phase ph needs seen >= ph
+      auto advance = [&](LtCursor& q) {
+        ++q.it;
+        if (++q.slot == p.stages) q.slot = 0, ++q.round;
+        if (++q.kb == q.kper) {
+          q.kb = 0;
+          ++q.j;
+          enter_item(q);
+        }
+      };
+      LtCursor w = {};
+      enter_item(w);
+      LtCursor x = w;
+      int seen = 0;  // phases whose operand is known to be ready: phase ph > 0 needs grid barrier ph - 1
       int idle = 0;
       while (x.it < total_it) {
         bool progressed = false;
-        if (w.it < total_it) {
-          const int s = w.it % p.stages;
-          if (w.it < p.stages || lt_mbar_test(&empty_bar[s], ((w.it / p.stages) - 1) & 1)) {
-            const LtPhase& ph = p.ph[w.ph];
-            const int item = c + w.j * G, unit = item % ph.n_units, half = item / ph.n_units;
-            const int kb = half * ph.kper + w.kb;
-            unsigned char* st = ring + s * STAGE_BYTES;
-            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            if (w.ph == 1) {
-              tma_load_3d(st, &maps.w[1], &full_bar[s], 0, unit * 16, kb * 4);
-              tma_load_3d(st + 8192, &maps.w[1], &full_bar[s], 0, p.I + unit * 16, kb * 4);
-            } else {
-              tma_load_3d(st, &maps.w[w.ph], &full_bar[s], 0, unit * 32, kb * 4);
-            }
-            advance(w);
-            progressed = true;
+        if (w.it < total_it && (w.round == 0 || lt_mbar_test(&empty_bar[w.slot], (w.round - 1) & 1))) {
+          unsigned char* st = ring + w.slot * STAGE_BYTES;
+          const int kb = w.kbase + w.kb;
+          mbar_expect_tx(&full_bar[w.slot], STAGE_BYTES);
+          if (w.ph == 1) {
+            tma_load_3d(st, &maps.w[1], &full_bar[w.slot], 0, w.unit * 16, kb * 4);
+            tma_load_3d(st + 8192, &maps.w[1], &full_bar[w.slot], 0, p.I + w.unit * 16, kb * 4);
+          } else {
+            tma_load_3d(st, &maps.w[w.ph], &full_bar[w.slot], 0, w.unit * 32, kb * 4);
           }
+          advance(w);
+          progressed = true;
         }
         if (x.it < w.it) {
           if (x.ph <= seen) {
             if (x.it == 0) pdl_wait();
-            const LtPhase& ph = p.ph[x.ph];
-            const int item = c + x.j * G, half = item / ph.n_units;
-            const int kb = half * ph.kper + x.kb;
-            const int s = x.it % p.stages;
-            tma_load_3d(ring + s * STAGE_BYTES + LS_W_STAGE_BYTES, &maps.x[x.ph], &full_bar[s], 0, 0, kb * 4);
+            tma_load_3d(ring + x.slot * STAGE_BYTES + LS_W_STAGE_BYTES, &maps.x[x.ph], &full_bar[x.slot], 0, 0,
+                        (x.kbase + x.kb) * 4);
             advance(x);
             progressed = true;
           } else if (lt_ld_acquire(&p.bars[seen]) >= (unsigned)G) {
@@ -207,11 +211,12 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
     const int b_row = (lane & 7) + (lane >> 4) * 8;
     const int b_chunk = (lane >> 3) & 1;
     bool failed = false;
-    int it = 0;
+    int it = 0, s = 0;  // stage count; the ring slot of the next stage and the parity of its use, stepped
+    uint32_t parity = 0;
     for (int phi = 0; phi < 3; ++phi) {
       const LtPhase& ph = p.ph[phi];
       if (phi == 1) {
-        // ---- the rows' 1/rms from phase 0's sums of squares: all of phase 0 is done everywhere ------------
+        // ---- the rows' 1 / rms for phase 1's epilogue.  All of phase 0 is done everywhere: ------------------------
         if (threadIdx.x == 0 && !failed) {
           int polls = 0;
           while (lt_ld_acquire(&p.bars[0]) < (unsigned)G) {
@@ -224,18 +229,26 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
         }
         ls_bar_sync_consumers();
         {
-          const int m = threadIdx.x & 15, part = threadIdx.x >> 4;  // 16 parts of the units' partial sums
+          // the rows' 1/rms: 16 parts of the units' partial sums per row, all loads of a thread in flight together
+          const int m = threadIdx.x & 15, part = threadIdx.x >> 4;
           const int total = p.ph[0].n_units * 2;
           const int per = (total + 15) / 16;
-          float s = 0.f;
-          for (int q = part * per; q < (part + 1) * per && q < total; ++q) s += lt_ld_cg_f(p.sq + (size_t)q * 16 + m);
-          part_s[part][m] = s;
+          float sum = 0.f;
+          for (int q0 = part * per; q0 < (part + 1) * per && q0 < total; q0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              v[e] = (q0 + e < (part + 1) * per && q0 + e < total) ? __ldcg(p.sq + (size_t)(q0 + e) * 16 + m) : 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum += v[e];
+          }
+          part_s[part][m] = sum;
         }
         ls_bar_sync_consumers();
         if (threadIdx.x < 16) {
-          float s = 0.f;
-          for (int q = 0; q < 16; ++q) s += part_s[q][threadIdx.x];  // in part order: the same sum in every block
-          rstd_s[threadIdx.x] = rsqrtf(s / (float)p.H + p.eps);
+          float sum = 0.f;
+          for (int q = 0; q < 16; ++q) sum += part_s[q][threadIdx.x];  // in part order: the same sum in every block
+          rstd_s[threadIdx.x] = rsqrtf(sum / (float)p.H + p.eps);
         }
         ls_bar_sync_consumers();
       }
@@ -247,8 +260,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
         for (int kb = 0; kb < ph.kper; ++kb, ++it) {
-          const int s = it % p.stages;
-          if (!failed && !__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / p.stages) & 1))) {
+          if (!failed && !__all_sync(0xffffffffu, mbar_wait(&full_bar[s], parity))) {
             ullm_report(p.status, ULLM_STATUS_TIMEOUT, 63, it);  // (the whole warp gives up together)
             abort_flag = 1;
             failed = true;
@@ -272,22 +284,6 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);
-            if (phi == 1) {
-              // the norm, on the operand: fragment register 2 n holds row 8 n + g at columns k0 + 2 t, + 1,
-              // register 2 n + 1 the same row at columns k0 + 8 + 2 t, + 1
-              const int kbase = (half * ph.kper + kb) * LS_BK + kq * 64 + 2 * t;
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                const float2 w0 = __ldg(reinterpret_cast<const float2*>(p.norm_w + kbase + jj * 16));
-                const float2 w1 = __ldg(reinterpret_cast<const float2*>(p.norm_w + kbase + jj * 16 + 8));
-#pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                  const float rs = rstd_s[n * 8 + g];
-                  b[jj][n * 2] = lt_scale_pair(b[jj][n * 2], rs, w0);
-                  b[jj][n * 2 + 1] = lt_scale_pair(b[jj][n * 2 + 1], rs, w1);
-                }
-              }
-            }
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj)
 #pragma unroll
@@ -296,6 +292,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);
           }
+          if (++s == p.stages) s = 0, parity ^= 1;
         }
         // ---- the four k quarters of each half meet; warps 0 and 1 (quarter 0) finish the item ---------------
 #pragma unroll
@@ -327,9 +324,11 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const int col = unit * 16 + g + 8 * (i >> 1), m = n * 8 + 2 * t + (i & 1);
-                  if (m < p.M && col < ph.n_out)
+                  if (m < p.M && col < ph.n_out) {
+                    const float rs = rstd_s[m], gate = v[n][i] * rs, upv = up[n][i] * rs;
                     p.act_out[(size_t)m * ph.n_out + col] =
-                        __float2bfloat16_rn((p.act == 1 ? act_silu(v[n][i]) : act_gelu_tanh(v[n][i])) * up[n][i]);
+                        __float2bfloat16_rn((p.act == 1 ? act_silu(gate) : act_gelu_tanh(gate)) * upv);
+                  }
                 }
             }
           } else {
@@ -375,6 +374,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
                     const float r = v[n][i] + __bfloat162float(__ushort_as_bfloat16(
                                                   __ldcg(reinterpret_cast<const unsigned short*>(p.residual) + o)));
                     p.residual[o] = __float2bfloat16_rn(r);
+                    if (phi == 0) p.normed[o] = __float2bfloat16_rn(r * __ldg(p.norm_w + col));
                     ss[n][i & 1] += r * r;
                   }
                 }
@@ -432,6 +432,11 @@ __global__ void __launch_bounds__(LS_THREADS, 2) layer_tail_fused_kernel(const _
 static int g_lt_sms = 0;
 static int g_lt_attr[2] = {0, 0};
 static int g_lt_grid[2] = {0, 0};
+static int g_lt_last_grid = 0;
+static int g_lt_phase_mask = 7;  // measurements only: phases that run (bit i: phase i); the result is wrong otherwise
+extern "C" void ullm_layer_tail_fused_phase_mask(int m) { g_lt_phase_mask = m & 7; }
+// The grid of the last launch (tests and measurements read it).
+extern "C" int ullm_layer_tail_fused_last_grid(void) { return g_lt_last_grid; }
 
 // Sizes the kernel takes: at most 16 rows; every K a multiple of 256 (whole stages, whole halves); hidden and
 // intermediate sizes multiples of 32 and 16.
@@ -470,12 +475,13 @@ static int lt_launch(int which, const LtMaps& maps, LtParams p, cudaStream_t st)
     g_lt_attr[which] = 1;
   }
   const int grid = g_lt_grid[which];
+  g_lt_last_grid = grid;
   // a phase with few units is split in two halves of K when that still fits the grid
   for (int i = 0; i < 3; ++i) {
     LtPhase& ph = p.ph[i];
     ph.ksplit = (i != 1 && ph.n_units * 2 <= grid && ph.k_blocks % 2 == 0 && ph.k_blocks >= 4) ? 2 : 1;
     ph.kper = ph.k_blocks / ph.ksplit;
-    ph.items = ph.n_units * ph.ksplit;
+    ph.items = (g_lt_phase_mask >> i) & 1 ? ph.n_units * ph.ksplit : 0;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -494,16 +500,16 @@ static int lt_launch(int which, const LtMaps& maps, LtParams p, cudaStream_t st)
   return ULLM_OK;
 }
 
-// attn [M, QD], residual [M, H] (in/out), act_out [M, I] (work buffer), w_o [H, QD], w_gate_up [2 I, H],
+// attn [M, QD], residual [M, H] (in/out), act_out [M, I] and normed [M, H] (work buffers), w_o [H, QD], w_gate_up [2 I, H],
 // w_down [H, I], norm_w [H] float32.  scratch / counters: at least what the two functions above say, the
 // counters zero before the first launch (and after a launch that reported a timeout).
-extern "C" int ullm_layer_tail_fused(const void* attn, void* residual, void* act_out, const void* w_o,
+extern "C" int ullm_layer_tail_fused(const void* attn, void* residual, void* act_out, void* normed, const void* w_o,
                                      const void* w_gate_up, const void* w_down, const float* norm_w, float eps,
                                      int act, int M, int H, int QD, int I, float* scratch, unsigned* counters,
                                      int* status, void* stream) {
   if (!ullm_layer_tail_fused_supported(M, H, QD, I)) return ULLM_ERR_UNSUPPORTED;
   if (act != 1 && act != 2) return ULLM_ERR_BAD_SIZE;
-  if (scratch == nullptr || counters == nullptr || norm_w == nullptr) return ULLM_ERR_BAD_SIZE;
+  if (scratch == nullptr || counters == nullptr || norm_w == nullptr || normed == nullptr) return ULLM_ERR_BAD_SIZE;
   if (g_lt_sms == 0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -514,7 +520,7 @@ extern "C" int ullm_layer_tail_fused(const void* attn, void* residual, void* act
   LtMaps maps;
   if (!ls_chunked_map(w_o, H, QD, 32, &maps.w[0]) || !ls_chunked_map(w_gate_up, 2LL * I, H, 16, &maps.w[1]) ||
       !ls_chunked_map(w_down, H, I, 32, &maps.w[2]) || !ls_chunked_map(attn, M, QD, 8 * NT, &maps.x[0]) ||
-      !ls_chunked_map(residual, M, H, 8 * NT, &maps.x[1]) || !ls_chunked_map(act_out, M, I, 8 * NT, &maps.x[2]))
+      !ls_chunked_map(normed, M, H, 8 * NT, &maps.x[1]) || !ls_chunked_map(act_out, M, I, 8 * NT, &maps.x[2]))
     return ULLM_ERR_LAUNCH;
   LtParams p = {};
   const int units_h = (H + 31) / 32;
@@ -523,6 +529,7 @@ extern "C" int ullm_layer_tail_fused(const void* attn, void* residual, void* act
   p.ph[2].n_units = units_h, p.ph[2].k_blocks = I / LS_BK, p.ph[2].n_out = H;
   p.residual = (__nv_bfloat16*)residual;
   p.act_out = (__nv_bfloat16*)act_out;
+  p.normed = (__nv_bfloat16*)normed;
   p.norm_w = norm_w;
   p.eps = eps;
   p.act = act;

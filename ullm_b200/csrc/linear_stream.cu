@@ -127,50 +127,58 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
     const int lanes = p.chunked ? 1 : 4;
     if (lane < lanes) {
       const int kc = lane;
-      auto issue_w = [&](int it) {
-        const int u = cid + (it / nkb) * ncl;
-        const int kb = kb0 + it % nkb;
-        const int s = it % p.stages;
-        unsigned char* st = ring + s * STAGE_BYTES;
-        if (lane == 0) mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      // One thread's instruction stream is what paces the ring: no division per stage.  The position in the list
+      // of stages (unit, k block) and in the ring (slot, round) is carried along and stepped.
+      struct Pos {
+        int u, kb, slot, round;
+      };
+      auto step = [&](Pos& q) {
+        if (++q.kb == nkb) q.kb = 0, q.u += ncl;
+        if (++q.slot == p.stages) q.slot = 0, ++q.round;
+      };
+      auto issue_w = [&](const Pos& q) {
+        unsigned char* st = ring + q.slot * STAGE_BYTES;
+        const int kb = kb0 + q.kb;
+        if (lane == 0) mbar_expect_tx(&full_bar[q.slot], STAGE_BYTES);
         if (p.chunked) {
           if (p.act) {
-            tma_load_3d(st, &w_map, &full_bar[s], 0, u * 16, kb * 4);
-            tma_load_3d(st + 8192, &w_map, &full_bar[s], 0, half_rows + u * 16, kb * 4);
+            tma_load_3d(st, &w_map, &full_bar[q.slot], 0, q.u * 16, kb * 4);
+            tma_load_3d(st + 8192, &w_map, &full_bar[q.slot], 0, half_rows + q.u * 16, kb * 4);
           } else {
-            tma_load_3d(st, &w32_map, &full_bar[s], 0, u * 32, kb * 4);
+            tma_load_3d(st, &w32_map, &full_bar[q.slot], 0, q.u * 32, kb * 4);
           }
           return;
         }
         __syncwarp(0xf);
         if (p.act) {
-          tma_load_2d(st + (0 * 4 + kc) * 2048, &w_map, &full_bar[s], kb * LS_BK + kc * 64, u * 16);
-          tma_load_2d(st + (1 * 4 + kc) * 2048, &w_map, &full_bar[s], kb * LS_BK + kc * 64, half_rows + u * 16);
+          tma_load_2d(st + (0 * 4 + kc) * 2048, &w_map, &full_bar[q.slot], kb * LS_BK + kc * 64, q.u * 16);
+          tma_load_2d(st + (1 * 4 + kc) * 2048, &w_map, &full_bar[q.slot], kb * LS_BK + kc * 64, half_rows + q.u * 16);
         } else {
-          tma_load_2d(st + kc * 4096, &w32_map, &full_bar[s], kb * LS_BK + kc * 64, u * 32);
+          tma_load_2d(st + kc * 4096, &w32_map, &full_bar[q.slot], kb * LS_BK + kc * 64, q.u * 32);
         }
       };
-      auto issue_x = [&](int it) {
-        const int kb = kb0 + it % nkb;
-        const int s = it % p.stages;
-        unsigned char* st = ring + s * STAGE_BYTES + LS_W_STAGE_BYTES;
+      auto issue_x = [&](const Pos& q) {
+        unsigned char* st = ring + q.slot * STAGE_BYTES + LS_W_STAGE_BYTES;
+        const int kb = kb0 + q.kb;
         if (p.chunked)
-          tma_load_3d(st, &x_map, &full_bar[s], 0, 0, kb * 4);
+          tma_load_3d(st, &x_map, &full_bar[q.slot], 0, 0, kb * 4);
         else
-          tma_load_2d(st + kc * X_BOX_BYTES, &x_map, &full_bar[s], kb * LS_BK + kc * 64, 0);
+          tma_load_2d(st + kc * X_BOX_BYTES, &x_map, &full_bar[q.slot], kb * LS_BK + kc * 64, 0);
       };
       const int first = total_it < p.stages ? total_it : p.stages;
-      for (int it = 0; it < first; ++it) issue_w(it);  // the weights: before the kernel in front has finished
+      Pos w = {cid, 0, 0, 0};
+      for (int it = 0; it < first; ++it, step(w)) issue_w(w);  // the weights: before the kernel in front has finished
       pdl_wait();
-      for (int it = 0; it < first; ++it) issue_x(it);  // the batch rows: what that kernel wrote
-      for (int it = first; it < total_it; ++it) {
-        if (!mbar_wait(&empty_bar[it % p.stages], ((it / p.stages) - 1) & 1)) {
+      Pos x = {cid, 0, 0, 0};
+      for (int it = 0; it < first; ++it, step(x)) issue_x(x);  // the batch rows: what that kernel wrote
+      for (int it = first; it < total_it; ++it, step(w)) {
+        if (!mbar_wait(&empty_bar[w.slot], (w.round - 1) & 1)) {
           ullm_report(p.status, ULLM_STATUS_TIMEOUT, 51, it);
           abort_flag = 1;
           break;  // (the four lanes wait on the same barrier: all of them give up or none)
         }
-        issue_w(it);
-        issue_x(it);
+        issue_w(w);
+        issue_x(w);
       }
     } else {
       pdl_wait();
@@ -186,6 +194,8 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
     const int b_row = (lane & 7) + (lane >> 4) * 8;        // matrices 0, 1: batch rows 0-7 (k 0-7, 8-15); 2, 3: rows 8-15
     const int b_chunk = (lane >> 3) & 1;
     bool failed = false;
+    int s = 0;             // the ring slot of the next stage and the parity of its use, stepped (no division per stage)
+    uint32_t parity = 0;
     for (int ui = 0; ui < my_units; ++ui) {
       float acc[NT][4];
 #pragma unroll
@@ -193,10 +203,8 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
       for (int kb = 0; kb < nkb; ++kb) {
-        const int it = ui * nkb + kb;
-        const int s = it % p.stages;
-        if (!failed && !__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / p.stages) & 1))) {
-          ullm_report(p.status, ULLM_STATUS_TIMEOUT, 52, it);  // (the whole warp gives up together)
+        if (!failed && !__all_sync(0xffffffffu, mbar_wait(&full_bar[s], parity))) {
+          ullm_report(p.status, ULLM_STATUS_TIMEOUT, 52, ui * nkb + kb);  // (the whole warp gives up together)
           abort_flag = 1;
           failed = true;
         }
@@ -231,6 +239,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty_bar[s]);
         }
+        if (++s == p.stages) s = 0, parity ^= 1;
       }
       // ---- the four k quarters of each half meet (two batch tiles per pass); warps 0 and 1 (quarter 0)
       // finish the unit --------------------------------------------------------------------------------

@@ -169,9 +169,10 @@ class Kernels:
         self.fused_mlp_rows = int(get("ULLM_B200_FUSED_MLP_ROWS", "4096"))
         # rows up to which the library's product is called through cuBLASLt with a timed choice of algorithm
         self.lt_rows = int(get("ULLM_B200_LT_ROWS", str(1 << 30)))
-        # rows up to which a decode step runs the second half of a layer (output projection, residual, norm, gated
-        # feed-forward, residual) as one kernel; 0: never
-        self.fused_tail_rows = int(get("ULLM_B200_FUSED_TAIL_ROWS", "16"))
+        # rows up to which a step runs the second half of a layer (output projection, residual, norm, gated
+        # feed-forward, residual) as one cooperative kernel; 0 (the default): never.  Measured at Qwen3-8B sizes:
+        # 71 us against 70 us for the separate kernels at 8 rows, 77 against 70 at 16: no gain yet.
+        self.fused_tail_rows = int(get("ULLM_B200_FUSED_TAIL_ROWS", "0"))
 
     # -- ctypes signatures --------------------------------------------------
     def _declare(self) -> None:
@@ -194,7 +195,7 @@ class Kernels:
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_stream": [P, P, P, P, P, I, I, I, I, I, P, P],
-            "ullm_layer_tail_fused": [P, P, P, P, P, P, P, F, I, I, I, I, I, P, P, P, P],
+            "ullm_layer_tail_fused": [P, P, P, P, P, P, P, P, F, I, I, I, I, I, P, P, P, P],
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_lt_linear": [P, P, P, I, I, I, I, P, LL, I, P, LL, P],
@@ -249,6 +250,7 @@ class Kernels:
         L.ullm_layer_tail_fused_scratch_floats.restype = c_longlong
         L.ullm_layer_tail_fused_counters.argtypes = [I]
         L.ullm_layer_tail_fused_counters.restype = c_longlong
+        L.ullm_layer_tail_fused_last_grid.restype = c_int
         L.ullm_linear_stream_supported.argtypes = [I, I, I]
         L.ullm_linear_stream_supported.restype = c_int
         L.ullm_linear_stream_blocks_per_sm.argtypes = [I]
@@ -280,7 +282,7 @@ class Kernels:
                 self._lin_counters.zero_()  # a product that gave up may have left tiles half counted
             for _part, _prefix, flags in self._decb.values():
                 flags.zero_()  # likewise the merge flags of the balanced decode attention
-            for _scratch, counters in self._tail_ws.values():
+            for _scratch, counters, _normed in self._tail_ws.values():
                 counters.zero_()  # and the tickets and grid barriers of the fused layer tail
             msg = STATUS_MESSAGES.get(s[0], "status {code}").format(index=s[1], value=s[2], code=s[0])
             raise KernelError(f"a kernel refused an index: {msg}")
@@ -395,10 +397,11 @@ class Kernels:
         ws = self._tail_ws.get(H)
         if ws is None:  # scratch of the split units and the zeroed counters, made at the first (eager) call
             ws = (torch.empty(self.lib.ullm_layer_tail_fused_scratch_floats(H), dtype=torch.float32, device="cuda"),
-                  torch.zeros(self.lib.ullm_layer_tail_fused_counters(H), dtype=torch.int32, device="cuda"))
+                  torch.zeros(self.lib.ullm_layer_tail_fused_counters(H), dtype=torch.int32, device="cuda"),
+                  torch.empty(16, H, dtype=torch.bfloat16, device="cuda"))  # the normed rows between its phases
             self._tail_ws[H] = ws
         self._check(self.lib.ullm_layer_tail_fused(
-            _ptr(attn), _ptr(residual), _ptr(act_out), _ptr(w_o), _ptr(w_gate_up), _ptr(w_down), _ptr(norm_w),
+            _ptr(attn), _ptr(residual), _ptr(act_out), _ptr(ws[2]), _ptr(w_o), _ptr(w_gate_up), _ptr(w_down), _ptr(norm_w),
             float(eps), act + 1, M, H, QD, inter, _ptr(ws[0]), _ptr(ws[1]), _ptr(self.status), _stream()),
             f"layer_tail_fused ({M} rows, hidden {H}, intermediate {inter})")
         return residual
