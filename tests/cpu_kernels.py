@@ -80,7 +80,7 @@ class CpuKernels:
                            slot_mapping, k_pages, v_pages):
         self._count("qk_norm_rope_store")
         T = qkv.shape[0]
-        x = qkv.float().view(T, num_q + 2 * num_kv, D)
+        x = qkv.float().clone().view(T, num_q + 2 * num_kv, D)
         q, k, v = x[:, :num_q], x[:, num_q:num_q + num_kv], x[:, num_q + num_kv:]
 
         def norm(t, w):
@@ -107,6 +107,15 @@ class CpuKernels:
             ok = sm >= 0
             kf[sm[ok]] = k[ok].to(kf.dtype)
             vf[sm[ok]] = v[ok].to(vf.dtype)
+
+    def qk_norm_in_place(self, qkv, num_q, num_kv, D, q_w, k_w, eps):
+        T = qkv.shape[0]
+        x = qkv.float().clone().view(T, num_q + 2 * num_kv, D)
+        for lo, hi, w in ((0, num_q, q_w), (num_q, num_q + num_kv, k_w)):
+            if w is not None:
+                t = x[:, lo:hi]
+                x[:, lo:hi] = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+        qkv.copy_(x.view(T, -1).to(qkv.dtype))
 
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req,
                         num_q, num_kv, D, page_size, window, scale, ctx=None, ragged=False):

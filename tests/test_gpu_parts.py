@@ -396,3 +396,102 @@ def test_toy_routed_feed_forward_and_another_position_encoding_register_build_an
         ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
         FEED_FORWARDS.pop("top1_experts", None)
         POSITION_ENCODINGS.pop("slow_partial_rope", None)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# a position encoding that is no rotation by tables: it changes queries and keys with code of its own
+# ---------------------------------------------------------------------------------------------------------
+TOY_GAIN = dict(architectures=["ToyGainForCausalLM"], hidden_size=48, intermediate_size=64, vocab_size=97, heads=6,
+                kv_heads=2, head_dim=16, eps=1e-5, gain=0.03, drift=0.2, max_positions=128)
+
+
+def _register_toy_gain():
+    from ullm_b200.config import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                                  ScheduleEntry, register_architecture)
+    from ullm_b200.parts import PositionEncoding, register_position_encoding
+
+    @register_position_encoding("position_gain")
+    class PositionGain(PositionEncoding):
+        """Queries grow with their position, keys get a position-dependent offset: no rotation, no tables."""
+
+        def __init__(self, rotary_dim, theta, max_positions, gain=0.0, drift=0.0):
+            super().__init__()
+            self.gain, self.drift, self.max_positions = gain, drift, max_positions
+
+        def transforms_qk(self):
+            return True
+
+        def apply(self, q, k, positions):
+            pos = positions.to(torch.float32)
+            q.mul_((1.0 + self.gain * pos)[:, None, None].to(q.dtype))
+            k.add_((self.drift * torch.sin(0.1 * pos))[:, None, None].to(k.dtype))
+
+    def spec(d):
+        H = d["hidden_size"]
+        norm = NormSpec("rmsnorm", H, d["eps"])
+        names = dict(mixer="mixer.", feed_forward="mlp.", mixer_norm="norm1.", feed_forward_norm="norm2.")
+        att = MixerSpec("paged_attention", dict(
+            hidden_size=H, num_heads=d["heads"], num_kv_heads=d["kv_heads"], head_dim=d["head_dim"],
+            qk_norm=NormSpec("rmsnorm", d["head_dim"], d["eps"]),
+            position=PositionSpec("position_gain", 0, 0.0, d["max_positions"], dict(gain=d["gain"], drift=d["drift"]))))
+        dense = FeedForwardSpec("gated_mlp", dict(hidden_size=H, intermediate_size=d["intermediate_size"], activation="silu"))
+        layers = [LayerSpec("prenorm_residual", att, dense, norm, norm, names) for _ in range(2)]
+        return ModelSpec(architecture="ToyGainForCausalLM", hidden_size=H, vocab_size=d["vocab_size"], layers=layers,
+                         schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm, tie_embeddings=True,
+                         max_positions=d["max_positions"], dtype="float32", embedding_name="emb.",
+                         layer_name="layers.{}.", final_norm_name="final_norm.", head_name="head.")
+
+    register_architecture("ToyGainForCausalLM", lambda d: d, spec)
+
+
+def toy_gain_plain(ids, w):
+    d = TOY_GAIN
+    T, D = len(ids), d["head_dim"]
+    x = w["emb.weight"][torch.tensor(ids)]
+    pos = torch.arange(T, dtype=torch.float32)
+    for l in range(2):
+        p = f"layers.{l}."
+        h = pm.rms_norm(x, w[p + "norm1.weight"], d["eps"])
+        m = p + "mixer."
+        q = pm.rms_norm((h @ w[m + "q_proj.weight"].T).view(T, d["heads"], D), w[m + "q_norm.weight"], d["eps"])
+        k = pm.rms_norm((h @ w[m + "k_proj.weight"].T).view(T, d["kv_heads"], D), w[m + "k_norm.weight"], d["eps"])
+        v = (h @ w[m + "v_proj.weight"].T).view(T, d["kv_heads"], D)
+        q = q * (1.0 + d["gain"] * pos)[:, None, None]
+        k = k + (d["drift"] * torch.sin(0.1 * pos))[:, None, None]
+        a = pm.causal_attention(q, k, v, D ** -0.5, None)
+        x = x + a.reshape(T, -1) @ w[m + "o_proj.weight"].T
+        h = pm.rms_norm(x, w[p + "norm2.weight"], d["eps"])
+        x = x + pm.gated_mlp(h, w, p + "mlp.")
+    return pm.rms_norm(x, w["final_norm.weight"], d["eps"]) @ w["emb.weight"].T
+
+
+def test_a_position_encoding_with_code_of_its_own_registers_builds_and_steps():
+    """An encoding that is no rotation by tables (queries scaled and keys shifted by functions of the position,
+    written here with plain tensor operations) is registered, built from a specification and stepped: whole, one
+    token at a time and in portions, against the plain computation; the keys it changed are the keys the cache
+    holds."""
+    from ullm_b200.config import ARCHITECTURES
+    from ullm_b200.engine import ModelRunner, StepEntry
+    from ullm_b200.parts.registry import POSITION_ENCODINGS
+
+    _register_toy_gain()
+    try:
+        runner = ModelRunner(config=TOY_GAIN, dtype="float32", device=device(), page_size=8, num_pages=24,
+                             max_requests=2, max_context=96, max_step_tokens=64, load_format="random", seed=5,
+                             random_std=0.2, random_norm_std=0.1, poison_cache=True)
+        w = {n: t.float().cpu() for n, t in runner.model.all_tensors().items()}
+        ids = random_ids(TOY_GAIN["vocab_size"], 60, 3)
+        ref = toy_gain_plain(ids, w)
+        assert not torch.allclose(ref, toy_gain_plain(ids[:30] + ids[30:][::-1], w)[:60], atol=1e-3)
+        for cuts in ([60], [28] + [1] * 32, [7, 2, 5, 3, 16, 2, 1, 9, 15]):
+            runner.add_request("a")
+            outs, i = [], 0
+            for n in cuts:
+                outs.append(runner.step([StepEntry("a", ids[i:i + n], list(range(n)))]).float().cpu().clone())
+                i += n
+            runner.end_request("a")
+            runner.check_device_status()
+            assert_close(torch.cat(outs), ref, "float32", f"position gain, cuts {cuts[:3]}")
+    finally:
+        ARCHITECTURES.pop("ToyGainForCausalLM", None)
+        POSITION_ENCODINGS.pop("position_gain", None)

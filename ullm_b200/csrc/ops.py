@@ -185,6 +185,7 @@ class Kernels:
             "ullm_act_mul": [I, I, P, P, I, I, P],
             "ullm_cast_bf16_f32": [P, P, LL, P],
             "ullm_qk_norm_rope_store": [I, P, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, LL, P, P],
+            "ullm_qk_norm_in_place": [I, P, I, I, I, I, P, P, F, P, P],
             "ullm_paged_attention_generic": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_decode_attention": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P],
             "ullm_decode_attention_balanced": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
@@ -636,6 +637,21 @@ class Kernels:
             _DT[qkv.dtype], _ptr(qkv), T, num_q, num_kv, head_dim, _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos),
             _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
             num_slots, _ptr(self.status), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
+
+    @_timed("qk_norm_rope_store")
+    def qk_norm_in_place(self, qkv, num_q, num_kv, head_dim, q_w, k_w, eps):
+        """Per-head RMSNorm of the queries and the keys of `qkv` ([T, (Hq + 2 Hkv) D]) where they lie; nothing is
+        stored in a cache.  (For a position encoding with code of its own, which then changes q and k.)"""
+        _need(qkv, "qkv")
+        T, W = qkv.shape
+        if W != (num_q + 2 * num_kv) * head_dim:
+            raise KernelError(f"qk_norm_in_place: qkv row length {W} != (Hq + 2 Hkv) * D")
+        for t, n in ((q_w, "q_norm weight"), (k_w, "k_norm weight")):
+            if t is not None:
+                _need(t, n, torch.float32)
+        self._check(self.lib.ullm_qk_norm_in_place(_DT[qkv.dtype], _ptr(qkv), T, num_q, num_kv, head_dim, _ptr(q_w),
+                                                   _ptr(k_w), float(eps), _ptr(self.status), _stream()),
+                    f"qk_norm_in_place (head_dim {head_dim})")
 
     def _decode_choice(self, T, ragged, num_q, num_kv, head_dim, page_size, row_stride) -> str:
         """Which decode attention kernel takes T one-token rows: "tcgen05", "balanced" or "split"."""

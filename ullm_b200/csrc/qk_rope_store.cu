@@ -21,7 +21,7 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                           int rotary_dim, int max_positions, const int* __restrict__ positions,
                                           const int* __restrict__ slot_mapping, T* k_cache, T* v_cache,
-                                          long long num_slots, int* status) {
+                                          long long num_slots, int* status, int k_in_place) {
   __shared__ float sh[QK_WARPS][QK_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
@@ -34,8 +34,11 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
   const bool is_q = h < num_q;
   const bool is_k = !is_q && h < num_q + num_kv;
   long long slot = -1;
-  if (!is_q) {
-    if (slot_mapping == nullptr) return;  // this execution reads another one's cache
+  if (!is_q && slot_mapping == nullptr) {
+    // nothing is stored (this execution reads another one's cache); with k_in_place the normed and rotated key
+    // goes back where it came from, as the query does
+    if (!(k_in_place && is_k)) return;
+  } else if (!is_q) {
     slot = slot_mapping[t];
     if (slot < 0) return;  // padding row
     if (slot >= num_slots) {
@@ -64,7 +67,7 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
     for (int e = lane; e < head_dim; e += 32) y[e] = y[e] * rstd * w[e];
   }
   __syncwarp();
-  T* dst = is_q ? src : k_cache + (slot * num_kv + (h - num_q)) * head_dim;
+  T* dst = (is_q || slot < 0) ? src : k_cache + (slot * num_kv + (h - num_q)) * head_dim;
   const int half = rotary_dim / 2;
   int pos = 0;
   if (rotary_dim > 0) {
@@ -189,11 +192,11 @@ qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int nu
   }
 }
 
-extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
-                                       const float* q_w, const float* k_w, float eps, const float* cos_t,
-                                       const float* sin_t, int rotary_dim, int max_positions, const int* positions,
-                                       const int* slot_mapping, void* k_cache, void* v_cache, long long num_slots,
-                                       int* status, void* stream) {
+static int qk_norm_rope_store_impl(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
+                                   const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                   const float* sin_t, int rotary_dim, int max_positions, const int* positions,
+                                   const int* slot_mapping, void* k_cache, void* v_cache, long long num_slots,
+                                   int* status, void* stream, int k_in_place) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0) return ULLM_ERR_BAD_SIZE;
   if (head_dim > QK_MAX_HEAD_DIM || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
@@ -203,7 +206,7 @@ extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num
   const long long units = (long long)tokens * (num_q + 2 * num_kv);
   const long long blocks = (units + QK_WARPS - 1) / QK_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
-  if (dtype == ULLM_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128) &&
+  if (!k_in_place && dtype == ULLM_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128) &&
       (uintptr_t)qkv % 8 == 0 && (slot_mapping == nullptr || ((uintptr_t)k_cache % 8 == 0 && (uintptr_t)v_cache % 8 == 0))) {
     const int warps = 8;
     const int steps = (long long)tokens * (num_q + 2 * num_kv) >= 8192 ? 6 : 1;
@@ -224,16 +227,34 @@ extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<float>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (float*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
-        positions, slot_mapping, (float*)k_cache, (float*)v_cache, num_slots, status);
+        positions, slot_mapping, (float*)k_cache, (float*)v_cache, num_slots, status, k_in_place);
   else if (dtype == ULLM_DTYPE_BF16)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (__nv_bfloat16*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
-        positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status);
+        positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status, k_in_place);
   else if (dtype == ULLM_DTYPE_F16)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<__half>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (__half*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
-        positions, slot_mapping, (__half*)k_cache, (__half*)v_cache, num_slots, status);
+        positions, slot_mapping, (__half*)k_cache, (__half*)v_cache, num_slots, status, k_in_place);
   else
     return ULLM_ERR_BAD_DTYPE;
   return ullm_launch_status();
+}
+
+extern "C" int ullm_qk_norm_rope_store(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
+                                       const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                       const float* sin_t, int rotary_dim, int max_positions, const int* positions,
+                                       const int* slot_mapping, void* k_cache, void* v_cache, long long num_slots,
+                                       int* status, void* stream) {
+  return qk_norm_rope_store_impl(dtype, qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim,
+                                 max_positions, positions, slot_mapping, k_cache, v_cache, num_slots, status, stream, 0);
+}
+
+// Queries AND keys normed (and rotated, if tables are given) where they lie; nothing is stored.  For mixers whose
+// position encoding has code of its own: it changes q and k afterwards, and a second call (no weights, no tables,
+// a slot mapping) stores the keys and values.
+extern "C" int ullm_qk_norm_in_place(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
+                                     const float* q_w, const float* k_w, float eps, int* status, void* stream) {
+  return qk_norm_rope_store_impl(dtype, qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, nullptr, nullptr, 0, 0,
+                                 nullptr, nullptr, nullptr, nullptr, 0, status, stream, 1);
 }

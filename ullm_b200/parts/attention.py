@@ -131,8 +131,18 @@ class PagedAttention(Mixer):
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         slot_mapping = g.slot_mapping if cache.writes else None
         fuse = None
-        if K.decode_fusion_applies(ctx, qkv, self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, rotary_dim,
-                                   tables.get("cos"), ragged):
+        if self.position is not None and self.position.transforms_qk():
+            # an encoding with code of its own: norm q and k, let it change them, then store the keys and values
+            if q_w is not None or k_w is not None:
+                K.qk_norm_in_place(qkv, self.num_heads, self.num_kv_heads, self.head_dim, q_w, k_w, eps)
+            self.position.apply(qkv[:, :self.q_size].view(T, self.num_heads, self.head_dim),
+                                qkv[:, self.q_size:self.q_size + self.kv_size].view(T, self.num_kv_heads, self.head_dim),
+                                ctx.positions)
+            if slot_mapping is not None:
+                K.qk_norm_rope_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim, None, None, 0.0, None, None, 0,
+                                     ctx.positions, slot_mapping, cache.k_pages, cache.v_pages)
+        elif K.decode_fusion_applies(ctx, qkv, self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, rotary_dim,
+                                     tables.get("cos"), ragged):
             # a decode step: the attention kernel norms and rotates q and k and writes k and v to their pages itself
             fuse = dict(q_w=q_w, k_w=k_w, eps=eps, cos=tables["cos"], sin=tables["sin"], positions=ctx.positions,
                         slot_mapping=slot_mapping)

@@ -11,7 +11,8 @@ Interfaces (what a new part must have):
 * Norm: `forward(x, residual=None, out=None) -> out`; with a residual the sum
   x + residual is formed in 32-bit, written back to `residual`, and normed.
 * PositionEncoding: `tables() -> dict of device tensors` handed to the mixer's
-  kernel, plus `rotary_dim`.
+  kernel, plus `rotary_dim`; or `transforms_qk() -> True` and `apply(q, k,
+  positions)` for an encoding that is no rotation by tables.
 * Mixer: `cache_need() -> CacheNeed | None`, `state_need() -> StateNeed | None`,
   `graph_key(ctx)` (what of a decode step changes its launches, default nothing),
   `forward(x[T, hidden], ctx, cache) -> [T, hidden]`; `cache` is the
@@ -112,10 +113,27 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """Two kinds.  A rotation by per-position tables hands `tables()` (`cos` / `sin` rows of `rotary_dim / 2`
+    floats per position) to the mixer's kernels, which rotate in 32-bit registers.  Any other encoding that acts
+    on queries and keys answers True from `transforms_qk()` and does its work in `apply`, with device code of
+    its own; the mixer then norms q and k first and stores the keys afterwards.  (An encoding that biases the
+    SCORES by both positions would need an argument of the attention kernels; there is none yet.)"""
+
     rotary_dim: int = 0
+
+    def build_tables(self, device) -> None:
+        """Called once, when the mixer's parameters exist: put what the encoding needs on `device`."""
 
     def tables(self) -> dict[str, torch.Tensor]:
         return {}
+
+    def transforms_qk(self) -> bool:
+        return False
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        """Changes this step's queries q [T, heads, head_dim] and keys k [T, kv heads, head_dim] in place
+        (views of the projection's output); positions [T] int32 on the device."""
+        raise NotImplementedError
 
 
 class Mixer(Part):
