@@ -235,12 +235,13 @@ def test_random_workloads_always_finish(seed):
 
 
 def test_decode_graph_sizes_and_padding():
-    """ullm/core/model_runner.py:431-433 records 1, 2, 4, 8 and then steps of 16; here 8 is left out (a batch of 5
-    to 15 is padded to 16, which measured faster) and the largest batch always has a graph of its own size."""
+    """ullm/core/model_runner.py:431-433 records 1, 2, 4, 8 and then steps of 16; the same here, sizes may be
+    left out (their batches are padded to the next one), and the largest batch always has a graph of its own size."""
     from ullm_b200.engine.graph import graph_batch_sizes
 
-    assert graph_batch_sizes(64) == [1, 2, 4, 16, 32, 48, 64]
-    assert graph_batch_sizes(50) == [1, 2, 4, 16, 32, 48, 50]
+    assert graph_batch_sizes(64) == [1, 2, 4, 8, 16, 32, 48, 64]
+    assert graph_batch_sizes(64, skip=(8,)) == [1, 2, 4, 16, 32, 48, 64]
+    assert graph_batch_sizes(50) == [1, 2, 4, 8, 16, 32, 48, 50]
     assert graph_batch_sizes(8) == [1, 2, 4, 8]
     assert graph_batch_sizes(3) == [1, 2, 3]
     assert graph_batch_sizes(1) == [1]

@@ -60,7 +60,6 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float cm[CL ? 16 * (D + 2) : 1];  // this block's merged partial (cluster form): [head][D outputs, max, sum]
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;       // k-steps of the score product
   constexpr int NT_O = D / 8;          // n-tiles of the output
@@ -81,6 +80,49 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
   const int tiles = (w_end - w_begin + DEC_TILE - 1) / DEC_TILE;
   const int* bt = block_table + (long long)req_slots[b] * max_pages;
   const long long kv_row = (long long)num_kv * D;
+
+  unsigned char* ring = smem + warp * S::WARP_BYTES;
+  auto issue = [&](int tile) {
+    unsigned char* kbuf = ring + (tile % DEC_STAGES) * 2 * S::TILE_BYTES;
+    unsigned char* vbuf = kbuf + S::TILE_BYTES;
+    const int base = w_begin + tile * DEC_TILE;
+    // lanes 0..15 look up the slot of row `lane`
+    long long my_slot = -1;
+    if (lane < DEC_TILE) {
+      const int key = base + lane;
+      if (key < w_end) {
+        const int page = bt[key / page_size];
+        if (page < 0 || page >= num_pages) ullm_report(status, ULLM_STATUS_PAGE, b, page);
+        else my_slot = (long long)page * page_size + key % page_size;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < DEC_TILE * CHUNKS / 32; ++i) {
+      const int c = i * 32 + lane;
+      const int row = c / CHUNKS, ch = c % CHUNKS;
+      const long long slot = __shfl_sync(0xffffffffu, my_slot, row);
+      const bool ok = slot >= 0;
+      const long long off = ok ? (slot * kv_row + (long long)kh * D + ch * 8) : 0;
+      const int sw = row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16);
+      cp_async_16(kbuf + sw, k_cache + off, ok);
+      cp_async_16(vbuf + sw, v_cache + off, ok);
+    }
+  };
+
+  // Under programmatic dependent launch the kernel in front (the projection that writes q and the new key and
+  // value) may still be running here.  The pages of the older keys do not depend on it (block tables and lengths
+  // were staged before the step's first kernel; this layer's pages are written by this kernel alone), so a kernel
+  // that prepares the new key itself starts its first tiles' copies now and waits only then.  What a copy finds
+  // in the newest key's slot does not matter: that row is replaced in shared memory below.
+  const bool early = fu.cos_t != nullptr;
+  if (early) {
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+      if (s < tiles) issue(s);
+      cp_async_commit();
+    }
+  }
+  pdl_wait();
 
   // ---- Q fragments (A operand), rows >= group are zero -------------------------------
   unsigned qa[KSTEPS][4];
@@ -202,43 +244,17 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     }
   }
 
-  unsigned char* ring = smem + warp * S::WARP_BYTES;
-  auto issue = [&](int tile) {
-    unsigned char* kbuf = ring + (tile % DEC_STAGES) * 2 * S::TILE_BYTES;
-    unsigned char* vbuf = kbuf + S::TILE_BYTES;
-    const int base = w_begin + tile * DEC_TILE;
-    // lanes 0..15 look up the slot of row `lane`
-    long long my_slot = -1;
-    if (lane < DEC_TILE) {
-      const int key = base + lane;
-      if (key < w_end) {
-        const int page = bt[key / page_size];
-        if (page < 0 || page >= num_pages) ullm_report(status, ULLM_STATUS_PAGE, b, page);
-        else my_slot = (long long)page * page_size + key % page_size;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < DEC_TILE * CHUNKS / 32; ++i) {
-      const int c = i * 32 + lane;
-      const int row = c / CHUNKS, ch = c % CHUNKS;
-      const long long slot = __shfl_sync(0xffffffffu, my_slot, row);
-      const bool ok = slot >= 0;
-      const long long off = ok ? (slot * kv_row + (long long)kh * D + ch * 8) : 0;
-      const int sw = row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16);
-      cp_async_16(kbuf + sw, k_cache + off, ok);
-      cp_async_16(vbuf + sw, v_cache + off, ok);
-    }
-  };
-
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[NT_O][4];
 #pragma unroll
   for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
+  if (!early) {
 #pragma unroll
-  for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < tiles) issue(s);
-    cp_async_commit();
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+      if (s < tiles) issue(s);
+      cp_async_commit();
+    }
   }
   for (int it = 0; it < tiles; ++it) {
     if (it + DEC_STAGES - 1 < tiles) issue(it + DEC_STAGES - 1);

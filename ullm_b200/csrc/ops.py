@@ -119,19 +119,31 @@ class Kernels:
         self.attention_path = None  # which attention kernel the last call chose (tests read it)
         self.launches = 0  # hand-written kernels launched (graph replays add what they captured)
 
+    def begin_step(self, rows: int, dtype) -> None:
+        """Called by the step function before a step's kernels are launched (or recorded into a CUDA graph): with
+        the automatic policy, programmatic dependent launch is on for exactly the steps whose products are all the
+        stream kernel (bfloat16, at most `stream_all_rows` rows), and off otherwise."""
+        if self.pdl_mode == "auto":
+            self.set_pdl(bool(dtype == torch.bfloat16 and self.small_m_mode == "auto" and rows <= self.stream_all_rows))
+
     # -- switches -----------------------------------------------------------
     SWITCHES = ("ULLM_B200_PDL", "ULLM_B200_DECODE_SPLIT_TARGET", "ULLM_B200_TC_ATTN", "ULLM_B200_DECODE_CLUSTER",
                 "ULLM_B200_FUSE_DECODE_ROPE", "ULLM_B200_MIXED_DECODE_ROWS", "ULLM_B200_DECODE_TC",
                 "ULLM_B200_DECODE_BALANCED", "ULLM_B200_SMALL_M_LINEAR", "ULLM_B200_STREAM_WEIGHT_MB",
-                "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS", "ULLM_B200_FUSED_TAIL_ROWS")
+                "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS", "ULLM_B200_FUSED_TAIL_ROWS",
+                "ULLM_B200_STREAM_ALL_ROWS")
 
     def apply_switches(self, env) -> None:
         """Sets every kernel choice from `env` (a mapping; the process environment at start-up): a switch that is
         not in it takes its default.  All switches are optional; the defaults are what was measured fastest."""
         get = env.get
-        # programmatic dependent launch for every kernel of the library (about + 1 % at Qwen3-0.6B sizes with the
-        # stream product, - 1 to 2 % at Qwen3-8B sizes with the library's products in between)
-        self.set_pdl(get("ULLM_B200_PDL", "0") == "1")
+        # programmatic dependent launch for every kernel of the library: "auto" (the default) for the steps whose
+        # products are all the stream kernel (see `begin_step`), where its ring fills with weights while the kernel
+        # in front drains (Qwen3-8B sizes, batch 1: 3.60 -> 3.38 ms per step); "1" always, "0" never (with the
+        # library's products in between it costs 1 to 2 %: waiting blocks hold SM slots and gain nothing)
+        mode = get("ULLM_B200_PDL", "auto")
+        self.pdl_mode = {"1": True, "0": False}.get(mode, "auto")
+        self.set_pdl(self.pdl_mode is True)
         # blocks the per-request decode attention aims for when it splits the requests' key ranges
         self.decode_split_target = int(get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         # prompt attention on the tcgen05 tensor cores (head size 128); 0: the mma.sync kernel
@@ -160,6 +172,9 @@ class Kernels:
         # kernel (M <= 64)
         mode = get("ULLM_B200_SMALL_M_LINEAR", "auto")
         self.small_m_mode = {"1": "tcgen05", "0": None, "": "auto"}.get(mode, mode)
+        # "auto": rows up to which EVERY product of a step is the stream kernel (with dependent launch it beats
+        # the library there: Qwen3-8B sizes, 8 requests 4.14 -> 3.90 ms per step, 1 request 3.63 -> 3.38)
+        self.stream_all_rows = int(get("ULLM_B200_STREAM_ALL_ROWS", "8"))
         if self.small_m_mode not in (None, "auto", "tcgen05", "skinny", "stream"):
             raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: auto, 0, stream, skinny or tcgen05")
         self.stream_weight_bytes = int(get("ULLM_B200_STREAM_WEIGHT_MB", "16")) << 20  # "auto": weights up to this
@@ -269,8 +284,9 @@ class Kernels:
     def set_pdl(self, on: bool) -> None:
         """Programmatic dependent launch for every kernel of the library: a kernel's launch and
         set-up overlap the tail of the kernel before it in the stream."""
-        self.lib.ullm_set_pdl(1 if on else 0)
-        self.pdl = bool(on)
+        if bool(on) != self.pdl:
+            self.lib.ullm_set_pdl(1 if on else 0)
+            self.pdl = bool(on)
 
     # -- status word ----------------------------------------------------------
     def raise_on_status(self) -> None:
@@ -485,7 +501,10 @@ class Kernels:
         if self.small_m_mode == "stream":
             return x.shape[0] <= self.stream_rows and self.stream_linear(x, weight, out, bias, act)
         if self.small_m_mode == "auto":
-            return (x.shape[0] <= self.stream_rows and weight.numel() * weight.element_size() <= self.stream_weight_bytes
+            rows = x.shape[0]
+            return (rows <= self.stream_rows
+                    and (rows <= self.stream_all_rows
+                         or weight.numel() * weight.element_size() <= self.stream_weight_bytes)
                     and self.stream_linear(x, weight, out, bias, act))
         if self.small_m_mode == "tcgen05":
             if x.shape[0] <= 64:

@@ -18,12 +18,12 @@ import torch
 from .batch import StepEntry
 
 
-def graph_batch_sizes(max_bs: int, smallest: int = 1, skip: tuple = (8,)) -> list[int]:
-    """ullm/core/model_runner.py:431-433: 1, 2, 4, 8, then steps of 16 up to max_bs.  Here 8 is left out by
-    default (a batch of 5 to 8 is padded to 16 rows): with the library's products at their timed choice of
-    algorithm, a step of 8 requests takes 4.19 ms recorded at 8 rows and 4.05 ms at 16 (Qwen3-8B sizes), while 1
-    and 2 requests are faster at their own size (3.74 against 3.92 ms, 3.84 against 3.94 ms) and 4 is a tie; the
-    padding rows cost nothing else.  `smallest` drops the sizes below it."""
+def graph_batch_sizes(max_bs: int, smallest: int = 1, skip: tuple = ()) -> list[int]:
+    """ullm/core/model_runner.py:431-433: 1, 2, 4, 8, then steps of 16 up to max_bs.  `smallest` drops the sizes
+    below it, `skip` leaves sizes out (their batches are padded to the next one).  Up to 8 rows a step's products
+    are the weight-streaming kernel under dependent launch, whose cost grows with the rows (Qwen3-8B sizes, 8
+    requests: 3.90 ms recorded at 8 rows, 4.26 at 16); with the library's products 8 requests were faster padded
+    to 16 rows (4.05 against 4.19 ms)."""
     sizes = [b for b in (1, 2, 4, 8) if b <= max_bs and b not in skip] + list(range(16, max_bs + 1, 16))
     if max_bs not in sizes:
         sizes.append(max_bs)
@@ -38,7 +38,8 @@ class DecodeGraphs:
         self.sampler = sampler
         import os
 
-        self.sizes = graph_batch_sizes(max_bs, int(os.environ.get("ULLM_B200_MIN_GRAPH_BATCH", "1")))
+        skip = tuple(int(t) for t in os.environ.get("ULLM_B200_GRAPH_SKIP", "").split(",") if t.strip())
+        self.sizes = graph_batch_sizes(max_bs, int(os.environ.get("ULLM_B200_MIN_GRAPH_BATCH", "1")), skip)
         # (size, the mixers' graph keys) -> (graph, signature, kernels recorded): a step is replayed from a graph
         # that was recorded with the kernels its mixers would choose for it (`Mixer.graph_key`)
         self.graphs: dict[tuple, tuple] = {}

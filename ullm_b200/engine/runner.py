@@ -321,6 +321,8 @@ class ModelRunner:
         return logits
 
     def run_model(self, ctx: StepContext) -> torch.Tensor | None:
+        if self.device.type == "cuda":
+            kernels().begin_step(ctx.num_tokens, self.dtype)  # (kernel choices that go by the size of the step)
         return self.model.forward(ctx, self.cache.layer_caches(ctx.groups))
 
     def commit(self, entries: list[StepEntry]) -> None:
