@@ -102,6 +102,7 @@ class Kernels:
         self.lib = ctypes.CDLL(self.lib_path)
         self._declare()
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self.sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self._f32_out_mm = None
         self._lin_ws = None  # partial sums and tile counters of the tcgen05 product, made at its first use
         self._lin_counters = None
@@ -150,8 +151,7 @@ class Kernels:
         self.use_tcgen05_attention = get("ULLM_B200_TC_ATTN", "1") == "1"
         # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
         # scratch arrays and a second kernel
-        # ("auto": for one or two requests, where it measured 1.5 % faster per step; at eight requests it is 1.5 %
-        # slower than the merge kernel)
+        # ("auto": for steps of at most 8 rows; "1" / "0": always / never, with `decode_split_target` splits)
         mode = get("ULLM_B200_DECODE_CLUSTER", "auto")
         self.decode_cluster_merge = {"1": True, "0": False}.get(mode, "auto")
         # decode steps: the per-request decode attention kernel applies the q/k norm and the rotation and writes the
@@ -725,9 +725,20 @@ class Kernels:
             self.launches += 1  # the merge of the shared pairs
             self.attention_path = "decode_tcgen05" if tc else "decode_balanced"
             return
-        cluster = T <= 2 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
+        # Up to 8 rows (the steps that run under dependent launch) the splits of a request merge inside a
+        # thread-block cluster: no merge kernel stands between the attention and the output projection, whose ring
+        # fills meanwhile.  The cluster is the largest power of two that keeps all blocks in one wave of two per
+        # SM (8 requests x 8 kv heads: 4 splits, 3.59 ms per step against 3.87 with 7 splits and the merge kernel;
+        # 3, 5, 6, 7 and 8 splits: 3.70, 4.06, 3.98, 3.93, 4.06).  More rows: splits by `decode_split_target`,
+        # merged by the second kernel.
+        cluster = T <= 8 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
         self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
-        splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
+        if cluster and self.decode_cluster_merge == "auto":
+            splits = 8
+            while splits > 1 and T * num_kv * splits > 2 * self.sm_count:
+                splits //= 2
+        else:
+            splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
         # (splits x rows stays below the blocks aimed for, per kv head, plus one split per row)
         most = num_q * (self.decode_split_target // num_kv + max(T, getattr(ctx.workspace, "max_requests", 0)))
         scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32,
