@@ -73,6 +73,9 @@ class CpuKernels:
     def layer_tail_applies(self, *args, **kwargs):
         return False
 
+    def stream_chain_applies(self, *args, **kwargs):
+        return False
+
     def decode_fusion_applies(self, *args, **kwargs):
         return False  # the stand-in always prepares q and k in a step of their own
 

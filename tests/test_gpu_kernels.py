@@ -672,6 +672,49 @@ def test_fused_layer_tail(M, H, QD, I, act):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+@pytest.mark.parametrize("M,H,QD,I,act", [
+    (8, 256, 256, 256, 0), (16, 520, 776, 1000, 0), (3, 4096, 4096, 12288, 0), (1, 1024, 2048, 3072, 1), (11, 80, 72, 176, 1),
+])
+def test_stream_products_with_the_norm_folded_between_them(M, H, QD, I, act):
+    """Three stream products as a block chains them in small steps: the output projection adds the residual and
+    leaves r * w and the units' sums of squares, the gate / up product multiplies its sums by the rows' 1 / rms
+    before the activation, the down projection adds the residual; against the same chain in float32 with the
+    roundings of the separate kernels.  Sizes with clusters (narrow outputs) and without, K and N that are no
+    multiples of the tiles."""
+    bf = torch.bfloat16
+    attn = rnd(M, QD, seed=210, dtype=bf)
+    res0 = rnd(M, H, seed=211, dtype=bf)
+    w_o = rnd(H, QD, seed=212, dtype=bf, scale=QD ** -0.5)
+    w_gu = rnd(2 * I, H, seed=213, dtype=bf, scale=H ** -0.5)
+    w_d = rnd(H, I, seed=214, dtype=bf, scale=I ** -0.5)
+    norm_w = (1.0 + 0.1 * rnd(H, seed=215, dtype=torch.float32)).contiguous()
+    eps = 1e-6
+    s1 = res0.float() + attn.float() @ w_o.float().t()
+    r1 = s1.to(bf)
+    h = (s1 * torch.rsqrt(s1.pow(2).mean(-1, keepdim=True) + eps) * norm_w).to(bf)
+    y = h.float() @ w_gu.float().t()
+    g, u = y[:, :I], y[:, I:]
+    a = ((g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u).to(bf)
+    ref = (r1.float() + a.float() @ w_d.float().t()).to(bf).float()
+    res = res0.clone()
+    operand = torch.empty(M, H, dtype=bf, device="cuda")
+    sq = torch.full((K().stream_sq_floats(H),), float("nan"), device="cuda")
+    work = torch.empty(M, I, dtype=bf, device="cuda")
+    assert K().stream_linear(attn, w_o, res, None, None, res, norm_behind=(norm_w, operand, sq))
+    assert K().stream_linear(operand, w_gu, work, None, act, norm_in_front=(sq, H, eps))
+    assert K().stream_linear(work, w_d, res, None, None, res)
+    K().raise_on_status()
+    assert torch.equal(res0.float() + 0, res0.float())  # (inputs untouched)
+    aerr = (work.float() - a.float()).abs().max().item() / max(a.float().abs().max().item(), 1e-6)
+    assert aerr <= 2e-2, f"activation: max err {aerr:.3e} of scale"
+    err = (res.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+    assert err <= 2e-2, f"residual after the layer: max err {err:.3e} of scale"
+    # the sums of squares add up to the rows' sums
+    got = sq.view(-1, 16).sum(0)[:M].cpu()
+    want = s1.pow(2).sum(-1).cpu()
+    assert torch.allclose(got, want, rtol=2e-2), (got, want)
+
+
 def test_skinny_linear_is_deterministic_and_refuses_what_it_does_not_take():
     x = rnd(16, 4096, seed=70, dtype=torch.bfloat16)
     w = rnd(512, 4096, seed=71, dtype=torch.bfloat16, scale=0.05)

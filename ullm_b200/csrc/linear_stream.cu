@@ -44,6 +44,16 @@ struct LsParams {
   int stages;
   int chunked;                    // K is a multiple of 64: a stage comes in by one copy per matrix (3-D boxes)
   int ksplit;                     // 1, 2, 4 or 8: blocks of a cluster that share a unit, each with a range of K
+  // An RMSNorm folded around two products (rmsnorm(r) * w = (1 / rms(r)) * (r * w)):
+  //   the product in FRONT of the norm (plain, with a residual) also writes r * pre_w, rounded once, as the
+  //   next product's operand, and per unit and 16-row half the rows' sums of squares of r;
+  const float* pre_w;             // [n_out] norm weight, or null
+  __nv_bfloat16* pre_out;         // [M, n_out]
+  float* sq_out;                  // [units][2][16]
+  //   the product BEHIND it multiplies its 32-bit sums by the rows' 1 / rms before bias and activation.
+  const float* sq_in;             // [sq_count][16] partial sums of squares, or null
+  int sq_count;
+  float sq_inv_cols, sq_eps;      // 1 / (columns of the normed row), the norm's eps
   int* status;
 };
 
@@ -89,6 +99,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
   extern __shared__ unsigned char ls_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[LS_MAX_STAGES], empty_bar[LS_MAX_STAGES];
   __shared__ __align__(8) uint64_t peer_bar;  // rank 0: the peers' partial sums of the current unit have arrived
+  __shared__ float rstd_s[16], part_s[16][17];  // the rows' 1 / rms (a norm folded in front of this product)
   __shared__ int abort_flag;
   pdl_launch_dependents();
   unsigned char* ring = (unsigned char*)(((uintptr_t)ls_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -186,6 +197,29 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
   } else {
     // ---- consumers --------------------------------------------------------------------------------
     pdl_wait();
+    if (p.sq_in != nullptr) {
+      // the rows' 1 / rms from the partial sums of squares that the product in front left (16 parts per row, all
+      // loads of a thread in flight together; parts added in a fixed order)
+      const int m = threadIdx.x & 15, part = threadIdx.x >> 4;
+      const int per = (p.sq_count + 15) / 16;
+      float sum = 0.f;
+      for (int q0 = part * per; q0 < (part + 1) * per && q0 < p.sq_count; q0 += 8) {
+        float v8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          v8[e] = (q0 + e < (part + 1) * per && q0 + e < p.sq_count) ? __ldcg(p.sq_in + (size_t)(q0 + e) * 16 + m) : 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v8[e];
+      }
+      part_s[part][m] = sum;
+      ls_bar_sync_consumers();
+      if (threadIdx.x < 16) {
+        float tot = 0.f;
+        for (int q = 0; q < 16; ++q) tot += part_s[q][threadIdx.x];
+        rstd_s[threadIdx.x] = rsqrtf(tot * p.sq_inv_cols + p.sq_eps);
+      }
+      ls_bar_sync_consumers();
+    }
     const int mt = warp & 1, kq = warp >> 1;
     const int g = lane >> 2, t = lane & 3;
     // ldmatrix row addresses inside a box (rows of 128 bytes, 16-byte chunks XORed with row & 7)
@@ -245,6 +279,9 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
       // finish the unit --------------------------------------------------------------------------------
       const int u = cid + ui * ncl;
       // the end of an output element: bias, activation, residual, one rounding, the store
+      float ss[NT][2];  // (a norm behind this product) sums of squares of this thread's results, per batch row
+#pragma unroll
+      for (int n = 0; n < NT; ++n) ss[n][0] = ss[n][1] = 0.f;
       auto finish = [&](int n_tile, const float (&v)[4], const float (&up)[4]) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -253,9 +290,10 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
           const int m = n_tile * 8 + 2 * t + (i & 1);
           const int col = p.act ? u * 16 + row : u * 32 + mt * 16 + row;  // column of out
           if (m >= p.M || col >= p.n_out) continue;
-          float r = v[i];
+          const float rs = p.sq_in != nullptr ? rstd_s[m] : 1.f;
+          float r = v[i] * rs;
           if (p.act) {
-            float gate = r, upv = up[i];
+            float gate = r, upv = up[i] * rs;
             if (p.bias != nullptr) {
               gate += __bfloat162float(p.bias[col]);
               upv += __bfloat162float(p.bias[half_rows + col]);
@@ -270,6 +308,28 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
             reinterpret_cast<float*>(p.out)[o] = r;
           else
             reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(r);
+          if (p.pre_w != nullptr) {
+            p.pre_out[o] = __float2bfloat16_rn(r * __ldg(p.pre_w + col));
+            ss[n_tile][i & 1] += r * r;
+          }
+        }
+      };
+      // the unit's sums of squares per batch row: over the 8 lanes that share t, then one store each
+      auto store_sq = [&]() {
+        if (p.pre_w == nullptr) return;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float sv = ss[n][e];
+            sv += __shfl_xor_sync(0xffffffffu, sv, 4);
+            sv += __shfl_xor_sync(0xffffffffu, sv, 8);
+            sv += __shfl_xor_sync(0xffffffffu, sv, 16);
+            if (g == 0 && n * 8 + 2 * t + e < 16) p.sq_out[((size_t)u * 2 + mt) * 16 + n * 8 + 2 * t + e] = sv;
+          }
+        if (NT == 1 && g == 0) {  // rows 8 to 15 do not exist
+          p.sq_out[((size_t)u * 2 + mt) * 16 + 8 + 2 * t] = 0.f;
+          p.sq_out[((size_t)u * 2 + mt) * 16 + 8 + 2 * t + 1] = 0.f;
         }
       };
       float v_all[NT][4];  // (clusters) this block's sums of the unit, kept until the peers' have arrived
@@ -303,6 +363,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
         }
         ls_bar_sync_consumers();  // the partial sums are read: the next pass may overwrite them
       }
+      if (p.ksplit == 1 && kq == 0 && !failed) store_sq();
       if (p.ksplit > 1 && kq == 0) {
         // ---- the blocks of the cluster meet: ranks 1.. put their sums into rank 0's buffer (distributed shared
         // memory) and arrive at its barrier; rank 0 adds them in rank order and finishes the unit.  (The host
@@ -330,6 +391,7 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
               }
               finish(n, v_all[n], zero);
             }
+            store_sq();
           }
         }
       }
@@ -416,10 +478,32 @@ static int ls_launch(int which, const CUtensorMap& wm, const CUtensorMap& wm32, 
   return ULLM_OK;
 }
 
+// Floats of `sq_out` for a product with N output columns: [units][2][16].
+extern "C" long long ullm_linear_stream_sq_floats(int N) { return (long long)((N + 31) / 32) * 2 * 16; }
+
 // act: 0 none, 1 silu gate, 2 gelu_tanh gate (weight = [gate rows; up rows], out [M, N / 2]).
 // residual: null or [M, n_out] bfloat16, added to the product in 32-bit before the one rounding.
+// pre_w / pre_out / sq_out (all or none; plain products of at most 16 rows): also write result * pre_w and the
+// units' sums of squares, for an RMSNorm folded behind this product.  sq_in / sq_count / sq_cols / sq_eps: the sums
+// of squares that such a product left; this product multiplies its sums by the rows' 1 / rms.
+extern "C" int ullm_linear_stream_norm(const void* x, const void* w, const void* bias, const void* residual, void* out,
+                                       int M, int N, int K, int out_f32, int act, const float* pre_w, void* pre_out,
+                                       float* sq_out, const float* sq_in, int sq_count, int sq_cols, float sq_eps,
+                                       int* status, void* stream);
+
 extern "C" int ullm_linear_stream(const void* x, const void* w, const void* bias, const void* residual, void* out,
                                   int M, int N, int K, int out_f32, int act, int* status, void* stream) {
+  return ullm_linear_stream_norm(x, w, bias, residual, out, M, N, K, out_f32, act, nullptr, nullptr, nullptr, nullptr, 0,
+                                 0, 0.f, status, stream);
+}
+
+extern "C" int ullm_linear_stream_norm(const void* x, const void* w, const void* bias, const void* residual, void* out,
+                                       int M, int N, int K, int out_f32, int act, const float* pre_w, void* pre_out,
+                                       float* sq_out, const float* sq_in, int sq_count, int sq_cols, float sq_eps,
+                                       int* status, void* stream) {
+  if ((pre_w != nullptr) != (pre_out != nullptr) || (pre_w != nullptr) != (sq_out != nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (pre_w != nullptr && (act != 0 || M > 16)) return ULLM_ERR_UNSUPPORTED;
+  if (sq_in != nullptr && (sq_count <= 0 || sq_cols <= 0 || M > 16)) return ULLM_ERR_BAD_SIZE;
   if (!ullm_linear_stream_supported(M, N, K)) return ULLM_ERR_UNSUPPORTED;
   if (act < 0 || act > 2 || (act && (N % 2))) return ULLM_ERR_BAD_SIZE;
   if (g_ls_sms == 0) {
@@ -452,6 +536,13 @@ extern "C" int ullm_linear_stream(const void* x, const void* w, const void* bias
   p.stages = 0;
   p.chunked = chunked;
   p.ksplit = 1;
+  p.pre_w = pre_w;
+  p.pre_out = (__nv_bfloat16*)pre_out;
+  p.sq_out = sq_out;
+  p.sq_in = sq_in;
+  p.sq_count = sq_count;
+  p.sq_inv_cols = sq_cols > 0 ? 1.f / (float)sq_cols : 0.f;
+  p.sq_eps = sq_eps;
   p.status = status;
   if (NT == 1) return ls_launch<1>(0, wm, wm32, xm, p, (cudaStream_t)stream);
   if (NT == 2) return ls_launch<2>(1, wm, wm32, xm, p, (cudaStream_t)stream);

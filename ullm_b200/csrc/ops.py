@@ -132,7 +132,7 @@ class Kernels:
                 "ULLM_B200_FUSE_DECODE_ROPE", "ULLM_B200_MIXED_DECODE_ROWS", "ULLM_B200_DECODE_TC",
                 "ULLM_B200_DECODE_BALANCED", "ULLM_B200_SMALL_M_LINEAR", "ULLM_B200_STREAM_WEIGHT_MB",
                 "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS", "ULLM_B200_FUSED_TAIL_ROWS",
-                "ULLM_B200_STREAM_ALL_ROWS")
+                "ULLM_B200_STREAM_ALL_ROWS", "ULLM_B200_CHAIN_NORMS")
 
     def apply_switches(self, env) -> None:
         """Sets every kernel choice from `env` (a mapping; the process environment at start-up): a switch that is
@@ -175,6 +175,9 @@ class Kernels:
         # "auto": rows up to which EVERY product of a step is the stream kernel (with dependent launch it beats
         # the library there: Qwen3-8B sizes, 8 requests 4.14 -> 3.90 ms per step, 1 request 3.63 -> 3.38)
         self.stream_all_rows = int(get("ULLM_B200_STREAM_ALL_ROWS", "8"))
+        # in those steps a block folds its feed-forward norm between the output projection and the gate / up
+        # product (one kernel less per layer); 0: the norm stays a kernel of its own
+        self.chain_norms = get("ULLM_B200_CHAIN_NORMS", "1") == "1"
         if self.small_m_mode not in (None, "auto", "tcgen05", "skinny", "stream"):
             raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: auto, 0, stream, skinny or tcgen05")
         self.stream_weight_bytes = int(get("ULLM_B200_STREAM_WEIGHT_MB", "16")) << 20  # "auto": weights up to this
@@ -211,6 +214,7 @@ class Kernels:
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_stream": [P, P, P, P, P, I, I, I, I, I, P, P],
+            "ullm_linear_stream_norm": [P, P, P, P, P, I, I, I, I, I, P, P, P, P, I, I, F, P, P],
             "ullm_layer_tail_fused": [P, P, P, P, P, P, P, P, F, I, I, I, I, I, P, P, P, P],
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
@@ -269,6 +273,8 @@ class Kernels:
         L.ullm_layer_tail_fused_last_grid.restype = c_int
         L.ullm_linear_stream_supported.argtypes = [I, I, I]
         L.ullm_linear_stream_supported.restype = c_int
+        L.ullm_linear_stream_sq_floats.argtypes = [I]
+        L.ullm_linear_stream_sq_floats.restype = c_longlong
         L.ullm_linear_stream_blocks_per_sm.argtypes = [I]
         L.ullm_linear_stream_blocks_per_sm.restype = None
         L.ullm_linear_stream_smem_kb.argtypes = [I]
@@ -361,11 +367,18 @@ class Kernels:
                     f"linear_skinny ({M}x{K} . {N}x{K})")
         return True
 
-    def stream_linear(self, x, weight, out, bias=None, act: int | None = None, residual=None) -> bool:
+    def stream_linear(self, x, weight, out, bias=None, act: int | None = None, residual=None, norm_behind=None,
+                      norm_in_front=None) -> bool:
         """The weight-streaming product for few rows (M <= 32; csrc/linear_stream.cu): a TMA ring per block that
         is filled with weight tiles before the kernel in front has finished (programmatic dependent launch),
         mma.sync on the swizzled tiles.  Same contract as `small_m_linear`; `residual` ([M, n_out], bfloat16;
-        may be `out`) is added to the product in 32-bit before the one rounding."""
+        may be `out`) is added to the product in 32-bit before the one rounding.
+
+        An RMSNorm between two such products costs no kernel (rmsnorm(r) * w = (1 / rms(r)) * (r * w)):
+        `norm_behind=(w, operand, sq)` on the product in front of the norm also writes result * w to `operand`
+        ([M, n_out] bfloat16) and the units' sums of squares to `sq` (float32, `stream_sq_floats(n_out)`);
+        `norm_in_front=(sq, cols, eps)` on the product behind it (whose x is that operand) multiplies its sums by
+        the rows' 1 / rms.  Both for at most 16 rows."""
         M, K = x.shape
         N = weight.shape[0]
         n_out = N // 2 if act is not None else N
@@ -378,11 +391,38 @@ class Kernels:
                 or not self.lib.ullm_linear_stream_supported(M, N, K)
                 or x.data_ptr() % 16 or weight.data_ptr() % 16):
             return False
-        self._check(self.lib.ullm_linear_stream(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
-                                                1 if out.dtype == torch.float32 else 0,
-                                                0 if act is None else act + 1, _ptr(self.status), _stream()),
-                    f"linear_stream ({M}x{K} . {N}x{K})")
+        pre_w = pre_out = sq_out = sq_in = None
+        sq_count, sq_cols, sq_eps = 0, 0, 0.0
+        if norm_behind is not None:
+            pre_w, pre_out, sq_out = norm_behind
+            _need(pre_w, "norm weight", torch.float32)
+            _need(pre_out, "normed operand", torch.bfloat16)
+            _need(sq_out, "sums of squares", torch.float32)
+            if (act is not None or M > 16 or pre_w.numel() != n_out or pre_out.shape != (M, n_out)
+                    or sq_out.numel() < self.stream_sq_floats(n_out)):
+                raise KernelError("stream_linear: norm_behind needs a plain product of at most 16 rows, a weight per "
+                                  "output column, an operand of the output's shape and room for the sums of squares")
+        if norm_in_front is not None:
+            sq_in, sq_cols, sq_eps = norm_in_front
+            _need(sq_in, "sums of squares", torch.float32)
+            if M > 16 or sq_cols != K or sq_in.numel() < self.stream_sq_floats(K):
+                raise KernelError("stream_linear: norm_in_front needs at most 16 rows and the sums of squares of K columns")
+            sq_count = self.stream_sq_floats(K) // 16
+        self._check(self.lib.ullm_linear_stream_norm(
+            _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, 1 if out.dtype == torch.float32 else 0,
+            0 if act is None else act + 1, _ptr(pre_w), _ptr(pre_out), _ptr(sq_out), _ptr(sq_in), sq_count, int(sq_cols),
+            float(sq_eps), _ptr(self.status), _stream()), f"linear_stream ({M}x{K} . {N}x{K})")
         return True
+
+    def stream_sq_floats(self, n_out: int) -> int:
+        """Floats of the sums-of-squares array that `stream_linear(norm_behind=...)` fills for `n_out` columns."""
+        return int(self.lib.ullm_linear_stream_sq_floats(int(n_out)))
+
+    def stream_chain_applies(self, rows: int, dtype) -> bool:
+        """True for the steps whose products are all the stream kernel (the automatic policy, bfloat16, few rows):
+        a block may then chain its products with the norm folded between them."""
+        return bool(self.small_m_mode == "auto" and dtype == torch.bfloat16 and rows <= min(self.stream_all_rows, 16)
+                    and self.chain_norms)
 
     def layer_tail_applies(self, rows: int, dtype, hidden: int, attn_width: int, intermediate: int) -> bool:
         """True when `fused_layer_tail` takes these sizes and the switch is on: decode-sized batches (at most

@@ -7,6 +7,8 @@ first block takes residual = x; afterwards each norm is the fused form
 
 from __future__ import annotations
 
+import torch
+
 from ..csrc import kernels
 from .base import Block
 from .registry import register_block
@@ -64,10 +66,40 @@ class PreNormResidualBlock(Block):
             work = ctx.workspace.tokens("mlp.act", T, w_down.shape[1], residual.dtype)
             kernels().fused_layer_tail(a, residual, work, w_o, w_gate_up, w_down, norm_w, eps, act)
             return None, residual
+        chain = self._fusable_chain(T, residual)
+        if chain is not None:
+            # few rows, every product the weight-streaming kernel: the output projection adds the residual itself
+            # and leaves r * w and the sums of squares for the norm, the gate / up product applies 1 / rms to its
+            # sums, the down projection adds the residual: three kernels, no norm kernel, nothing pending
+            K, (w_o, norm_w, eps, w_gate_up, w_down, act) = kernels(), chain
+            a = self.mixer.forward(h, ctx, cache, project_output=False)
+            H = residual.shape[1]
+            sq = ctx.workspace.get("block.norm_sq", 1, K.stream_sq_floats(H), torch.float32)
+            work = ctx.workspace.tokens("mlp.act", T, w_down.shape[1], residual.dtype)
+            if (K.stream_linear(a, w_o, residual, None, None, residual, norm_behind=(norm_w, h, sq))
+                    and K.stream_linear(h, w_gate_up, work, None, act, norm_in_front=(sq, H, eps))
+                    and K.stream_linear(work, w_down, residual, None, None, residual)):
+                return None, residual
+            raise RuntimeError("the chained products were refused after the sizes had been accepted")
         a = self.mixer.forward(h, ctx, cache)
         self.feed_forward_norm.forward(a, residual, out=h)
         y = self.feed_forward.forward(h, ctx)
         return y, residual
+
+    def _fusable_chain(self, rows: int, residual):
+        """The same parts as `_fusable_tail` needs, when the step's products are all the stream kernel."""
+        if not residual.is_cuda or not kernels().stream_chain_applies(rows, residual.dtype):
+            return None
+        proj, norm, ffn = self.mixer.output_projection(), self.feed_forward_norm.rms_params(), self.feed_forward.gated_weights()
+        if proj is None or norm is None or ffn is None or proj[1] is not None:
+            return None
+        w_o, (norm_w, eps), (w_gate_up, w_down, act) = proj[0], norm, ffn
+        K = kernels()
+        H = residual.shape[1]
+        if (w_o.dtype != torch.bfloat16 or H % 8 or w_o.shape[1] % 8 or w_down.shape[1] % 8
+                or not K.lib.ullm_linear_stream_supported(rows, H, w_o.shape[1])):
+            return None
+        return w_o, norm_w, eps, w_gate_up, w_down, act
 
     def _fusable_tail(self, rows: int, residual):
         """What the fused kernel needs, if this block's parts offer it (a mixer that ends in a bias-free linear
