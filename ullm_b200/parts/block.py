@@ -57,7 +57,7 @@ class PreNormResidualBlock(Block):
             self.mixer_norm.forward(residual, None, out=h)
         else:
             self.mixer_norm.forward(x, residual, out=h)
-        fused = self._fusable_tail(T, residual)
+        fused = self._fusable_tail(T, residual) if ctx.decode_only else None
         if fused is not None:
             # few rows (decode steps): output projection, residual, norm, gated feed-forward and residual in one
             # kernel; the stream then holds everything and nothing is pending
@@ -66,7 +66,7 @@ class PreNormResidualBlock(Block):
             work = ctx.workspace.tokens("mlp.act", T, w_down.shape[1], residual.dtype)
             kernels().fused_layer_tail(a, residual, work, w_o, w_gate_up, w_down, norm_w, eps, act)
             return None, residual
-        chain = self._fusable_chain(T, residual)
+        chain = self._fusable_chain(T, residual) if ctx.decode_only else None
         if chain is not None:
             # few rows, every product the weight-streaming kernel: the output projection adds the residual itself
             # and leaves r * w and the sums of squares for the norm, the gate / up product applies 1 / rms to its
