@@ -173,8 +173,9 @@ class Kernels:
         mode = get("ULLM_B200_SMALL_M_LINEAR", "auto")
         self.small_m_mode = {"1": "tcgen05", "0": None, "": "auto"}.get(mode, mode)
         # "auto": rows up to which EVERY product of a step is the stream kernel (with dependent launch it beats
-        # the library there: Qwen3-8B sizes, 8 requests 4.14 -> 3.90 ms per step, 1 request 3.63 -> 3.38)
-        self.stream_all_rows = int(get("ULLM_B200_STREAM_ALL_ROWS", "8"))
+        # the library there: Qwen3-8B sizes, 8 requests 4.14 -> 3.60 ms per step, 1 request 3.63 -> 3.32, 16 requests
+        # 4.68 -> 4.58)
+        self.stream_all_rows = int(get("ULLM_B200_STREAM_ALL_ROWS", "16"))
         # in those steps a block folds its feed-forward norm between the output projection and the gate / up
         # product (one kernel less per layer); 0: the norm stays a kernel of its own
         self.chain_norms = get("ULLM_B200_CHAIN_NORMS", "1") == "1"
@@ -771,7 +772,7 @@ class Kernels:
         # SM (8 requests x 8 kv heads: 4 splits, 3.59 ms per step against 3.87 with 7 splits and the merge kernel;
         # 3, 5, 6, 7 and 8 splits: 3.70, 4.06, 3.98, 3.93, 4.06).  More rows: splits by `decode_split_target`,
         # merged by the second kernel.
-        cluster = T <= 8 if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
+        cluster = T <= max(8, self.stream_all_rows) if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
         self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
         if cluster and self.decode_cluster_merge == "auto":
             splits = 8
