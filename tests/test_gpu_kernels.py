@@ -702,8 +702,23 @@ def test_stream_products_with_the_norm_folded_between_them(M, H, QD, I, act):
     work = torch.empty(M, I, dtype=bf, device="cuda")
     assert K().stream_linear(attn, w_o, res, None, None, res, norm_behind=(norm_w, operand, sq))
     assert K().stream_linear(operand, w_gu, work, None, act, norm_in_front=(sq, H, eps))
-    assert K().stream_linear(work, w_d, res, None, None, res)
+    # the down projection prepares the NEXT norm the same way (a product that splits K over a cluster when its
+    # output is narrow), and a product with a bias behind that norm applies 1 / rms before the bias
+    norm_w2 = (1.0 + 0.1 * rnd(H, seed=216, dtype=torch.float32)).contiguous()
+    operand2 = torch.empty(M, H, dtype=bf, device="cuda")
+    sq2 = torch.full((K().stream_sq_floats(H),), float("nan"), device="cuda")
+    assert K().stream_linear(work, w_d, res, None, None, res, norm_behind=(norm_w2, operand2, sq2))
+    w_n = rnd(96, H, seed=217, dtype=bf, scale=H ** -0.5)
+    b_n = rnd(96, seed=218, dtype=bf)
+    nxt = torch.empty(M, 96, dtype=bf, device="cuda")
+    assert K().stream_linear(operand2, w_n, nxt, b_n, None, None, norm_in_front=(sq2, H, eps))
     K().raise_on_status()
+    s2 = r1.float() + a.float() @ w_d.float().t()
+    h2 = (s2 * torch.rsqrt(s2.pow(2).mean(-1, keepdim=True) + eps) * norm_w2).to(bf)
+    want_n = h2.float() @ w_n.float().t() + b_n.float()
+    nerr = (nxt.float() - want_n).abs().max().item() / max(want_n.abs().max().item(), 1e-6)
+    assert nerr <= 2e-2, f"product behind the next norm: max err {nerr:.3e} of scale"
+    assert torch.allclose(sq2.view(-1, 16).sum(0)[:M].cpu(), s2.pow(2).sum(-1).cpu(), rtol=2e-2)
     assert torch.equal(res0.float() + 0, res0.float())  # (inputs untouched)
     aerr = (work.float() - a.float()).abs().max().item() / max(a.float().abs().max().item(), 1e-6)
     assert aerr <= 2e-2, f"activation: max err {aerr:.3e} of scale"

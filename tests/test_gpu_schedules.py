@@ -346,7 +346,7 @@ SWITCH_SETTINGS = [
     {"ULLM_B200_DECODE_TC": "1"}, {"ULLM_B200_DECODE_CLUSTER": "1"}, {"ULLM_B200_DECODE_CLUSTER": "0"},
     {"ULLM_B200_FUSE_DECODE_ROPE": "0"}, {"ULLM_B200_TC_ATTN": "0"}, {"ULLM_B200_DECODE_BALANCED": "1"},
     {"ULLM_B200_DECODE_BALANCED": "0"}, {"ULLM_B200_MIXED_DECODE_ROWS": "0"}, {"ULLM_B200_LT_ROWS": "0"},
-    {"ULLM_B200_FUSED_MLP_ROWS": "1"}, {"ULLM_B200_FUSED_TAIL_ROWS": "16"}, {"ULLM_B200_CHAIN_NORMS": "0"},
+    {"ULLM_B200_FUSED_MLP_ROWS": "1"}, {"ULLM_B200_FUSED_TAIL_ROWS": "16"}, {"ULLM_B200_CHAIN_NORMS": "0"}, {"ULLM_B200_CHAIN_NORMS": "1"},
     {"ULLM_B200_STREAM_ALL_ROWS": "0"}, {"ULLM_B200_STREAM_ALL_ROWS": "32"}, {"ULLM_B200_GRAPH_SKIP": "2,8"},
     {"ULLM_B200_PDL": "0"}, {"ULLM_B200_SMALL_M_LINEAR": "0", "ULLM_B200_PDL": "1"}, {"ULLM_B200_DECODE_SPLIT_TARGET": "37"}, {"ULLM_B200_MIN_GRAPH_BATCH": "4"},
 ]

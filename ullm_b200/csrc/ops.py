@@ -178,7 +178,9 @@ class Kernels:
         self.stream_all_rows = int(get("ULLM_B200_STREAM_ALL_ROWS", "16"))
         # in those steps a block folds its feed-forward norm between the output projection and the gate / up
         # product (one kernel less per layer); 0: the norm stays a kernel of its own
-        self.chain_norms = get("ULLM_B200_CHAIN_NORMS", "1") == "1"
+        # 0: norms stay kernels of their own; 1: a block's feed-forward norm is folded between its products in
+        # small decode steps; 2: the next block's first norm too (behind this block's last product)
+        self.chain_norms = int(get("ULLM_B200_CHAIN_NORMS", "2"))
         if self.small_m_mode not in (None, "auto", "tcgen05", "skinny", "stream"):
             raise KernelError(f"ULLM_B200_SMALL_M_LINEAR={mode!r}: auto, 0, stream, skinny or tcgen05")
         self.stream_weight_bytes = int(get("ULLM_B200_STREAM_WEIGHT_MB", "16")) << 20  # "auto": weights up to this
@@ -423,7 +425,7 @@ class Kernels:
         """True for the steps whose products are all the stream kernel (the automatic policy, bfloat16, few rows):
         a block may then chain its products with the norm folded between them."""
         return bool(self.small_m_mode == "auto" and dtype == torch.bfloat16 and rows <= min(self.stream_all_rows, 16)
-                    and self.chain_norms)
+                    and self.chain_norms > 0)
 
     def layer_tail_applies(self, rows: int, dtype, hidden: int, attn_width: int, intermediate: int) -> bool:
         """True when `fused_layer_tail` takes these sizes and the switch is on: decode-sized batches (at most

@@ -99,6 +99,8 @@ class StepContext:
     max_kv_len: int = 1
     decode_only: bool = False
     last_tokens: torch.Tensor | None = None  # int32 [request slots]: what each request sampled last (for id -1)
+    # what a block prepared for the next block's first norm (norm object, operand r * w, sums of squares, eps)
+    folded_norm: object = None
     sum_kv_len: int = 0  # tokens all requests of the step hold after it, padding rows not counted
     num_live_requests: int = 0  # requests of the step without padding rows
 

@@ -116,13 +116,21 @@ class PagedAttention(Mixer):
     def output_projection(self):
         return self.tensors["o_proj.weight"], None
 
+    def takes_input_norm(self):
+        return True
+
     # -- one step ---------------------------------------------------------
-    def forward(self, x, ctx, cache, project_output: bool = True):
+    def forward(self, x, ctx, cache, project_output: bool = True, input_norm=None):
         K = kernels()
         T = x.shape[0]
         ragged = self._ragged(ctx)
         qkv = ctx.workspace.tokens("attn.qkv", T, self.q_size + 2 * self.kv_size, x.dtype)
-        linear(x, self.w_qkv, qkv, self.b_qkv)
+        if input_norm is not None:
+            # x is r * w: the projection multiplies its sums by the rows' 1 / rms (a norm folded in front of it)
+            if not K.stream_linear(x, self.w_qkv, qkv, self.b_qkv, norm_in_front=input_norm):
+                raise RuntimeError("the projection with a folded norm was refused")
+        else:
+            linear(x, self.w_qkv, qkv, self.b_qkv)
         g = cache.group
         tables = self.position.tables() if self.position is not None else {}
         q_w = self.q_norm.tensors["weight"] if self.q_norm is not None else None

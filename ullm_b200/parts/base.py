@@ -153,6 +153,12 @@ class Mixer(Part):
         """Mixers with equal groups give equal graph keys for the same step (one of them is asked)."""
         return type(self)
 
+    def takes_input_norm(self) -> bool:
+        """True when `forward(..., input_norm=(sq, cols, eps))` is understood: x is then r * w (the norm weight
+        already applied) and the mixer's first product multiplies its sums by the rows' 1 / rms, computed from the
+        sums of squares `sq` (see `Kernels.stream_linear`).  Only asked for in small decode steps."""
+        return False
+
     def output_projection(self):
         """(weight [hidden, width], bias or None) if the mixer ends in a plain linear map and can also stop in
         front of it (`forward(..., project_output=False)` then returns its [T, width] input); None otherwise.
@@ -174,5 +180,10 @@ class FeedForward(Part):
 
 
 class Block(Part):
+    takes_next_norm = False  # True: `forward` has a `next_norm=` argument (see PreNormResidualBlock)
+
+    def accepts_folded_norm(self) -> bool:
+        return False
+
     def forward(self, x, residual, ctx, cache):
         raise NotImplementedError

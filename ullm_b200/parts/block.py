@@ -43,21 +43,44 @@ class PreNormResidualBlock(Block):
         size = getattr(self.mixer_norm, "size", 0)
         return size + max(self.mixer.activation_elems(), self.feed_forward.activation_elems())
 
-    def forward(self, x, residual, ctx, cache):
+    takes_next_norm = True  # `forward` accepts the norm that the next block (or nobody) will apply first
+
+    def accepts_folded_norm(self) -> bool:
+        """True when this block can start from an operand r * w and the rows' sums of squares that the block
+        before left (instead of norming r itself): an RMSNorm in front of a mixer whose first step is a product."""
+        return self.mixer_norm.rms_params() is not None and self.mixer.takes_input_norm()
+
+    def forward(self, x, residual, ctx, cache, next_norm=None):
         """x: the previous sub-layer's output that is still to be added to the stream (the embedding for the
         first block, with residual None; None when nothing is pending).  Returns (feed-forward output or None,
-        residual); the caller's next norm adds them."""
+        residual); the caller's next norm adds them.  `next_norm`: the norm the next block will apply to the
+        stream first, if that block `accepts_folded_norm()`; in small decode steps this block's last product then
+        prepares it (`ctx.folded_norm`), and the next block's mixer starts from that."""
         pending = x if x is not None else residual
         T = pending.shape[0]
-        h = ctx.workspace.tokens("block.normed", T, pending.shape[1], pending.dtype)
-        if residual is None:
-            residual = x
-            self.mixer_norm.forward(x, None, out=h)
-        elif x is None:
-            self.mixer_norm.forward(residual, None, out=h)
+        folded, ctx.folded_norm = getattr(ctx, "folded_norm", None), None
+        input_norm = None
+        fused = chain = None
+        if ctx.decode_only and residual is not None:
+            fused = self._fusable_tail(T, residual)
+            chain = self._fusable_chain(T, residual) if fused is None else None
+        if (folded is not None and folded[0] is self.mixer_norm and x is None and residual is not None
+                and chain is not None):
+            # the block before left r * w and the sums of squares: the mixer's first product applies 1 / rms
+            _norm, h, sq, eps = folded
+            input_norm = (sq, residual.shape[1], eps)
         else:
-            self.mixer_norm.forward(x, residual, out=h)
-        fused = self._fusable_tail(T, residual) if ctx.decode_only else None
+            h = ctx.workspace.tokens("block.normed", T, pending.shape[1], pending.dtype)
+            if residual is None:
+                residual = x
+                self.mixer_norm.forward(x, None, out=h)
+            elif x is None:
+                self.mixer_norm.forward(residual, None, out=h)
+            else:
+                self.mixer_norm.forward(x, residual, out=h)
+        if fused is None and chain is None and ctx.decode_only:
+            fused = self._fusable_tail(T, residual)  # the first block: the stream has only now got its rows
+            chain = self._fusable_chain(T, residual) if fused is None else None
         if fused is not None:
             # few rows (decode steps): output projection, residual, norm, gated feed-forward and residual in one
             # kernel; the stream then holds everything and nothing is pending
@@ -66,19 +89,31 @@ class PreNormResidualBlock(Block):
             work = ctx.workspace.tokens("mlp.act", T, w_down.shape[1], residual.dtype)
             kernels().fused_layer_tail(a, residual, work, w_o, w_gate_up, w_down, norm_w, eps, act)
             return None, residual
-        chain = self._fusable_chain(T, residual) if ctx.decode_only else None
         if chain is not None:
             # few rows, every product the weight-streaming kernel: the output projection adds the residual itself
             # and leaves r * w and the sums of squares for the norm, the gate / up product applies 1 / rms to its
-            # sums, the down projection adds the residual: three kernels, no norm kernel, nothing pending
+            # sums, the down projection adds the residual (and prepares the next block's norm the same way):
+            # three kernels, no norm kernel, nothing pending
             K, (w_o, norm_w, eps, w_gate_up, w_down, act) = kernels(), chain
-            a = self.mixer.forward(h, ctx, cache, project_output=False)
+            if input_norm is not None:
+                a = self.mixer.forward(h, ctx, cache, project_output=False, input_norm=input_norm)
+            else:
+                a = self.mixer.forward(h, ctx, cache, project_output=False)
             H = residual.shape[1]
+            hn = ctx.workspace.tokens("block.normed", T, H, residual.dtype)
             sq = ctx.workspace.get("block.norm_sq", 1, K.stream_sq_floats(H), torch.float32)
             work = ctx.workspace.tokens("mlp.act", T, w_down.shape[1], residual.dtype)
-            if (K.stream_linear(a, w_o, residual, None, None, residual, norm_behind=(norm_w, h, sq))
-                    and K.stream_linear(h, w_gate_up, work, None, act, norm_in_front=(sq, H, eps))
-                    and K.stream_linear(work, w_down, residual, None, None, residual)):
+            behind = None
+            nxt = next_norm.rms_params() if next_norm is not None else None
+            if nxt is not None and nxt[0].numel() == H and K.chain_norms >= 2:
+                operand = ctx.workspace.tokens("block.next_operand", T, H, residual.dtype)
+                sq2 = ctx.workspace.get("block.next_sq", 1, K.stream_sq_floats(H), torch.float32)
+                behind = (nxt[0], operand, sq2)
+            if (K.stream_linear(a, w_o, residual, None, None, residual, norm_behind=(norm_w, hn, sq))
+                    and K.stream_linear(hn, w_gate_up, work, None, act, norm_in_front=(sq, H, eps))
+                    and K.stream_linear(work, w_down, residual, None, None, residual, norm_behind=behind)):
+                if behind is not None:
+                    ctx.folded_norm = (next_norm, behind[1], behind[2], nxt[1])
                 return None, residual
             raise RuntimeError("the chained products were refused after the sizes had been accepted")
         a = self.mixer.forward(h, ctx, cache)

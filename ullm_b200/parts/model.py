@@ -79,8 +79,17 @@ class DecoderModel(Part):
         x = ctx.workspace.tokens("model.hidden", T, self.spec.hidden_size, self.dtype)
         self.embedding.forward(ctx.token_ids, x, ctx)
         residual = None
+        n = len(self.schedule)
         for i, e in enumerate(self.schedule):
-            x, residual = self.blocks[e.layer].forward(x, residual, ctx, caches[i])
+            block = self.blocks[e.layer]
+            if block.takes_next_norm:
+                # the norm that the next block applies first, if that block can start from what this one prepares
+                nxt = self.blocks[self.schedule[i + 1].layer] if i + 1 < n else None
+                nxt_norm = nxt.mixer_norm if (nxt is not None and nxt.accepts_folded_norm()) else None
+                x, residual = block.forward(x, residual, ctx, caches[i], next_norm=nxt_norm)
+            else:
+                x, residual = block.forward(x, residual, ctx, caches[i])
+        ctx.folded_norm = None
         return x, residual
 
     def forward(self, ctx, caches):
