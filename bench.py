@@ -703,6 +703,91 @@ def run_decode_attention_probe(args) -> int:
     return 0
 
 
+def run_prefill_attention_probe(args) -> int:
+    """`--probe prefill-attention`: the bfloat16 prompt attention kernels alone (Qwen3-8B head sizes): whole
+    prompts and portions that continue a context; microseconds per call (ten calls back to back in a CUDA graph,
+    median of 5 replays after 2; `--steps 1`: one call per replay),
+    TFLOP/s of the causal work, and the largest difference between the kernels' outputs."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+
+    K = kernels()
+    Hq, Hkv, D, page = (QWEN3_8B["num_attention_heads"], QWEN3_8B["num_key_value_heads"], QWEN3_8B["head_dim"],
+                        args.page_size)
+    pk = peaks()
+
+    class Ctx:
+        pass
+
+    def case(name, q_lens, kv_lens):
+        B, T = len(q_lens), sum(q_lens)
+        per = [-(-n // page) for n in kv_lens]
+        pages = sum(per) + 4
+        kp = torch.randn(pages, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+        vp = torch.randn(pages, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+        bt = torch.full((B, max(per)), -1, dtype=torch.int32)
+        o = 0
+        for i, n in enumerate(per):
+            bt[i, :n] = torch.arange(o, o + n, dtype=torch.int32)
+            o += n
+        bt = bt.cuda()
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+        ctx = Ctx()
+        ctx.decode_only, ctx.num_requests, ctx.max_q_len = False, B, max(q_lens)
+        ctx.cu_q_host = None
+        slots = torch.arange(B, dtype=torch.int32, device="cuda")
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+        token_req = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)]).cuda()
+        res, outs = {}, []
+        for mode in ("pair", "single", "0"):
+            K.tc_attention_mode, K.use_tcgen05_attention = mode, mode != "0"
+            out = torch.empty(T, Hq * D, device="cuda", dtype=torch.bfloat16)
+
+            def call():
+                K.paged_attention(qkv, out, kp, vp, bt, slots, cu, kvl, token_req, Hq, Hkv, D, page, 0, D ** -0.5, ctx)
+
+            call()
+            torch.cuda.synchronize()
+            reps = 1 if args.steps == 1 else 10
+            graph = torch.cuda.CUDAGraph()  # `reps` launches back to back: no host time between them
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(reps):
+                        call()
+            ts = []
+            for _ in range(7):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1000 / reps)
+            res[mode] = statistics.median(ts[2:])
+            outs.append(out.float())
+        K.raise_on_status()
+        # causal work: row t of a request sees kv - q + t + 1 keys; 4 flops per (row, key, head, dim)
+        keys = sum(q * (k - q) + q * (q + 1) // 2 for q, k in zip(q_lens, kv_lens))
+        gf = 4.0 * keys * Hq * D / 1e9
+        tf = {m: gf / res[m] * 1e3 for m in res}
+        print(f"{name:34s} {gf:8.1f} GFLOP   two tiles per block {res['pair']:8.1f} us = {tf['pair']:6.0f} TFLOP/s "
+              f"({tf['pair'] / pk['bf16_tflops']:.2f} of burst)   one tile {res['single']:8.1f} us = {tf['single']:6.0f}   "
+              f"mma.sync {res['0']:8.1f} us = {tf['0']:6.0f}   (largest differences "
+              f"{(outs[0] - outs[1]).abs().max().item():.1e}, {(outs[0] - outs[2]).abs().max().item():.1e})", flush=True)
+
+    cases = [("1 x 2048", [2048], [2048]), ("1 x 512", [512], [512]), ("4 x 512", [512] * 4, [512] * 4),
+             ("1 x 8192", [8192], [8192]), ("1 x 16384", [16384], [16384]),
+             ("2048 behind 6144", [2048], [8192]), ("8 x 256 behind 1792", [256] * 8, [2048] * 8),
+             ("64 + 37 + 300 + 1 (mixed)", [64, 37, 300, 1], [640, 37, 900, 77])]
+    for c in cases:
+        if args.case is None or args.case == c[0]:
+            case(*c)
+    K.apply_switches(os.environ)
+    return 0
+
+
 def run_sampling_probe(args) -> int:
     """`--probe sampling`: the two sampling kernels alone on `--batch` rows of the benchmark's vocabulary, one
     parameter set for all rows; microseconds per call, 20 calls recorded in a CUDA graph (the logits stay in L2,
@@ -988,12 +1073,13 @@ def main() -> int:
                     help="the default line without the 32b and serve-0.6b runs that it adds to `points`")
     ap.add_argument("--no-groups", action="store_true", help="skip the per-kernel-group times of the decode step")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "sampling"],
+    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "prefill-attention", "sampling"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
     ap.add_argument("--only", default=None, choices=["stream", "skinny", "tcgen05", "library", "tail"],
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
     ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
                     help="--probe linear --only: which of the decode step's products")
+    ap.add_argument("--case", default=None, help="run only the case of this name (--probe prefill-attention)")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
     args = ap.parse_args()
@@ -1004,6 +1090,8 @@ def main() -> int:
         args.warmup = 3
     if args.probe == "linear":
         return run_linear_probe(args)
+    if args.probe == "prefill-attention":
+        return run_prefill_attention_probe(args)
     if args.probe == "decode-attention":
         return run_decode_attention_probe(args)
     if args.probe == "sampling":

@@ -148,7 +148,10 @@ class Kernels:
         # blocks the per-request decode attention aims for when it splits the requests' key ranges
         self.decode_split_target = int(get("ULLM_B200_DECODE_SPLIT_TARGET", "400"))
         # prompt attention on the tcgen05 tensor cores (head size 128); 0: the mma.sync kernel
-        self.use_tcgen05_attention = get("ULLM_B200_TC_ATTN", "1") == "1"
+        # prompt attention at head size 128: "1" the tcgen05 kernels (two query tiles per block where a request
+        # brings more than one tile, else one), "pair" / "single" one of them always, "0" the mma.sync kernel
+        self.tc_attention_mode = get("ULLM_B200_TC_ATTN", "1")
+        self.use_tcgen05_attention = self.tc_attention_mode != "0"
         # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
         # scratch arrays and a second kernel
         # ("auto": for steps of at most 8 rows; "1" / "0": always / never, with `decode_split_target` splits)
@@ -214,6 +217,7 @@ class Kernels:
                                             P, P, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_prefill_attention_pair": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_stream": [P, P, P, P, P, I, I, I, I, I, P, P],
@@ -258,6 +262,8 @@ class Kernels:
         L.ullm_prefill_attention_tcgen05_supported.argtypes = [I, I, I, I]
         L.ullm_prefill_attention_tcgen05_supported.restype = c_int
         L.ullm_prefill_attention_tcgen05_blocks_per_sm.restype = c_int
+        L.ullm_prefill_attention_pair_supported.argtypes = [I, I, I, I]
+        L.ullm_prefill_attention_pair_supported.restype = c_int
         L.ullm_set_pdl.argtypes = [I]
         L.ullm_set_pdl.restype = None
         L.ullm_linear_tcgen05_supported.argtypes = [I, I, I]
@@ -857,7 +863,11 @@ class Kernels:
         if (ctx is not None and qkv.dtype == torch.bfloat16 and self.use_tcgen05_attention
                 and self.lib.ullm_prefill_attention_tcgen05_supported(head_dim, num_q, num_kv, page_size)
                 and qkv.stride(0) % head_dim == 0):
-            self._check(self.lib.ullm_prefill_attention_tcgen05(
+            pair = (self.tc_attention_mode != "single"
+                    and self.lib.ullm_prefill_attention_pair_supported(head_dim, num_q, num_kv, page_size))
+            entry = self.lib.ullm_prefill_attention_pair if pair else self.lib.ullm_prefill_attention_tcgen05
+            self.prefill_attention_kernel = "pair" if pair else "single"
+            self._check(entry(
                 _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                 block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, num_requests, num_q, num_kv,
                 head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream()),
