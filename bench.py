@@ -788,6 +788,32 @@ def run_prefill_attention_probe(args) -> int:
     return 0
 
 
+def run_mma_rate_probe(args) -> int:
+    """`--probe mma-rate`: clocks per tcgen05.mma (bfloat16, M = 128, K = 16) issued back to back by one thread, on
+    one block and on one block per SM (csrc/tcgen05_rate_probe.cu)."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+
+    K = kernels()
+    lib = K.lib
+    lib.ullm_tcgen05_mma_rate.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_void_p]
+    lib.ullm_tcgen05_mma_rate.restype = ctypes.c_int
+    out = torch.zeros(2, dtype=torch.int64, device="cuda")
+    names = ["A and B from shared memory, N = 128", "A and B from shared memory, N = 256",
+             "A from tensor memory, B MN-major, N = 128", "A and B from shared memory, N = 64",
+             "8 x (shared, N = 128) then 8 x (tensor memory, N = 128)"]
+    for blocks in (1, K.sm_count):
+        for mode, name in enumerate(names):
+            for _ in range(2):
+                n = lib.ullm_tcgen05_mma_rate(mode, 2000, blocks, out.data_ptr(), K.status.data_ptr(), None)
+                torch.cuda.synchronize()
+            K.raise_on_status()
+            print(f"{blocks:4d} block(s)  {name:58s} {out[0].item() / n:6.1f} clocks per product", flush=True)
+    return 0
+
+
 def run_sampling_probe(args) -> int:
     """`--probe sampling`: the two sampling kernels alone on `--batch` rows of the benchmark's vocabulary, one
     parameter set for all rows; microseconds per call, 20 calls recorded in a CUDA graph (the logits stay in L2,
@@ -1073,7 +1099,7 @@ def main() -> int:
                     help="the default line without the 32b and serve-0.6b runs that it adds to `points`")
     ap.add_argument("--no-groups", action="store_true", help="skip the per-kernel-group times of the decode step")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "prefill-attention", "sampling"],
+    ap.add_argument("--probe", default=None, choices=["decode", "prefill", "linear", "decode-attention", "prefill-attention", "mma-rate", "sampling"],
                     help="a few eager steps for a profiler; linear: the decode step's matrix products alone")
     ap.add_argument("--only", default=None, choices=["stream", "skinny", "tcgen05", "library", "tail"],
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
@@ -1090,6 +1116,8 @@ def main() -> int:
         args.warmup = 3
     if args.probe == "linear":
         return run_linear_probe(args)
+    if args.probe == "mma-rate":
+        return run_mma_rate_probe(args)
     if args.probe == "prefill-attention":
         return run_prefill_attention_probe(args)
     if args.probe == "decode-attention":

@@ -820,12 +820,16 @@ def test_small_m_linear_refuses_what_it_does_not_take():
     assert not K().small_m_linear(xf, rnd(128, 64, seed=2), torch.empty(4, 128, device="cuda"))
 
 
+@pytest.mark.parametrize("mode", ["pair", "single"])
 @pytest.mark.parametrize("Hq,Hkv,page,window", [(32, 8, 16, 0), (8, 8, 16, 0), (16, 1, 16, 0), (8, 2, 32, 0),
-                                                 (4, 2, 8, 0), (8, 2, 16, 100), (4, 1, 64, 37)])
-def test_prefill_attention_tcgen05_mixed_batch(Hq, Hkv, page, window):
-    """The tcgen05/TMA attention kernel (head size 128) on the same ragged batch as the mma.sync kernel:
-    whole prompts, portions that continue a context, two-token portions, single tokens; unwritten slots
-    of the pool hold NaN."""
+                                                 (4, 2, 8, 0), (8, 2, 16, 100), (4, 1, 64, 37), (8, 4, 128, 0),
+                                                 (4, 4, 16, 300)])
+def test_prefill_attention_tcgen05_mixed_batch(Hq, Hkv, page, window, mode):
+    """The two tcgen05/TMA attention kernels (head size 128; two query tiles per block, and one) on the same ragged
+    batch as the mma.sync kernel: whole prompts, portions that continue a context, two-token portions, single
+    tokens, requests of one to six key tiles; unwritten slots of the pool hold NaN."""
+    if mode == "single" and page == 128:
+        pytest.skip("the one-tile kernel takes pages of at most 64 tokens")
     dtype, D = torch.bfloat16, 128
     q_lens = [1, 37, 1, 2, 64, 129, 300, 31, 200]
     kv_lens = [150, 37, 1, 100, 130, 129, 700, 95, 200]
@@ -854,8 +858,8 @@ def test_prefill_attention_tcgen05_mixed_batch(Hq, Hkv, page, window):
     out = torch.full((T, Hq * D), 9.0, dtype=dtype, device="cuda")
     scale = D ** -0.5
     k = K()
-    old = k.use_tcgen05_attention
-    k.use_tcgen05_attention = True
+    old = k.use_tcgen05_attention, k.tc_attention_mode
+    k.use_tcgen05_attention, k.tc_attention_mode = True, mode
     try:
         k.paged_attention(qkv, out, kp, vp, bt.cuda(), torch.tensor(slots_of_req, dtype=torch.int32).cuda(), cu,
                           torch.tensor(kv_lens, dtype=torch.int32).cuda(), token_req, Hq, Hkv, D, page, window, scale,
@@ -863,8 +867,8 @@ def test_prefill_attention_tcgen05_mixed_batch(Hq, Hkv, page, window):
         torch.cuda.synchronize()
         k.raise_on_status()
     finally:
-        k.use_tcgen05_attention = old
-    assert k.attention_path == "prefill_tcgen05"
+        k.use_tcgen05_attention, k.tc_attention_mode = old
+    assert k.attention_path == "prefill_tcgen05" and k.prefill_attention_kernel == mode
     ref = attention_reference(qkv[:, : Hq * D].float().cpu().view(T, Hq, D),
                               torch.nan_to_num(kp.float().cpu()).view(-1, Hkv, D),
                               torch.nan_to_num(vp.float().cpu()).view(-1, Hkv, D), bt.long(), slots_of_req, q_lens,

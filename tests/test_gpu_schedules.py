@@ -344,7 +344,7 @@ SWITCH_SETTINGS = [
     {"ULLM_B200_SMALL_M_LINEAR": "skinny"}, {"ULLM_B200_SMALL_M_LINEAR": "tcgen05"},
     {"ULLM_B200_SMALL_M_LINEAR": "stream", "ULLM_B200_PDL": "1"}, {"ULLM_B200_STREAM_WEIGHT_MB": "0"},
     {"ULLM_B200_DECODE_TC": "1"}, {"ULLM_B200_DECODE_CLUSTER": "1"}, {"ULLM_B200_DECODE_CLUSTER": "0"},
-    {"ULLM_B200_FUSE_DECODE_ROPE": "0"}, {"ULLM_B200_TC_ATTN": "0"}, {"ULLM_B200_DECODE_BALANCED": "1"},
+    {"ULLM_B200_FUSE_DECODE_ROPE": "0"}, {"ULLM_B200_TC_ATTN": "0"}, {"ULLM_B200_TC_ATTN": "single"}, {"ULLM_B200_DECODE_BALANCED": "1"},
     {"ULLM_B200_DECODE_BALANCED": "0"}, {"ULLM_B200_MIXED_DECODE_ROWS": "0"}, {"ULLM_B200_LT_ROWS": "0"},
     {"ULLM_B200_FUSED_MLP_ROWS": "1"}, {"ULLM_B200_FUSED_TAIL_ROWS": "16"}, {"ULLM_B200_CHAIN_NORMS": "0"}, {"ULLM_B200_CHAIN_NORMS": "1"},
     {"ULLM_B200_STREAM_ALL_ROWS": "0"}, {"ULLM_B200_STREAM_ALL_ROWS": "32"}, {"ULLM_B200_GRAPH_SKIP": "2,8"},

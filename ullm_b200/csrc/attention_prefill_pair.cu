@@ -16,9 +16,11 @@
 //
 // The MMA thread issues   P.V_0(j), S_0(j+1), P.V_1(j), S_1(j+1), ...   so the tensor pipe works on one query
 // tile while the other tile's warp group does its softmax.  Tensor memory: S_0, S_1, O_0, O_1 = 512 columns; one
-// block per SM.  Shared memory: two Q tiles (64 KB) and a ring of five 32 KB slots that K and V tiles go
-// through in the order K_0 V_0 K_1 V_1 ...; a K slot is free again when both score products of its tile are done,
-// a V slot when both P.V products are.
+// block per SM.  Shared memory: two Q tiles (64 KB), K tile 0, and two slots for the pairs (V_j, K_{j+1}): all
+// that step j of the MMA thread reads, loaded under one barrier and given back by one commit.  (What this thread
+// does between two products is on the critical path: its waits poll, its descriptors are stepped by adds, and a
+// step has three commits: the two score barriers, which also cover the P.V products issued before them, and the
+// pair's release.)
 //
 // Q, K and V tiles are brought in by TMA (cp.async.bulk.tensor, 128-byte swizzle): Q as 3-D boxes of the
 // projection buffer that gather (token, head) rows, K and V page by page through 4-D maps of the cache.  Slots of
@@ -43,11 +45,11 @@
 #define TP_WAIT_LIMIT (1 << 20)
 #define TP_TILE_Q (TP_ROWS * TP_D * 2)    // 32 KB: two halves of [128 rows x 128 B]
 #define TP_TILE_KV (TP_KEYS * TP_D * 2)   // 32 KB: two halves of [128 keys x 128 B]
-#define TP_SLOTS 5
-#define TP_TILES_BYTES (2 * TP_TILE_Q + TP_SLOTS * TP_TILE_KV)  // 224 KB
+#define TP_TILES_BYTES (2 * TP_TILE_Q + 5 * TP_TILE_KV)  // 224 KB: two Q tiles, K tile 0, two (V, K) pairs
 #define TP_BARRIER_BYTES 256
 #define TP_SMEM (TP_TILES_BYTES + TP_BARRIER_BYTES)
 #define TP_TMEM_COLS 512
+
 
 __device__ __forceinline__ uint32_t tp_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tp_mbar_init(uint64_t* bar, uint32_t count) {
@@ -59,11 +61,34 @@ __device__ __forceinline__ void tp_mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 __device__ __forceinline__ void tp_mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tp_smem(bar)) : "memory");
 }
+// test_wait first: it is the cheaper instruction when the phase is already complete
 __device__ __forceinline__ bool tp_mbar_wait(uint64_t* bar, uint32_t parity) {
+  {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(tp_smem(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
   for (int i = 0; i < TP_WAIT_LIMIT; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(tp_smem(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// the same by polling without suspension (the MMA thread: its wake-up is on the critical path)
+__device__ __forceinline__ bool tp_mbar_spin(uint64_t* bar, uint32_t parity) {
+  for (int i = 0; i < TP_WAIT_LIMIT * 16; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
         : "r"(tp_smem(bar)), "r"(parity)
         : "memory");
@@ -135,6 +160,17 @@ __device__ __forceinline__ void tp_tmem_ld32_nowait(uint32_t taddr, uint32_t* r)
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+// 8 columns at a time (the rescaling of O: a rare path that must not cost the common one its registers)
+__device__ __forceinline__ void tp_tmem_ld8_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tp_tmem_st8_nowait(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tp_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tp_tmem_st32_nowait(uint32_t taddr, const uint32_t* r) {
   asm volatile(
@@ -152,6 +188,11 @@ __device__ __forceinline__ float tp_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float tp_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 // two floats to packed bfloat16 (round to nearest even): `lo` in the low half
 __device__ __forceinline__ uint32_t tp_pack_bf16(float lo, float hi) {
@@ -185,14 +226,16 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(tp_raw + TP_TILES_BYTES);
   uint64_t& q_full = bars[0];
-  uint64_t* full = bars + 1;                    // [TP_SLOTS] a K or V tile has landed
-  uint64_t* empty = bars + 1 + TP_SLOTS;        // [TP_SLOTS] the products that read the slot are done
-  uint64_t* s_full = bars + 1 + 2 * TP_SLOTS;   // [2] scores of query tile i are in tensor memory
-  uint64_t* p_ready = s_full + 2;               // [2] P of query tile i is in tensor memory (128 arrivals)
-  uint64_t* pv_done = s_full + 4;               // [2] P.V of query tile i is done
-  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(s_full + 6);
+  uint64_t& k0_full = bars[1];                  // the first K tile has landed
+  uint64_t* full = bars + 2;                    // [2] the pair (V_j, K_{j+1}) has landed in pair slot j & 1
+  uint64_t* empty = bars + 4;                   // [2] the products that read the pair are done
+  uint64_t* s_full = bars + 6;                  // [2] scores of query tile i are in tensor memory
+  uint64_t* p_ready = bars + 8;                 // [2] P of query tile i is in tensor memory (one arrival per warp)
+  uint64_t* pv_done = bars + 10;                // [2] the LAST P.V product of query tile i is done
+  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 12);
   unsigned char* q_s = tp_raw;                  // query tile i at i * TP_TILE_Q
-  unsigned char* ring = tp_raw + 2 * TP_TILE_Q;
+  unsigned char* k0_s = tp_raw + 2 * TP_TILE_Q;          // K tile 0
+  unsigned char* pair_s = k0_s + TP_TILE_KV;             // pair slot s: V at s * 2 * TP_TILE_KV, K right behind it
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // A 1-D grid, numbered so that consecutive blocks are the same token block of all kv heads: the block
   // scheduler then starts the heaviest blocks of EVERY head first (longest work first keeps the SMs level).
@@ -243,13 +286,14 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
 
   if (tid == 0) {
     tp_mbar_init(&q_full, 1);
-    for (int s = 0; s < TP_SLOTS; ++s) {
+    tp_mbar_init(&k0_full, 1);
+    for (int s = 0; s < 2; ++s) {
       tp_mbar_init(&full[s], 1);
       tp_mbar_init(&empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       tp_mbar_init(&s_full[i], 1);
-      tp_mbar_init(&p_ready[i], 128);
+      tp_mbar_init(&p_ready[i], 4);  // one arrival per warp of the group
       tp_mbar_init(&pv_done[i], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -291,32 +335,39 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
       }
       return page;
     };
-    int pages_next = page_of(0);
-    int slot = 0, round = 0;
+    // K tile 0, then the pairs (V_j, K_{j+1}): what step j of the MMA thread reads
+    int pages_now = page_of(0);
+    int pages_next = tiles > 1 ? page_of(1) : -1;
+    auto load_tile = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int page) {
+      // a page that is not there (-1) is out of the map's range: the box is filled with zeros
+      if (lane < pages_per_tile) {
+        const int pcoord = page >= 0 ? page : (int)p.num_pages;
+        unsigned char* d = dst + lane * p.page_size * 128;
+        tp_tma_4d(d, map, bar, 0, kh, 0, pcoord);
+        tp_tma_4d(d + TP_TILE_KV / 2, map, bar, 64, kh, 0, pcoord);
+      }
+    };
+    if (lane == 0) tp_mbar_expect_tx(&k0_full, TP_TILE_KV);
+    __syncwarp();
+    load_tile(k0_s, &map_k, &k0_full, pages_now);
     bool ok = true;
     for (int t = 0; t < tiles && ok; ++t) {
-      const int pages_now = pages_next;
-      if (t + 1 < tiles) pages_next = page_of(t + 1);  // in flight while this tile's slots are awaited
-      // a page that is not there (-1) is out of the map's range: the box is filled with zeros
-      const int pcoord = pages_now >= 0 ? pages_now : (int)p.num_pages;
-      for (int kv = 0; kv < 2 && ok; ++kv) {  // the K tile, then the V tile
-        unsigned char* dst = ring + slot * TP_TILE_KV;
-        if (lane == 0 && !tp_mbar_wait(&empty[slot], (round & 1) ^ 1)) {
-          ullm_report(p.status, ULLM_STATUS_TIMEOUT, 21, t);
-          ok = false;
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        if (lane == 0) tp_mbar_expect_tx(&full[slot], TP_TILE_KV);
-        __syncwarp();
-        if (lane < pages_per_tile) {
-          const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
-          unsigned char* d = dst + lane * p.page_size * 128;
-          tp_tma_4d(d, map, &full[slot], 0, kh, 0, pcoord);
-          tp_tma_4d(d + TP_TILE_KV / 2, map, &full[slot], 64, kh, 0, pcoord);
-        }
-        if (++slot == TP_SLOTS) slot = 0, ++round;
+      const int s = t & 1;
+      const bool has_k = t + 1 < tiles;
+      const int pages_after = t + 2 < tiles ? page_of(t + 2) : -1;  // in flight while this pair's slot is awaited
+      if (lane == 0 && !tp_mbar_wait(&empty[s], ((t >> 1) & 1) ^ 1)) {
+        ullm_report(p.status, ULLM_STATUS_TIMEOUT, 21, t);
+        ok = false;
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane == 0) tp_mbar_expect_tx(&full[s], has_k ? 2 * TP_TILE_KV : TP_TILE_KV);
+      __syncwarp();
+      unsigned char* dst = pair_s + s * 2 * TP_TILE_KV;
+      load_tile(dst, &map_v, &full[s], pages_now);
+      if (has_k) load_tile(dst + TP_TILE_KV, &map_k, &full[s], pages_next);
+      pages_now = pages_next;
+      pages_next = pages_after;
     }
   } else if (warp == 9) {
     if (lane == 0) {
@@ -328,62 +379,84 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                                ((uint32_t)(TP_ROWS >> 4) << 24);
       bool ok = tp_mbar_wait(&q_full, 0);
       if (!ok) ullm_report(p.status, ULLM_STATUS_TIMEOUT, 22, 0);
-      // ring entry e (K_j: 2 j, V_j: 2 j + 1) lives in slot e % TP_SLOTS, in the slot's round e / TP_SLOTS
-      auto wait_entry = [&](int e, int code) -> bool {
-        if (tp_mbar_wait(&full[e % TP_SLOTS], (e / TP_SLOTS) & 1)) return true;
-        ullm_report(p.status, ULLM_STATUS_TIMEOUT, code, e);
-        return false;
+      // This one thread's instruction stream paces the tensor pipe, so everything is kept to adds: descriptors as
+      // their 32-bit halves (the high word is the same for all of them: 8-row groups 1024 bytes apart, version 1,
+      // 128-byte swizzle; the low word holds the start address in 16-byte units and the leading-dimension field),
+      // ring slots and parities stepped, not divided.
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t k0_lo = ((tp_smem(k0_s) & 0x3FFFF) >> 4) | (1u << 16);
+      const uint32_t pair_lo = (tp_smem(pair_s) & 0x3FFFF) >> 4;
+      const uint32_t q_lo[2] = {((tp_smem(q_s) & 0x3FFFF) >> 4) | (1u << 16),
+                                ((tp_smem(q_s + TP_TILE_Q) & 0x3FFFF) >> 4) | (1u << 16)};
+      auto mma_ss = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t acc) {
+        asm volatile(
+            "{\n .reg .b64 da, db;\n .reg .pred p;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+            " setp.ne.b32 p, %5, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n"
+            ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc_s), "r"(acc)
+            : "memory");
       };
-      auto scores = [&](int i, int j) {
-        const unsigned char* k_t = ring + ((2 * j) % TP_SLOTS) * TP_TILE_KV;
-        const unsigned char* q_t = q_s + i * TP_TILE_Q;
+      auto mma_ts = [&](uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t acc) {
+        asm volatile(
+            "{\n .reg .b64 db;\n .reg .pred p;\n mov.b64 db, {%2, %3};\n"
+            " setp.ne.b32 p, %5, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+            ::"r"(d), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc_o), "r"(acc)
+            : "memory");
+      };
+      // scores of query tile i from the K tile whose descriptor low word is `b0`
+      auto scores = [&](int i, uint32_t b0) {
 #pragma unroll
         for (int kk = 0; kk < TP_D / 16; ++kk) {
-          // d = 16 kk: half kk / 4 of the Q and K tiles, 32 bytes further per step inside a half
-          const uint64_t a = tp_desc_kmajor(q_t + (kk >> 2) * (TP_TILE_Q / 2)) + 2 * (kk & 3);
-          const uint64_t b = tp_desc_kmajor(k_t + (kk >> 2) * (TP_TILE_KV / 2)) + 2 * (kk & 3);
-          tp_mma_ss(tmem + i * TP_KEYS, a, b, idesc_s, kk > 0 ? 1u : 0u);
+          // d = 16 kk: half kk / 4 of the Q and K tiles (16 KB = 1024 units further), 32 bytes per step inside a half
+          const uint32_t off = (kk >> 2) * ((TP_TILE_KV / 2) >> 4) + 2 * (kk & 3);
+          mma_ss(tmem + i * TP_KEYS, q_lo[i] + off, b0 + off, kk > 0 ? 1u : 0u);
         }
         tp_commit(&s_full[i]);
       };
-      auto p_times_v = [&](int i, int j) {
-        const unsigned char* v_t = ring + ((2 * j + 1) % TP_SLOTS) * TP_TILE_KV;
+      // O_i += P_i V from the V tile at `v_lo` (16-byte units)
+      auto p_times_v = [&](int i, int j, uint32_t v_lo) {
+        // MN-major: the leading-dimension field is the distance of the two 64-column halves
+        const uint32_t b0 = v_lo | ((uint32_t)((TP_TILE_KV / 2) >> 4) << 16);
 #pragma unroll
-        for (int ks = 0; ks < TP_KEYS / 16; ++ks) {
-          // 16 keys: 8 columns of P (two bfloat16 each); two 8-key groups = 2048 bytes down the V tile
-          const uint64_t b = tp_desc_mnmajor(v_t + ks * 2048, TP_TILE_KV / 2);
-          tp_mma_ts(tmem + 2 * TP_KEYS + i * TP_D, tmem + i * TP_KEYS + ks * 8, b, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        tp_commit(&pv_done[i]);
+        for (int ks = 0; ks < TP_KEYS / 16; ++ks)  // 16 keys: 8 columns of P; two 8-key groups = 2048 bytes down the V tile
+          mma_ts(tmem + 2 * TP_KEYS + i * TP_D, tmem + i * TP_KEYS + ks * 8, b0 + ks * (2048 >> 4),
+                 (j > 0 || ks > 0) ? 1u : 0u);
       };
-      if (ok) ok = wait_entry(0, 23);
+      if (ok && !tp_mbar_wait(&k0_full, 0)) {
+        ullm_report(p.status, ULLM_STATUS_TIMEOUT, 23, 0);
+        ok = false;
+      }
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        scores(0, 0);
-        if (tiles1 > 0) scores(1, 0);
-        tp_commit(&empty[0]);
+        scores(0, k0_lo);
+        if (tiles1 > 0) scores(1, k0_lo);
       }
       for (int j = 0; j < tiles && ok; ++j) {
-        const bool more = j + 1 < tiles;
-        ok = wait_entry(2 * j + 1, 24);
-        if (ok && more) ok = wait_entry(2 * j + 2, 25);
-        if (!ok) break;
+        // the pair (V_j, K_{j+1}): all this step reads.  (The commits behind the score products also cover the
+        // P.V products issued before them, so the softmax warps need no signal of their own for those.)
+        if (!tp_mbar_wait(&full[j & 1], (j >> 1) & 1)) {
+          ullm_report(p.status, ULLM_STATUS_TIMEOUT, 24, j);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_lo = pair_lo + (j & 1) * ((2 * TP_TILE_KV) >> 4);
+        const uint32_t k_lo = (v_lo + (TP_TILE_KV >> 4)) | (1u << 16);
         for (int i = 0; i < 2 && ok; ++i) {
           const int tiles_i = i == 0 ? tiles0 : tiles1;
           if (j < tiles_i) {
-            if (!tp_mbar_wait(&p_ready[i], j & 1)) {
+            if (!tp_mbar_spin(&p_ready[i], j & 1)) {
               ullm_report(p.status, ULLM_STATUS_TIMEOUT, 26 + i, j);
               ok = false;
               break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            p_times_v(i, j);
+            p_times_v(i, j, v_lo);
+            if (j + 1 == tiles_i) tp_commit(&pv_done[i]);
           }
-          if (j + 1 < tiles_i) scores(i, j + 1);
+          if (j + 1 < tiles_i) scores(i, k_lo);
         }
         if (!ok) break;
-        tp_commit(&empty[(2 * j + 1) % TP_SLOTS]);          // V_j: both P.V products have been issued
-        if (more) tp_commit(&empty[(2 * j + 2) % TP_SLOTS]);  // K_{j+1}: both score products have been issued
+        tp_commit(&empty[j & 1]);  // every product that reads the pair has been issued
       }
     }
   } else {
@@ -426,7 +499,8 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int k = 0; k < TP_KEYS; ++k) mx[k & 3] = fmaxf(mx[k & 3], __uint_as_float(sr[k]));
+      for (int k = 0; k < TP_KEYS / 2; ++k)
+        mx[k & 3] = tp_max3(mx[k & 3], __uint_as_float(sr[2 * k]), __uint_as_float(sr[2 * k + 1]));
       const float row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       // The reference point of the exponents only moves when the row's maximum grows by more than 2^8:
       // until then P is at most 256 (exact in bf16 range, sums in 32-bit), and O and l, which share the
@@ -437,13 +511,14 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
       const float alpha = m == -INFINITY ? 1.f : tp_ex2(m - m_use);  // (no key seen yet: O and l are still zero)
       m = m_new;
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_use;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const float a = tp_ex2(fmaf(__uint_as_float(sr[h * 64 + 2 * k]), p.scale_log2, -m_use));
-          const float b = tp_ex2(fmaf(__uint_as_float(sr[h * 64 + 2 * k + 1]), p.scale_log2, -m_use));
+          const float a = tp_ex2(fmaf(__uint_as_float(sr[h * 64 + 2 * k]), p.scale_log2, neg_m));
+          const float b = tp_ex2(fmaf(__uint_as_float(sr[h * 64 + 2 * k + 1]), p.scale_log2, neg_m));
           sum[(2 * k) & 3] += a;
           sum[(2 * k + 1) & 3] += b;
           pk[k] = tp_pack_bf16(a, b);
@@ -454,12 +529,11 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
       // the last key tile may hold slots past the request's length: whatever they contain must not reach O.
       // The first warp group that works on this tile clears them (its P.V product is issued first).
       if (key0 + TP_KEYS > kvl && (i == 0 || j >= tiles0)) {
-        const int e = 2 * j + 1;
-        if (!tp_mbar_wait(&full[e % TP_SLOTS], (e / TP_SLOTS) & 1)) {
+        if (!tp_mbar_wait(&full[j & 1], (j >> 1) & 1)) {
           if (lane == 0) ullm_report(p.status, ULLM_STATUS_TIMEOUT, 30 + i, j);
           ok = false;
         } else {
-          unsigned char* v_t = ring + (e % TP_SLOTS) * TP_TILE_KV;
+          unsigned char* v_t = pair_s + (j & 1) * 2 * TP_TILE_KV;
           const int first_bad = max(0, kvl - key0);
           for (int x = row; x < (TP_KEYS - first_bad) * 16; x += 128) {
             const int key = first_bad + x / 16, ch = x % 16;  // 16 chunks of 16 bytes per key: 8 per half
@@ -469,29 +543,25 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
         }
       }
       if (ok && j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O shares the reference point: wait until P.V of the tile before is in it, then rescale this warp's rows
-        if (!tp_mbar_wait(&pv_done[i], (j - 1) & 1)) {
-          if (lane == 0) ullm_report(p.status, ULLM_STATUS_TIMEOUT, 32 + i, j);
-          ok = false;
-        } else {
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // O shares the reference point.  P.V of the tile before is in it: this tile's scores were issued behind
+        // that product, and their completion was awaited above.  Rescale this warp's rows.
+#pragma unroll 1
+        for (int c = 0; c < TP_D / 8; ++c) {
+          uint32_t v[8];
+          tp_tmem_ld8_nowait(tmem_o + c * 8, v);
+          tp_tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < TP_D / 32; ++c) {
-            uint32_t v[32];
-            tp_tmem_ld32_nowait(tmem_o + c * 32, v);
-            tp_tmem_ld_wait();
-#pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
-            tp_tmem_st32_nowait(tmem_o + c * 32, v);
-          }
+          for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
+          tp_tmem_st8_nowait(tmem_o + c * 8, v);
         }
       }
       tp_tmem_st_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      tp_mbar_arrive(&p_ready[i]);  // (also after a failed wait: the MMA thread is not left waiting for this tile)
+      __syncwarp();
+      if (lane == 0) tp_mbar_arrive(&p_ready[i]);  // (also after a failed wait: the MMA thread is not left waiting for this tile)
     }
     if (tiles_i > 0) {
-      if (ok && !tp_mbar_wait(&pv_done[i], (tiles_i - 1) & 1)) {
+      if (ok && !tp_mbar_wait(&pv_done[i], 0)) {
         if (lane == 0) ullm_report(p.status, ULLM_STATUS_TIMEOUT, 34 + i, tiles_i);
         ok = false;
       }
@@ -579,7 +649,6 @@ extern "C" int ullm_prefill_attention_pair_supported(int head_dim, int num_q, in
 }
 
 static int g_tp_attr_set = 0;
-
 extern "C" int ullm_prefill_attention_pair(const void* q, long long q_row_stride, void* out, const void* k_cache,
                                            const void* v_cache, const int* block_table, int max_pages,
                                            const int* req_slots, const int* cu_q, const int* kv_len, int tokens,

@@ -860,11 +860,12 @@ class Kernels:
                               num_q, num_kv, head_dim, page_size, window, scale, num_pages, ragged, ctx)
             req_slots, cu_q, kv_len = req_slots[n_dec:], cu_q[n_dec:], kv_len[n_dec:]
         num_requests = (ctx.num_requests - n_dec) if ctx is not None else 0
-        if (ctx is not None and qkv.dtype == torch.bfloat16 and self.use_tcgen05_attention
-                and self.lib.ullm_prefill_attention_tcgen05_supported(head_dim, num_q, num_kv, page_size)
-                and qkv.stride(0) % head_dim == 0):
-            pair = (self.tc_attention_mode != "single"
-                    and self.lib.ullm_prefill_attention_pair_supported(head_dim, num_q, num_kv, page_size))
+        pair = single = False
+        if ctx is not None and qkv.dtype == torch.bfloat16 and self.use_tcgen05_attention and qkv.stride(0) % head_dim == 0:
+            pair = bool(self.tc_attention_mode != "single"
+                        and self.lib.ullm_prefill_attention_pair_supported(head_dim, num_q, num_kv, page_size))
+            single = bool(not pair and self.lib.ullm_prefill_attention_tcgen05_supported(head_dim, num_q, num_kv, page_size))
+        if pair or single:
             entry = self.lib.ullm_prefill_attention_pair if pair else self.lib.ullm_prefill_attention_tcgen05
             self.prefill_attention_kernel = "pair" if pair else "single"
             self._check(entry(
