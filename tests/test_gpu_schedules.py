@@ -337,6 +337,60 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_kernel_runs():
 
 
 # ---------------------------------------------------------------------------------------------------------
+# norms folded between products: fewer kernels, the same logits
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.needs_cuda
+def test_norms_folded_between_products_save_kernels_and_keep_the_logits(tmp_path, monkeypatch):
+    """A three-layer bfloat16 model (head size 128) decoding three requests one token at a time, with the norms
+    as kernels of their own (0), the feed-forward norm folded between o_proj and gate_up (1), and the next
+    block's first norm folded behind down_proj as well (2): each level launches fewer kernels per step, and every
+    level's logits are within the bfloat16 tolerance of the plain implementation."""
+    import os
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine import ModelRunner, StepEntry
+
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 3, "hidden_size": 256,
+           "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 640,
+           "vocab_size": 523, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "attention_bias": False,
+           "tie_word_embeddings": True, "max_position_embeddings": 256, "torch_dtype": "bfloat16"}
+    w = {n: t.to(torch.bfloat16) for n, t in pm.random_weights(cfg, seed=23, std=0.05, norm_std=0.2).items()}
+    d = write_model_dir(str(tmp_path / "fold_model"), cfg, w)
+    wf = {k: v.float() for k, v in w.items()}
+    prompts = [random_ids(cfg["vocab_size"], n, 70 + n) for n in (33, 9, 20)]
+    tails = [random_ids(cfg["vocab_size"], 6, 90 + i) for i in range(3)]
+    want = [pm.forward_logits(p + t, wf, cfg) for p, t in zip(prompts, tails)]
+    K = kernels()
+    launches = {}
+    try:
+        for level in ("0", "1", "2"):
+            monkeypatch.setenv("ULLM_B200_CHAIN_NORMS", level)
+            K.apply_switches(os.environ)
+            r = ModelRunner(d, dtype="bfloat16", device=device(), page_size=16, num_pages=32, max_requests=4,
+                            max_context=256, max_step_tokens=64)
+            for i, p in enumerate(prompts):
+                r.add_request(f"q{i}")
+                r.step([StepEntry(f"q{i}", p, [])])
+            got = [[] for _ in prompts]
+            l0 = K.launches
+            for t in range(6):
+                lg = r.step([StepEntry(f"q{i}", [tails[i][t]], [0]) for i in range(3)]).float().cpu()
+                for i in range(3):
+                    got[i].append(lg[i])
+            launches[level] = (K.launches - l0) / 6
+            r.check_device_status()
+            for i in range(3):
+                ref = want[i][len(prompts[i]):len(prompts[i]) + 6]
+                assert_close(torch.stack(got[i]), ref, "bfloat16", f"fold level {level}, request {i}")
+    finally:
+        monkeypatch.undo()
+        K.apply_switches(os.environ)
+    # level 1 saves the feed-forward norm of every layer, level 2 also the first norm of every layer but the first
+    assert launches["0"] - launches["1"] == cfg["num_hidden_layers"], launches
+    assert launches["1"] - launches["2"] == cfg["num_hidden_layers"] - 1, launches
+
+
+# ---------------------------------------------------------------------------------------------------------
 # every environment switch: generation with it set still follows the plain implementation
 # ---------------------------------------------------------------------------------------------------------
 SWITCH_SETTINGS = [
