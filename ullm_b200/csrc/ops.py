@@ -67,14 +67,15 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
         raise KernelError(f"{name} must be contiguous")
 
 
-def _timed(group: str, nbytes=None):
+def _timed(group: str, nbytes=None, skipped=None):
     """While a timer is installed (`Kernels.timer`, see engine/profiler.py), the wrapped call is bracketed by
-    two CUDA events and booked under `group`; `nbytes(*args)` says what it had to read, if that is known."""
+    two CUDA events and booked under `group`; `nbytes(*args)` says what it had to read, if that is known.
+    `skipped`: what the call returns when a measurement leaves its group out."""
 
     def outer(fn):
         def inner(self, *a, **k):
             if self.skip_groups and group in self.skip_groups:
-                return None  # a measurement leaves this group out (the step's results are then meaningless)
+                return skipped  # a measurement leaves this group out (the step's results are then meaningless)
             t = self.timer
             if t is None:
                 return fn(self, *a, **k)
@@ -376,8 +377,15 @@ class Kernels:
                     f"linear_skinny ({M}x{K} . {N}x{K})")
         return True
 
+    @_timed("linear", _weight_bytes, skipped=True)
     def stream_linear(self, x, weight, out, bias=None, act: int | None = None, residual=None, norm_behind=None,
                       norm_in_front=None) -> bool:
+        """`_stream_linear` as a call of its own (a block that chains its products): booked under the products'
+        group."""
+        return self._stream_linear(x, weight, out, bias, act, residual, norm_behind, norm_in_front)
+
+    def _stream_linear(self, x, weight, out, bias=None, act: int | None = None, residual=None, norm_behind=None,
+                       norm_in_front=None) -> bool:
         """The weight-streaming product for few rows (M <= 32; csrc/linear_stream.cu): a TMA ring per block that
         is filled with weight tiles before the kernel in front has finished (programmatic dependent launch),
         mma.sync on the swizzled tiles.  Same contract as `small_m_linear`; `residual` ([M, n_out], bfloat16;
@@ -548,13 +556,13 @@ class Kernels:
         if self.small_m_mode == "skinny":
             return x.shape[0] <= 32 and self.skinny_linear(x, weight, out, bias, act)
         if self.small_m_mode == "stream":
-            return x.shape[0] <= self.stream_rows and self.stream_linear(x, weight, out, bias, act)
+            return x.shape[0] <= self.stream_rows and self._stream_linear(x, weight, out, bias, act)
         if self.small_m_mode == "auto":
             rows = x.shape[0]
             return (rows <= self.stream_rows
                     and (rows <= self.stream_all_rows
                          or weight.numel() * weight.element_size() <= self.stream_weight_bytes)
-                    and self.stream_linear(x, weight, out, bias, act))
+                    and self._stream_linear(x, weight, out, bias, act))
         if self.small_m_mode == "tcgen05":
             if x.shape[0] <= 64:
                 return self.small_m_linear(x, weight, out, bias, act)

@@ -66,7 +66,7 @@ class KernelGroupTimer:
         for t in out.values():
             t["us"] = round(t["us"], 1)
             if t["bytes"] and t["us"] > 0:
-                t["gb_per_s"] = round(t["bytes"] / t["us"] / 1e3, 1)
+                t["gb_per_s"] = round(t["bytes"] / t["us"] / 1e3, 3)
         return dict(out)
 
 
