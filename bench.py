@@ -439,11 +439,77 @@ def run_serve(args) -> dict:
     }
 
 
+def run_long_context(args) -> dict:
+    """`--workload 8b-long`: the same layer sizes at a context of 16,384 tokens: the prefill of one 16,384-token
+    prompt (in portions of the engine's token budget, each behind the pages of the portions before it), and decode
+    steps of 8 requests that each hold 16,384 tokens.  One line for `points`."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.sampling import SamplingParams
+
+    LONG, B, steps, warm = 16384, 8, 32, 4
+    cfg = dict(QWEN3_8B)
+    layers = args.layers or cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers
+    pk = peaks()
+    nums = model_numbers(cfg, layers)
+    per_req = LONG + 2 * (steps + warm) + 64
+    llm, _ = _make_llm(QWEN3_8B, layers, B, (B + 1) * (-(-per_req // PAGE_SIZE)) + 64, budget=4096, context=LONG + 1024)
+    eng = llm.engine
+    g = torch.Generator().manual_seed(2)
+
+    def prompt(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+
+    def drain():
+        while eng.has_unfinished_sequences():
+            eng.step()
+
+    pre_ms = []
+    for i in range(4):
+        eng.add_sequence(f"p{i}", prompt(LONG), SamplingParams(temperature=0.0, ignore_eos=True, max_new_tokens=1))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        drain()
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+    pre = statistics.median(pre_ms[1:])
+    sp = SamplingParams(temperature=0.0, ignore_eos=True, max_new_tokens=10**9)
+    ids = [f"d{i}" for i in range(B)]
+    for sid in ids:
+        eng.add_sequence(sid, prompt(LONG), sp)
+    while any(s.num_pending > 1 or s.status.name == "WAITING" for s in [eng.scheduler.get_sequence(i) for i in ids]):
+        eng.step()
+    for _ in range(warm):
+        eng.step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        eng.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    for sid in ids:
+        eng.abort_sequence(sid)
+    drain()
+    kernels().raise_on_status()
+    ctx = LONG + warm + steps / 2.0
+    return {"workload": "8b-long", "context": LONG, "layers": layers,
+            "prefill_tok_s": round(LONG / (pre / 1e3), 1), "prefill_ms": round(pre, 2),
+            "prefill_frac": round(prefill_flops(cfg, layers, LONG) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+            "decode_b8_ms": round(ms, 4), "decode_b8_tok_s": round(B / (ms / 1e3), 1),
+            "decode_b8_frac": round(decode_bytes(nums, B, ctx, cfg["hidden_size"]) / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+
+
 def run_extra_shapes(args, impl: str) -> dict:
     """The two further workloads, each in a process of its own (the 32B shape needs the device to itself), as
     flat entries for `points`."""
     points = {}
-    jobs = [("serve-0.6b", "qwen3_0_6b_serve")] + ([("32b", "qwen3_32b")] if impl == "ours" else [])
+    jobs = [("serve-0.6b", "qwen3_0_6b_serve")] + ([("32b", "qwen3_32b"), ("8b-long", "qwen3_8b_ctx16k")] if impl == "ours" else [])
     for workload, key in jobs:
         cmd = [sys.executable, os.path.abspath(__file__), "--workload", workload, "--impl", impl, "--steps",
                str(args.steps), "--warmup", str(args.warmup), "--no-groups"]
@@ -456,6 +522,9 @@ def run_extra_shapes(args, impl: str) -> dict:
             continue
         if "unavailable" in d:
             points[f"{key}_unavailable"] = d["unavailable"][:200]
+        elif workload == "8b-long":
+            for k in ("prefill_tok_s", "prefill_frac", "decode_b8_ms", "decode_b8_tok_s", "decode_b8_frac"):
+                points[f"{key}_{k}"] = d[k]
         elif workload == "32b":
             for k, v in d["points"].items():
                 points[f"{key}_{k}"] = v
@@ -1092,9 +1161,10 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long"],
                     help="8b: the default line (Qwen3-8B layer sizes); 32b: the same at Qwen3-32B layer sizes; "
-                         "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes")
+                         "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes; 8b-long: "
+                         "prefill of 16,384 tokens and decode of 8 requests at that context")
     ap.add_argument("--no-extra-shapes", action="store_true",
                     help="the default line without the 32b and serve-0.6b runs that it adds to `points`")
     ap.add_argument("--no-groups", action="store_true", help="skip the per-kernel-group times of the decode step")
@@ -1138,6 +1208,9 @@ def main() -> int:
     if not torch.cuda.is_available():
         print("bench.py: no CUDA device: this engine has no CPU path", file=sys.stderr)
         return 1
+    if args.workload == "8b-long":
+        print(json.dumps(run_long_context(args)))
+        return 0
     out = run_serve(args) if args.workload == "serve-0.6b" else run_ours(args)
     if extra:
         import gc
