@@ -318,9 +318,11 @@ def run_ours(args) -> dict:
     clocks = clk.summary()
     value = B / (ms / 1e3)
     # End to end through the call a user makes: LLM.generate_batch, token ids in, token ids out.  Pairs of calls
-    # on fresh prompts of the same lengths, W and W + K new tokens each: their prompt work is the same, the
+    # on fresh prompts of the same lengths, WE and WE + K new tokens each: their prompt work is the same, the
     # difference of their wall times is K decode steps (each with its staging copy from pinned memory and the
-    # read of its sampled ids) as the user sees them.  The median of five such differences.
+    # read of its sampled ids) as the user sees them.  The median of five such differences.  (WE = at least 24
+    # tokens: the first steps behind a burst of prompts run at the clocks the power cap left, as `value`'s own
+    # warm-up steps do; the difference then covers steps like those `value` times.)
     def user_call(n_new):
         ps = [prompt(START_CONTEXT) for _ in range(B)]
         torch.cuda.synchronize()
@@ -329,12 +331,13 @@ def run_ours(args) -> dict:
         dt = time.perf_counter() - t0
         assert all(len(o.token_ids) == n_new for o in outs)
         return dt
-    user_call(W)  # warm
+    WE = max(W, 24)
+    user_call(WE)  # warm
     KE = max(K, 32)
     diffs = []
     for _ in range(5):
-        t_short = user_call(W)
-        diffs.append(user_call(W + KE) - t_short)
+        t_short = user_call(WE)
+        diffs.append(user_call(WE + KE) - t_short)
     e2e_value = B * KE / max(statistics.median(diffs), 1e-9)
     e2e_steps_value = B / wall  # the same loop as `value`, by the wall clock
     dbytes = decode_bytes(nums, B, ctx, cfg["hidden_size"])
