@@ -93,13 +93,14 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
   }
 }
 
-// The same for bfloat16 with head size 64 or 128, moved in 16-byte pieces: D / 8 lanes hold one (token, head)
-// row (8 elements each), so a warp works on 32 / (D / 8) rows side by side.  A warp takes QKV_STEPS such sets
-// of one token's heads (6 for many tokens: fewer table reads and more bytes in flight per lane; 1 for the few
-// tokens of a decode step, where the shortest chain of work per warp counts): the token's position, its rows of the rotation tables and its cache slot are read once
-// for all of them, and all the rows are loaded before any arithmetic (96 bytes in flight per lane).  The
-// rotation partner of an element (D / 2 further) sits in the lane D / 16 away; sums and partners travel by
-// shuffles inside the row's lanes.  Nothing returns early: lanes without work stay in the shuffles.
+// The same for bfloat16 with head size 64 or 128: D / 8 lanes hold one (token, head) row, each lane FOUR
+// neighbouring elements of the row's first half and the four elements D / 2 further (two 8-byte pieces), so an
+// element and its rotation partner sit in the same lane and only the sum of squares travels by shuffles.  A warp
+// works on 32 / (D / 8) rows side by side and takes QKV_STEPS such sets of one token's heads (6 for many tokens:
+// fewer table reads and more bytes in flight per lane; 1 for the few tokens of a decode step, where the shortest
+// chain of work per warp counts): the token's position, its rows of the rotation tables and its cache slot are
+// read once for all of them, and all the rows are loaded before any arithmetic.  Nothing returns early: lanes
+// without work stay in the shuffles.
 template <int D, int QKV_STEPS>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int num_kv, const float* __restrict__ q_w,
@@ -110,6 +111,7 @@ qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int nu
   constexpr int LW = D / 8;                  // lanes of a row
   constexpr int ROWS = 32 / LW;              // rows of a warp, side by side
   constexpr int CHUNK = ROWS * QKV_STEPS;    // heads of a token that one warp takes
+  constexpr int HALF = D / 2;
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,21 +137,19 @@ qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int nu
     if (lane == 0) ullm_report(status, ULLM_STATUS_POSITION, t, pos);
     pos = 0;
   }
-  uint4 raw[QKV_STEPS];
+  uint2 raw_lo[QKV_STEPS], raw_hi[QKV_STEPS];
 #pragma unroll
   for (int u = 0; u < QKV_STEPS; ++u) {
     const int h = h0 + u * ROWS + sub;
     // key and value rows of a token without a slot (padding, or an execution that reads another one's cache) are skipped
     const bool live = h < heads && (h < num_q || slot >= 0);
-    raw[u] = live ? *reinterpret_cast<const uint4*>(qkv + ((long long)t * heads + h) * D + sl * 8) : make_uint4(0, 0, 0, 0);
+    const __nv_bfloat16* row = qkv + ((long long)t * heads + h) * D + sl * 4;
+    raw_lo[u] = live ? *reinterpret_cast<const uint2*>(row) : make_uint2(0, 0);
+    raw_hi[u] = live ? *reinterpret_cast<const uint2*>(row + HALF) : make_uint2(0, 0);
   }
-  const int j0 = (sl % (LW / 2)) * 8;  // index into the half-size tables
-  const float* cr = cos_t + (long long)pos * (D / 2) + j0;
-  const float* sr = sin_t + (long long)pos * (D / 2) + j0;
-  const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
-  const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
-  const float c8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-  const float s8[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  const float4 c4 = *reinterpret_cast<const float4*>(cos_t + (long long)pos * HALF + sl * 4);
+  const float4 s4 = *reinterpret_cast<const float4*>(sin_t + (long long)pos * HALF + sl * 4);
+  const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 
 #pragma unroll
   for (int u = 0; u < QKV_STEPS; ++u) {
@@ -157,37 +157,45 @@ qk_norm_rope_store_bf16_kernel(__nv_bfloat16* qkv, int tokens, int num_q, int nu
     const bool is_q = h < num_q, is_k = !is_q && h < num_q + num_kv;
     const bool live = h < heads && (is_q || slot >= 0);
     if (live && !is_q && !is_k) {  // value row: plain copy
-      *reinterpret_cast<uint4*>(v_cache + (slot * num_kv + (h - num_q - num_kv)) * D + sl * 8) = raw[u];
+      __nv_bfloat16* dst = v_cache + (slot * num_kv + (h - num_q - num_kv)) * D + sl * 4;
+      *reinterpret_cast<uint2*>(dst) = raw_lo[u];
+      *reinterpret_cast<uint2*>(dst + HALF) = raw_hi[u];
     }
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw[u]);
-    float y[8];
+    const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&raw_lo[u]);
+    const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&raw_hi[u]);
+    const float2 l01 = __bfloat1622float2(pl[0]), l23 = __bfloat1622float2(pl[1]);
+    const float2 h01 = __bfloat1622float2(ph[0]), h23 = __bfloat1622float2(ph[1]);
+    float lo[4] = {l01.x, l01.y, l23.x, l23.y}, hi[4] = {h01.x, h01.y, h23.x, h23.y};
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      y[i] = __bfloat162float(e[i]);
-      ss += y[i] * y[i];
-    }
-    const float* w = is_q ? q_w : k_w;
+    for (int i = 0; i < 4; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
 #pragma unroll
     for (int off = LW / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);  // every lane takes part
+    const float* w = is_q ? q_w : k_w;
     if (w != nullptr) {
       const float rstd = rsqrtf(ss / (float)D + eps);
-      const float4 w0 = *reinterpret_cast<const float4*>(w + sl * 8), w1 = *reinterpret_cast<const float4*>(w + sl * 8 + 4);
-      y[0] *= rstd * w0.x; y[1] *= rstd * w0.y; y[2] *= rstd * w0.z; y[3] *= rstd * w0.w;
-      y[4] *= rstd * w1.x; y[5] *= rstd * w1.y; y[6] *= rstd * w1.z; y[7] *= rstd * w1.w;
+      const float4 w0 = *reinterpret_cast<const float4*>(w + sl * 4), w1 = *reinterpret_cast<const float4*>(w + HALF + sl * 4);
+      lo[0] *= rstd * w0.x; lo[1] *= rstd * w0.y; lo[2] *= rstd * w0.z; lo[3] *= rstd * w0.w;
+      hi[0] *= rstd * w1.x; hi[1] *= rstd * w1.y; hi[2] *= rstd * w1.z; hi[3] *= rstd * w1.w;
     }
-    uint4 ov;
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&ov);
+    float ol[4], oh[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float partner = __shfl_xor_sync(0xffffffffu, y[i], LW / 2);
-      const float v = sl < LW / 2 ? y[i] * c8[i] - partner * s8[i] : y[i] * c8[i] + partner * s8[i];
-      o[i] = __float2bfloat16_rn(v);
+    for (int i = 0; i < 4; ++i) {
+      ol[i] = lo[i] * c[i] - hi[i] * sn[i];
+      oh[i] = hi[i] * c[i] + lo[i] * sn[i];
     }
     if (live && (is_q || is_k)) {
-      __nv_bfloat16* dst = is_q ? qkv + ((long long)t * heads + h) * D + sl * 8
-                                : k_cache + (slot * num_kv + (h - num_q)) * D + sl * 8;
-      *reinterpret_cast<uint4*>(dst) = ov;
+      __nv_bfloat16* dst = is_q ? qkv + ((long long)t * heads + h) * D + sl * 4
+                                : k_cache + (slot * num_kv + (h - num_q)) * D + sl * 4;
+      uint2 vl, vh;
+      __nv_bfloat162* ql = reinterpret_cast<__nv_bfloat162*>(&vl);
+      __nv_bfloat162* qh = reinterpret_cast<__nv_bfloat162*>(&vh);
+      ql[0] = __floats2bfloat162_rn(ol[0], ol[1]);
+      ql[1] = __floats2bfloat162_rn(ol[2], ol[3]);
+      qh[0] = __floats2bfloat162_rn(oh[0], oh[1]);
+      qh[1] = __floats2bfloat162_rn(oh[2], oh[3]);
+      *reinterpret_cast<uint2*>(dst) = vl;
+      *reinterpret_cast<uint2*>(dst + HALF) = vh;
     }
   }
 }
