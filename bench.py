@@ -333,7 +333,7 @@ def run_ours(args) -> dict:
         return dt
     WE = max(W, 24)
     user_call(WE)  # warm
-    KE = max(K, 32)
+    KE = max(K, 64)  # (differences of fewer steps are a few percent of noise)
     diffs = []
     for _ in range(5):
         t_short = user_call(WE)
