@@ -763,6 +763,10 @@ def run_decode_attention_probe(args) -> int:
 
     random.seed(1)
     case("8 x 2048", [2048] * 8)
+    case("16 x 2048", [2048] * 16)
+    case("24 x 2048", [2048] * 24)
+    case("32 x 2048", [2048] * 32)
+    case("48 x 2048", [2048] * 48)
     case("64 x 2048", [2048] * 64)
     case("1 x 2048", [2048])
     case("4 x 8192", [8192] * 4)
