@@ -343,7 +343,7 @@ class _DecodeCtx:
     (32, 8, 128, 16, 0), (8, 8, 128, 16, 0), (16, 1, 64, 16, 0), (12, 3, 64, 8, 0), (6, 2, 128, 32, 0),
     (32, 8, 128, 16, 100), (4, 2, 64, 4, 37), (9, 3, 128, 1, 0), (24, 2, 128, 8, 0), (16, 1, 128, 128, 300),
 ])
-@pytest.mark.parametrize("batch", [1, 3, 40])
+@pytest.mark.parametrize("batch", [1, 3, 24, 40])  # (24 requests x 8 kv heads: the pairs that run unsplit in one wave)
 @pytest.mark.parametrize("mode", ["split", "split-merge-kernel", "balanced", "tcgen05"])
 def test_decode_attention_bf16(Hq, Hkv, D, page, window, batch, mode):
     """The three tensor-core decode kernels (every request split alike; the whole batch's keys cut evenly over
