@@ -343,7 +343,7 @@ def run_ours(args) -> dict:
     dbytes = decode_bytes(nums, B, ctx, cfg["hidden_size"])
     achieved = dbytes / (ms / 1e3) / 1e9
     points = {f"decode_b{B}": round(value, 1)}
-    for pb in (1, 8, 64):
+    for pb in (1, 8, 32, 64):
         if pb == B:
             pms, pctx, pgraph = ms, ctx, graph_ms
         else:
