@@ -115,11 +115,38 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
   // that prepares the new key itself starts its first tiles' copies now and waits only then.  What a copy finds
   // in the newest key's slot does not matter: that row is replaced in shared memory below.
   const bool early = fu.cos_t != nullptr;
+  // What the preparation of q needs besides q itself does not depend on that kernel either (the positions are
+  // staged with the block tables; tables and norm weights never change): fetched now, so that after the wait only
+  // q's own loads stand before the first product.
+  int qpos = 0;
+  float2 q_cos[KSTEPS / 2][2], q_sin[KSTEPS / 2][2], q_nw[KSTEPS][2];
   if (early) {
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) {
       if (s < tiles) issue(s);
       cp_async_commit();
+    }
+    qpos = kvl > 0 ? fu.positions[b] : 0;
+    if (qpos < 0 || qpos >= fu.max_positions) {
+      if (threadIdx.x == 0 && kvl > 0) ullm_report(status, ULLM_STATUS_POSITION, b, qpos);
+      qpos = 0;
+    }
+    const int c = (lane & 3) * 2;
+    const float* cr = fu.cos_t + (long long)qpos * (D / 2);
+    const float* sr = fu.sin_t + (long long)qpos * (D / 2);
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS / 2; ++kk) {
+      q_cos[kk][0] = *reinterpret_cast<const float2*>(cr + kk * 16 + c);
+      q_cos[kk][1] = *reinterpret_cast<const float2*>(cr + kk * 16 + 8 + c);
+      q_sin[kk][0] = *reinterpret_cast<const float2*>(sr + kk * 16 + c);
+      q_sin[kk][1] = *reinterpret_cast<const float2*>(sr + kk * 16 + 8 + c);
+    }
+    if (fu.q_w != nullptr) {
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        q_nw[kk][0] = *reinterpret_cast<const float2*>(fu.q_w + kk * 16 + c);
+        q_nw[kk][1] = *reinterpret_cast<const float2*>(fu.q_w + kk * 16 + 8 + c);
+      }
     }
   }
   pdl_wait();
@@ -141,14 +168,9 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
   uint4 new_kv = make_uint4(0, 0, 0, 0);  // this lane's 16 bytes of the new key (lanes < D / 8) or value (the next D / 8)
   bool have_new = false;
   if (fu.cos_t != nullptr) {
-    int qpos = kvl > 0 ? fu.positions[b] : 0;
-    if (qpos < 0 || qpos >= fu.max_positions) {
-      if (threadIdx.x == 0 && kvl > 0) ullm_report(status, ULLM_STATUS_POSITION, b, qpos);
-      qpos = 0;
-    }
     // ---- q: RMSNorm over the head, then the rotation; a thread holds, of rows r0 and r1, the columns
-    // 16 kk + c, + 1, + 8, + 9 for every kk: the rotation partner (D / 2 further) is its own kk + KSTEPS / 2 ----
-    const int c = (lane & 3) * 2;
+    // 16 kk + c, + 1, + 8, + 9 (c = 2 (lane % 4)) for every kk: the rotation partner (D / 2 further) is its own
+    // kk + KSTEPS / 2 ----
     const float* cr = fu.cos_t + (long long)qpos * (D / 2);
     const float* sr = fu.sin_t + (long long)qpos * (D / 2);
 #pragma unroll
@@ -169,15 +191,14 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
         const float rstd = rsqrtf(ss / (float)D + fu.eps);
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
-          const float2 w0 = *reinterpret_cast<const float2*>(fu.q_w + kk * 16 + c);
-          const float2 w1 = *reinterpret_cast<const float2*>(fu.q_w + kk * 16 + 8 + c);
+          const float2 w0 = q_nw[kk][0], w1 = q_nw[kk][1];
           y[kk][0] *= rstd * w0.x, y[kk][1] *= rstd * w0.y, y[kk][2] *= rstd * w1.x, y[kk][3] *= rstd * w1.y;
         }
       }
 #pragma unroll
       for (int kk = 0; kk < KSTEPS / 2; ++kk) {
-        const float2 c0 = *reinterpret_cast<const float2*>(cr + kk * 16 + c), c1 = *reinterpret_cast<const float2*>(cr + kk * 16 + 8 + c);
-        const float2 s0 = *reinterpret_cast<const float2*>(sr + kk * 16 + c), s1 = *reinterpret_cast<const float2*>(sr + kk * 16 + 8 + c);
+        const float2 c0 = q_cos[kk][0], c1 = q_cos[kk][1];
+        const float2 s0 = q_sin[kk][0], s1 = q_sin[kk][1];
         const float cs[4] = {c0.x, c0.y, c1.x, c1.y}, sn[4] = {s0.x, s0.y, s1.x, s1.y};
         float lo4[4], hi4[4];
 #pragma unroll
