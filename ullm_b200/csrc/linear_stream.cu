@@ -236,6 +236,28 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
       for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+      // What the end of an output element adds (the residual, the norm weight of a norm folded behind this
+      // product) is fetched now by the threads that will finish the unit: its way from L2 then runs beside the
+      // k loop, not behind it.
+      float res_pre[NT][4], pw_pre[2] = {0.f, 0.f};
+      const bool finisher = kq == 0 && rank == 0 && (p.act == 0 || mt == 0);
+      if (finisher && (p.residual != nullptr || p.pre_w != nullptr)) {
+        const int u2 = cid + ui * ncl;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int col = p.act ? u2 * 16 + g + 8 * i : u2 * 32 + mt * 16 + g + 8 * i;
+          if (p.pre_w != nullptr && col < p.n_out) pw_pre[i] = __ldg(p.pre_w + col);
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = p.act ? u2 * 16 + g + 8 * (i >> 1) : u2 * 32 + mt * 16 + g + 8 * (i >> 1);
+            const int m = n * 8 + 2 * t + (i & 1);
+            res_pre[n][i] = (p.residual != nullptr && m < p.M && col < p.n_out)
+                                ? __bfloat162float(p.residual[(size_t)m * p.n_out + col]) : 0.f;
+          }
+      }
       for (int kb = 0; kb < nkb; ++kb) {
         if (!failed && !__all_sync(0xffffffffu, mbar_wait(&full_bar[s], parity))) {
           ullm_report(p.status, ULLM_STATUS_TIMEOUT, 52, ui * nkb + kb);  // (the whole warp gives up together)
@@ -303,13 +325,13 @@ __global__ void __launch_bounds__(LS_THREADS, 2) linear_stream_kernel(const __gr
             r += __bfloat162float(p.bias[col]);
           }
           const size_t o = (size_t)m * p.n_out + col;
-          if (p.residual != nullptr) r += __bfloat162float(p.residual[o]);
+          if (p.residual != nullptr) r += res_pre[n_tile][i];
           if (p.out_f32)
             reinterpret_cast<float*>(p.out)[o] = r;
           else
             reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(r);
           if (p.pre_w != nullptr) {
-            p.pre_out[o] = __float2bfloat16_rn(r * __ldg(p.pre_w + col));
+            p.pre_out[o] = __float2bfloat16_rn(r * pw_pre[i >> 1]);
             ss[n_tile][i & 1] += r * r;
           }
         }
