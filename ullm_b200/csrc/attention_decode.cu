@@ -423,15 +423,28 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     cluster.sync();
     for (int idx = split * blockDim.x + threadIdx.x; idx < group * D; idx += num_splits * blockDim.x) {
       const int r = idx / D, d = idx - r * D;
+      // all peers' values first (the loads through distributed shared memory are then in flight together: a
+      // loop that adds as it loads pays their latency once per peer), then the arithmetic, in split order
+      float ms[8], ls[8], as[8];
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) {
+        ms[s2] = -INFINITY, ls[s2] = 0.f, as[s2] = 0.f;
+        if (s2 < num_splits) {
+          const float* peer = cluster.map_shared_rank(cm, s2) + r * (D + 2);
+          ms[s2] = peer[D];
+          ls[s2] = peer[D + 1];
+          as[s2] = peer[d];
+        }
+      }
       float mm = -INFINITY;
-      for (int s2 = 0; s2 < num_splits; ++s2) mm = fmaxf(mm, cluster.map_shared_rank(cm, s2)[r * (D + 2) + D]);
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) mm = fmaxf(mm, ms[s2]);
       float ll = 0.f, acc = 0.f;
-      for (int s2 = 0; s2 < num_splits; ++s2) {
-        const float* peer = cluster.map_shared_rank(cm, s2) + r * (D + 2);
-        const float ms = peer[D];
-        const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-        ll += peer[D + 1] * f;
-        acc += peer[d] * f;
+#pragma unroll
+      for (int s2 = 0; s2 < 8; ++s2) {
+        const float f = ms[s2] == -INFINITY ? 0.f : exp2f(ms[s2] - mm);
+        ll += ls[s2] * f;
+        acc += as[s2] * f;
       }
       out[((long long)b * num_q + kh * group + r) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
     }
