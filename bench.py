@@ -722,6 +722,8 @@ def run_decode_attention_probe(args) -> int:
         pass
 
     def case(name, lens):
+        if args.case is not None and args.case != name:
+            return
         B = len(lens)
         per = [-(-n // page) for n in lens]
         pages = sum(per) + 4
@@ -1182,7 +1184,7 @@ def main() -> int:
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
     ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
                     help="--probe linear --only: which of the decode step's products")
-    ap.add_argument("--case", default=None, help="run only the case of this name (--probe prefill-attention)")
+    ap.add_argument("--case", default=None, help="run only the case of this name (--probe prefill-attention, decode-attention)")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
     args = ap.parse_args()
