@@ -295,13 +295,27 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     }
     // ---- scores: 2 n-tiles of 8 keys ------------------------------------------------
     float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      // even and odd k steps into accumulators of their own (four chains of KSTEPS / 2 dependent products
+      // instead of two of KSTEPS: with one or two warps per scheduler that chain is what a tile waits for)
+      float sd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
-      const int mat = lane >> 3, row = (mat >> 1) * 8 + (lane & 7), ch = 2 * kk + (mat & 1);
-      unsigned b0, b1, b2, b3;
-      ldmatrix_x4(b0, b1, b2, b3, kbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
-      mma_bf16(sc[0], qa[kk], b0, b1);
-      mma_bf16(sc[1], qa[kk], b2, b3);
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int mat = lane >> 3, row = (mat >> 1) * 8 + (lane & 7), ch = 2 * kk + (mat & 1);
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, kbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
+        if (kk & 1) {
+          mma_bf16(sd[0], qa[kk], b0, b1);
+          mma_bf16(sd[1], qa[kk], b2, b3);
+        } else {
+          mma_bf16(sc[0], qa[kk], b0, b1);
+          mma_bf16(sc[1], qa[kk], b2, b3);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[t][e] += sd[t][e];
     }
     // ---- mask, online softmax -------------------------------------------------------
     const int base = w_begin + it * DEC_TILE;
@@ -344,10 +358,14 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
       pa[3] = pack_bf16(p[1][2], p[1][3]);
     }
     // ---- O = alpha O + P V ------------------------------------------------------------
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {  // (most tiles leave the maxima where they are)
+#pragma unroll
+      for (int j = 0; j < NT_O; ++j) {
+        o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+      }
+    }
 #pragma unroll
     for (int j = 0; j < NT_O; j += 2) {
-      o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
-      o[j + 1][0] *= alpha[0]; o[j + 1][1] *= alpha[0]; o[j + 1][2] *= alpha[1]; o[j + 1][3] *= alpha[1];
       const int mat = lane >> 3, row = (mat & 1) * 8 + (lane & 7), ch = j + (mat >> 1);
       unsigned b0, b1, b2, b3;
       ldmatrix_x4_trans(b0, b1, b2, b3, vbuf + row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16));
