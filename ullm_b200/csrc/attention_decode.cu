@@ -47,6 +47,13 @@ struct DecFuse {
   float eps;
 };
 
+// 2^x by the hardware's unit alone (exp2f adds a range fix-up around the same instruction)
+__device__ __forceinline__ float dec_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // CL: the splits of a (request, kv head) pair are the blocks of one thread-block cluster (at most 8) and merge
 // their partials through distributed shared memory; no scratch arrays, no second kernel.
 template <int D, bool CL>
@@ -338,7 +345,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     float alpha[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      alpha[r] = mx[r] == -INFINITY ? 1.f : exp2f(m[r] - mx[r]);
+      alpha[r] = mx[r] == -INFINITY ? 1.f : dec_ex2(m[r] - mx[r]);
       m[r] = mx[r];
       l[r] *= alpha[r];
     }
@@ -349,7 +356,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
       for (int t = 0; t < 2; ++t)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          p[t][e] = m[e >> 1] == -INFINITY ? 0.f : exp2f(sc[t][e] - m[e >> 1]);
+          p[t][e] = m[e >> 1] == -INFINITY ? 0.f : dec_ex2(sc[t][e] - m[e >> 1]);
           l[e >> 1] += p[t][e];
         }
       pa[0] = pack_bf16(p[0][0], p[0][1]);
